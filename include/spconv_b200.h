@@ -1,0 +1,203 @@
+/*
+ * spconv_b200 -- C ABI of the B200 (sm_100a) sparse-convolution hot path.
+ *
+ * One shared library, libspconv_b200.so, replaces the three private modules
+ * the reference's operator layer imports at spconv_triton/pytorch/ops.py:24-30
+ * (`_impl.pairs`, `_impl.gemm`, `_impl.pool`).  Every entry point below names
+ * the reference function it stands in for.
+ *
+ * Conventions
+ *   - all data pointers are DEVICE pointers owned by the caller (PyTorch
+ *     allocates them); the library allocates nothing except where noted;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and
+ *     the call returns without synchronising, except spc_rulebook_prepare,
+ *     which must hand the data-dependent output count back to the host (the
+ *     reference synchronises at the same point, _impl/pairs.py:209);
+ *   - every function returns an spc_status; spc_last_error() gives the text
+ *     of the last failure on the calling thread;
+ *   - row-major, contiguous tensors; indices are int32 [n, ndim+1] with the
+ *     batch index in column 0, exactly as SparseConvTensor.indices.
+ */
+#ifndef SPCONV_B200_H_
+#define SPCONV_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SPC_MAX_NDIM 4
+
+typedef enum {
+  SPC_OK = 0,
+  SPC_ERR_INVALID_ARGUMENT = 1,
+  SPC_ERR_CUDA = 2,
+  SPC_ERR_WORKSPACE_TOO_SMALL = 3,
+  SPC_ERR_HASH_TABLE_FULL = 4,
+  SPC_ERR_UNSUPPORTED = 5,
+  SPC_ERR_DEVICE_WAIT_EXPIRED = 6,
+  SPC_ERR_SIZE_LIMIT = 7
+} spc_status;
+
+typedef enum { SPC_F16 = 0, SPC_BF16 = 1, SPC_F32 = 2, SPC_F64 = 3 } spc_dtype;
+
+/* Arithmetic used for fp32 inputs: IEEE fused multiply-add on the CUDA cores,
+ * or TF32 on the tensor cores (the reference's live SPCONV_ALLOW_TF32 switch,
+ * _impl/gemm.py:460-463).  Ignored for 16-bit inputs, which always multiply
+ * exactly and accumulate in fp32. */
+typedef enum { SPC_PREC_IEEE = 0, SPC_PREC_TF32 = 1 } spc_precision;
+
+/* Which implementation a GEMM entry point may use.  AUTO picks the tcgen05
+ * kernel whenever the shape allows it and the CUDA-core kernel otherwise;
+ * the other two force one of them (SPC_ERR_UNSUPPORTED if impossible). */
+typedef enum { SPC_GEMM_AUTO = 0, SPC_GEMM_SIMT = 1, SPC_GEMM_TCGEN05 = 2 } spc_gemm_path;
+
+/* Geometry of one rulebook.  in_shape/out_shape are the spatial shapes before
+ * and after the layer (the caller computes out_shape with
+ * spc_conv_output_size / spc_deconv_output_size).  For subm the library
+ * ignores stride/padding and uses padding = (ksize/2)*dilation, stride 1
+ * (_impl/pairs.py:182-187). */
+typedef struct {
+  int32_t ndim;
+  int32_t batch_size;
+  int32_t in_shape[SPC_MAX_NDIM];
+  int32_t out_shape[SPC_MAX_NDIM];
+  int32_t ksize[SPC_MAX_NDIM];
+  int32_t stride[SPC_MAX_NDIM];
+  int32_t padding[SPC_MAX_NDIM];
+  int32_t dilation[SPC_MAX_NDIM];
+  int32_t subm;
+  int32_t transpose;
+} spc_geometry;
+
+/* ---- housekeeping ------------------------------------------------------ */
+
+int spc_version(void);
+const char* spc_last_error(void);
+
+/* ---- output-shape formulas --------------------------------------------- */
+
+/* replaces get_conv_output_size, _impl/pairs.py:59-70 (ksize -1 -> 1). */
+int spc_conv_output_size(int ndim, const int32_t* in_shape, const int32_t* ksize,
+                         const int32_t* stride, const int32_t* padding,
+                         const int32_t* dilation, int32_t* out_shape);
+/* replaces get_deconv_output_size, _impl/pairs.py:73-88 (ksize -1 is an error). */
+int spc_deconv_output_size(int ndim, const int32_t* in_shape, const int32_t* ksize,
+                           const int32_t* stride, const int32_t* padding,
+                           const int32_t* dilation, const int32_t* out_padding,
+                           int32_t* out_shape);
+
+/* ---- rulebook generation ----------------------------------------------- */
+
+/* Bytes of device scratch the rulebook calls need for this geometry and
+ * input count.  The same buffer must be passed, untouched, from
+ * spc_rulebook_prepare to the fill call that follows it. */
+size_t spc_rulebook_workspace_bytes(const spc_geometry* g, int64_t n_in);
+
+/* Phase 1 of compute_candidates (_impl/pairs.py:126-220): hashes the input
+ * coordinates; for strided / transposed layers also enumerates every
+ * candidate output coordinate, de-duplicates them in a second hash table,
+ * sorts the unique linear coordinates ascending (the order torch.unique
+ * gives the reference) and numbers them.  Writes the number of output rows
+ * to *n_out_host after synchronising `stream` (subm: n_out = n_in, no
+ * synchronisation).  n_out == 0 is the reference's "points vanished" case. */
+int spc_rulebook_prepare(const spc_geometry* g, const int32_t* indices, int64_t n_in,
+                         void* workspace, size_t workspace_bytes, int64_t* n_out_host,
+                         void* stream);
+
+/* Phase 2, implicit-gemm format: replaces igemm_pairs, _impl/pairs.py:281-426.
+ *   out_indices  [n_out, ndim+1] (NULL for subm: the output rows are the input rows)
+ *   pair_fwd     [kv, n_out]  input row feeding (offset, output row), -1 if none
+ *   pair_bwd     [kv, n_in]   output row fed by (offset, input row), -1; NULL to skip
+ *   mask_fwd     [n_split, n_out, ceil(kv/32)] sorted per-row offset bitmasks
+ *   argsort_fwd  [n_split, n_out] original row of each sorted slot
+ *   mask_bwd / argsort_bwd  same over the n_in rows of pair_bwd; NULL to skip
+ *   split_masks  n_split host words ANDed into mask word 0 (0xFFFFFFFF for
+ *                MaskImplicitGemm; the two MaskSplit halves otherwise)
+ *   n_out may be smaller than the prepared count (num_out_act_bound): rows
+ *   beyond it are dropped, as _impl/pairs.py:318-323 does. */
+int spc_rulebook_igemm(const spc_geometry* g, const int32_t* indices, int64_t n_in,
+                       int64_t n_out, void* workspace, size_t workspace_bytes,
+                       int32_t* out_indices, int32_t* pair_fwd, int32_t* pair_bwd,
+                       int32_t* mask_fwd, int32_t* argsort_fwd, int32_t* mask_bwd,
+                       int32_t* argsort_bwd, const uint32_t* split_masks, int n_split,
+                       int do_sort, void* stream);
+
+/* Phase 2, Native format: replaces native_pairs, _impl/pairs.py:223-278.
+ *   pair [2, kv, n_in] (-1 fill): per offset the contributing input rows in
+ *   ascending order and their output rows; indice_num_per_loc [kv]. */
+int spc_rulebook_native(const spc_geometry* g, const int32_t* indices, int64_t n_in,
+                        int64_t n_out, void* workspace, size_t workspace_bytes,
+                        int32_t* out_indices, int32_t* pair, int32_t* indice_num_per_loc,
+                        void* stream);
+
+/* replaces native_pair_to_tables, _impl/pairs.py:429-469.  pair is
+ * [2, kv, n_pair]; pair_fwd [kv, n_out]; pair_bwd [kv, n_in] or NULL. */
+int spc_native_to_tables(const int32_t* pair, int kv, int64_t n_pair, int inverse,
+                         int32_t* pair_fwd, int64_t n_out, int32_t* pair_bwd, int64_t n_in,
+                         void* stream);
+
+/* ---- implicit gather-GEMM ---------------------------------------------- */
+
+/* Forward: replaces conv_forward, _impl/gemm.py:501-568.
+ *   out[m, n] = sum_k sum_c features[pair_fwd[k, m], c] * weight[n, k, c] (+ bias[n])
+ *   features [n_in, c_in] dtype; weight [c_out, kv, c_in] dtype (KRSC);
+ *   bias [c_out] dtype or NULL; out [n_out, c_out] out_dtype;
+ *   mask_argsort [n_out] or NULL: the order in which rows are grouped into
+ *   tiles (rows with equal offset bitmasks become neighbours). */
+int spc_conv_forward(const void* features, const void* weight, const void* bias,
+                     const int32_t* pair_fwd, const int32_t* mask_argsort, void* out,
+                     int64_t n_in, int64_t n_out, int c_in, int c_out, int kv, int dtype,
+                     int out_dtype, int precision, int path, void* stream);
+
+/* Input gradient: replaces conv_backward_input, _impl/gemm.py:571-631.
+ *   din[j, c] = sum_k sum_n grad_out[pair_bwd[k, j], n] * weight[n, k, c]
+ *   grad_out [n_out, c_out]; din [n_in, c_in], both `dtype`. */
+int spc_conv_backward_input(const void* grad_out, const void* weight,
+                            const int32_t* pair_bwd, const int32_t* mask_argsort, void* din,
+                            int64_t n_in, int64_t n_out, int c_in, int c_out, int kv,
+                            int dtype, int precision, int path, void* stream);
+
+/* Bytes of device scratch spc_conv_backward_weight needs (fp32 partial sums
+ * of the split reduction). */
+size_t spc_conv_backward_weight_workspace_bytes(int64_t n_out, int c_in, int c_out, int kv);
+
+/* Weight gradient: replaces conv_backward_weight, _impl/gemm.py:634-713.
+ *   dweight[n, k, c] = sum over m with pair_fwd[k, m] >= 0 of
+ *                      features[pair_fwd[k, m], c] * grad_out[m, n]
+ *   dweight [c_out, kv, c_in] dtype.  The reduction over rows is split into
+ *   chunks whose fp32 partial sums live in `workspace` and are added in a
+ *   fixed order, so the result is deterministic. */
+int spc_conv_backward_weight(const void* features, const void* grad_out,
+                             const int32_t* pair_fwd, void* dweight, void* workspace,
+                             size_t workspace_bytes, int64_t n_in, int64_t n_out, int c_in,
+                             int c_out, int kv, int dtype, int precision, int path,
+                             void* stream);
+
+/* ---- sparse pooling ---------------------------------------------------- */
+
+/* replaces maxpool_forward, _impl/pool.py:260-288: accumulator starts at 0. */
+int spc_maxpool_forward(const void* features, const int32_t* pair_fwd, void* out,
+                        int64_t n_out, int channels, int kv, int dtype, void* stream);
+/* replaces maxpool_backward, _impl/pool.py:291-330: every input equal to the
+ * output receives the gradient. */
+int spc_maxpool_backward(const void* features, const void* out_features, const void* grad_out,
+                         const int32_t* pair_bwd, void* din, int64_t n_in, int channels,
+                         int kv, int dtype, void* stream);
+/* replaces avgpool_forward, _impl/pool.py:333-364: mean over the inputs that
+ * are present; count [n_out] int32 (may be NULL). */
+int spc_avgpool_forward(const void* features, const int32_t* pair_fwd, void* out,
+                        int32_t* count, int64_t n_out, int channels, int kv, int dtype,
+                        void* stream);
+/* replaces avgpool_backward, _impl/pool.py:367-397: the gradient is
+ * multiplied by the window count (the reference's behaviour). */
+int spc_avgpool_backward(const void* grad_out, const int32_t* pair_bwd, const int32_t* count,
+                         void* din, int64_t n_in, int channels, int kv, int dtype,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPCONV_B200_H_ */
