@@ -1,0 +1,92 @@
+// C-ABI entry points of the implicit gather-GEMM and the choice between the
+// tcgen05 kernels and the CUDA-core kernels.
+#include "common.cuh"
+#include "gemm_internal.cuh"
+
+using namespace spc;
+
+namespace {
+
+bool is_16bit(int dtype) { return dtype == SPC_F16 || dtype == SPC_BF16; }
+
+// The tensor-core kernels take 16-bit inputs always and fp32 inputs only when
+// the caller allows TF32; IEEE fp32 stays on the CUDA cores.
+bool want_tc(int path, int n_dim, int r_dim, int kv, int dtype, int out_dtype, int precision, int* status) {
+  *status = SPC_OK;
+  const bool ok = gather_gemm_tc_supported(n_dim, r_dim, kv, dtype, out_dtype, precision);
+  if (path == SPC_GEMM_SIMT) return false;
+  if (path == SPC_GEMM_TCGEN05) {
+    if (!ok) *status = fail(SPC_ERR_UNSUPPORTED, "tcgen05 path does not take this shape/dtype "
+                            "(n=%d r=%d kv=%d dtype=%d precision=%d)", n_dim, r_dim, kv, dtype, precision);
+    return ok;
+  }
+  return ok;
+}
+
+}  // namespace
+
+extern "C" int spc_conv_forward(const void* features, const void* weight, const void* bias,
+                                const int32_t* pair_fwd, const int32_t* mask_argsort, void* out,
+                                int64_t n_in, int64_t n_out, int c_in, int c_out, int kv, int dtype,
+                                int out_dtype, int precision, int path, void* stream) {
+  if (!features || !weight || !pair_fwd || !out || n_in < 0 || n_out < 0 || c_in <= 0 || c_out <= 0 || kv <= 0)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "conv_forward: bad arguments");
+  if (n_out == 0) return SPC_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int status;
+  if (want_tc(path, c_out, c_in, kv, dtype, out_dtype, precision, &status))
+    return gather_gemm_tc(features, weight, bias, pair_fwd, mask_argsort, out, n_out, c_out, c_in, kv,
+                          /*transposed_weight=*/false, dtype, out_dtype, precision, st);
+  if (status != SPC_OK) return status;
+  // weight[n, k, c]: reduction index c has stride 1, output channel n stride kv*c_in.
+  return gather_gemm_simt(features, weight, bias, pair_fwd, mask_argsort, out, n_out, c_out, c_in, kv,
+                          /*s_wk=*/c_in, /*s_wr=*/1, /*s_wn=*/static_cast<long long>(kv) * c_in, dtype,
+                          out_dtype, st);
+}
+
+extern "C" int spc_conv_backward_input(const void* grad_out, const void* weight, const int32_t* pair_bwd,
+                                       const int32_t* mask_argsort, void* din, int64_t n_in, int64_t n_out,
+                                       int c_in, int c_out, int kv, int dtype, int precision, int path,
+                                       void* stream) {
+  if (!grad_out || !weight || !pair_bwd || !din || n_in < 0 || n_out < 0 || c_in <= 0 || c_out <= 0 || kv <= 0)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "conv_backward_input: bad arguments");
+  if (n_in == 0) return SPC_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int status;
+  if (want_tc(path, c_in, c_out, kv, dtype, dtype, precision, &status))
+    return gather_gemm_tc(grad_out, weight, nullptr, pair_bwd, mask_argsort, din, n_in, c_in, c_out, kv,
+                          /*transposed_weight=*/true, dtype, dtype, precision, st);
+  if (status != SPC_OK) return status;
+  // output channel is c (stride 1), reduction index is n (stride kv*c_in).
+  return gather_gemm_simt(grad_out, weight, nullptr, pair_bwd, mask_argsort, din, n_in, c_in, c_out, kv,
+                          /*s_wk=*/c_in, /*s_wr=*/static_cast<long long>(kv) * c_in, /*s_wn=*/1, dtype, dtype,
+                          st);
+}
+
+extern "C" size_t spc_conv_backward_weight_workspace_bytes(int64_t n_out, int c_in, int c_out, int kv) {
+  if (n_out < 0 || c_in <= 0 || c_out <= 0 || kv <= 0) return 0;
+  return wgrad_split(n_out, c_in, c_out, kv).bytes;
+}
+
+extern "C" int spc_conv_backward_weight(const void* features, const void* grad_out, const int32_t* pair_fwd,
+                                        void* dweight, void* workspace, size_t workspace_bytes, int64_t n_in,
+                                        int64_t n_out, int c_in, int c_out, int kv, int dtype, int precision,
+                                        int path, void* stream) {
+  (void)n_in;
+  (void)precision;
+  if (!features || !grad_out || !pair_fwd || !dweight || n_out < 0 || c_in <= 0 || c_out <= 0 || kv <= 0)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "conv_backward_weight: bad arguments");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_out == 0) {
+    SPC_CUDA_OK(cudaMemsetAsync(dweight, 0, static_cast<size_t>(c_out) * kv * c_in * dtype_size(dtype), st));
+    return SPC_OK;
+  }
+  if (path == SPC_GEMM_TCGEN05)
+    return fail(SPC_ERR_UNSUPPORTED, "conv_backward_weight: no tcgen05 kernel for this op yet");
+  const WgradSplit s = wgrad_split(n_out, c_in, c_out, kv);
+  if (!workspace || workspace_bytes < s.bytes)
+    return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "conv_backward_weight: workspace %zu < %zu bytes", workspace_bytes,
+                s.bytes);
+  return wgrad_simt(features, grad_out, pair_fwd, dweight, static_cast<float*>(workspace), n_out, c_in, c_out,
+                    kv, dtype, st);
+}

@@ -1,0 +1,297 @@
+// CUDA-core implicit gather-GEMM: forward, input gradient and weight gradient.
+//
+// These kernels carry the fp32 IEEE path (Blackwell tensor cores have no IEEE
+// fp32 mode; the reference's default fp32 arithmetic is IEEE,
+// spconv_triton/pytorch/_impl/gemm.py:11-13) and every 16-bit shape the tcgen05
+// kernels do not take (channel counts that are not multiples of 16).  They
+// accumulate in fp32 with fused multiply-add.
+//
+// Forward and input gradient are one kernel with different weight strides,
+// as in the reference (spconv_triton/pytorch/_impl/gemm.py:541-567,604-630).  A tile of
+// BM output rows loops over the kernel offsets; offsets with no contributing
+// row in the tile are skipped after one block-wide vote, which is the
+// reference's tile-bitmask trick (gemm.py:282-296) without needing the mask
+// words, so it also works for kernel volumes above 32.
+#include <algorithm>
+
+#include "common.cuh"
+#include "gemm_internal.cuh"
+
+namespace spc {
+namespace {
+
+template <typename T>
+struct AccOf { using type = float; };
+
+template <typename A, typename T>
+__device__ __forceinline__ A to_acc(T v) { return static_cast<A>(to_float(v)); }
+
+template <typename T, typename A>
+__device__ __forceinline__ T from_acc(A v) { return from_float<T>(static_cast<float>(v)); }
+
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+constexpr int kGemmThreads = (BM / TM) * (BN / TN);  // 256
+
+// out[rm, n] = sum_k sum_r src[pairs[k, rm], r] * w[n*s_wn + k*s_wk + r*s_wr] (+ bias[n])
+template <typename T, typename TO>
+__global__ void __launch_bounds__(kGemmThreads)
+gather_gemm_simt_kernel(const T* __restrict__ src, const T* __restrict__ w, const T* __restrict__ bias,
+                        const int32_t* __restrict__ pairs, const int32_t* __restrict__ order,
+                        TO* __restrict__ out, long long m_rows, int n_dim, int r_dim, int kv,
+                        long long s_wk, long long s_wr, long long s_wn) {
+  using A = typename AccOf<T>::type;
+  __shared__ A As[BK][BM + 4];
+  __shared__ A Bs[BK][BN + 4];
+  __shared__ long long rows_s[BM];
+  __shared__ int idx_s[BM];
+
+  const int tid = threadIdx.x;
+  const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+  const long long m0 = static_cast<long long>(blockIdx.x) * BM;
+  const int n0 = blockIdx.y * BN;
+
+  if (tid < BM) {
+    const long long slot = m0 + tid;
+    rows_s[tid] = slot < m_rows ? (order ? static_cast<long long>(order[slot]) : slot) : -1;
+  }
+  __syncthreads();
+
+  A acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = A(0);
+
+  for (int k = 0; k < kv; ++k) {
+    int mine = -1;
+    if (tid < BM && rows_s[tid] >= 0) mine = __ldg(&pairs[static_cast<long long>(k) * m_rows + rows_s[tid]]);
+    if (tid < BM) idx_s[tid] = mine;
+    if (!__syncthreads_or(mine >= 0)) continue;
+    for (int r0 = 0; r0 < r_dim; r0 += BK) {
+      // A tile: BM x BK, thread loads 4 consecutive reduction channels of one row.
+      {
+        const int row = tid / (BK / 4), c4 = (tid % (BK / 4)) * 4;
+        const int j = idx_s[row];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int r = r0 + c4 + u;
+          A v = A(0);
+          if (j >= 0 && r < r_dim) v = to_acc<A>(src[static_cast<long long>(j) * r_dim + r]);
+          As[c4 + u][row] = v;
+        }
+      }
+      // B tile: BK x BN.
+      {
+        const int n = tid / (BK / 4), c4 = (tid % (BK / 4)) * 4;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int r = r0 + c4 + u;
+          A v = A(0);
+          if (n0 + n < n_dim && r < r_dim) v = to_acc<A>(w[(n0 + n) * s_wn + k * s_wk + r * s_wr]);
+          Bs[c4 + u][n] = v;
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int kk = 0; kk < BK; ++kk) {
+        A a[TM], b[TN];
+#pragma unroll
+        for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+        for (int j = 0; j < TN; ++j) b[j] = Bs[kk][tx * TN + j];
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+          for (int j = 0; j < TN; ++j) acc[i][j] += a[i] * b[j];
+      }
+      __syncthreads();
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const long long rm = rows_s[ty * TM + i];
+    if (rm < 0) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int n = n0 + tx * TN + j;
+      if (n >= n_dim) continue;
+      A v = acc[i][j];
+      if (bias != nullptr) v += to_acc<A>(bias[n]);
+      out[rm * n_dim + n] = from_acc<TO>(v);
+    }
+  }
+}
+
+// Weight gradient partial sums.  grid.x = kv * splits, grid.y tiles c_in,
+// grid.z tiles c_out.  Each block walks its chunk of pair_fwd[k, :], compacts
+// the rows that exist into shared lists with warp ballots, and accumulates
+// g[o,:]^T f[i,:] over them.
+constexpr int WP = 16;  // pairs per accumulation step
+
+template <typename T>
+__global__ void __launch_bounds__(kGemmThreads)
+wgrad_simt_kernel(const T* __restrict__ feats, const T* __restrict__ gout,
+                  const int32_t* __restrict__ pair_fwd, float* __restrict__ partial, long long n_out,
+                  int c_in, int c_out, int kv, int splits, long long rows_per_split) {
+  using A = typename AccOf<T>::type;
+  __shared__ A Gs[WP][BM + 4];  // [pair][out channel]
+  __shared__ A Fs[WP][BN + 4];  // [pair][in channel]
+  __shared__ int list_i[kGemmThreads];
+  __shared__ int list_o[kGemmThreads];
+  __shared__ int warp_cnt[kGemmThreads / 32];
+
+  const int tid = threadIdx.x;
+  const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+  const int k = blockIdx.x / splits, split = blockIdx.x % splits;
+  const int c0 = blockIdx.y * BN, n0 = blockIdx.z * BM;
+  const long long lo = split * rows_per_split;
+  const long long hi = min(n_out, lo + rows_per_split);
+
+  A acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = A(0);
+
+  for (long long base = lo; base < hi; base += kGemmThreads) {
+    const long long m = base + tid;
+    const int in_row = m < hi ? __ldg(&pair_fwd[static_cast<long long>(k) * n_out + m]) : -1;
+    const unsigned ballot = __ballot_sync(0xffffffffu, in_row >= 0);
+    const int lane = tid & 31, warp = tid >> 5;
+    if (lane == 0) warp_cnt[warp] = __popc(ballot);
+    __syncthreads();
+    int total = 0, before = 0;
+#pragma unroll
+    for (int wi = 0; wi < kGemmThreads / 32; ++wi) {
+      const int c = warp_cnt[wi];
+      if (wi < warp) before += c;
+      total += c;
+    }
+    if (in_row >= 0) {
+      const int pos = before + __popc(ballot & ((1u << lane) - 1u));
+      list_i[pos] = in_row;
+      list_o[pos] = static_cast<int>(m - base);
+    }
+    __syncthreads();
+    for (int p0 = 0; p0 < total; p0 += WP) {
+      {
+        const int p = tid / 16, ch4 = (tid % 16) * 4;  // 16 pairs x 64 channels
+        const bool live = p0 + p < total;
+        const long long o = live ? base + list_o[p0 + p] : 0;
+        const long long i = live ? list_i[p0 + p] : 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int n = n0 + ch4 + u, c = c0 + ch4 + u;
+          Gs[p][ch4 + u] = (live && n < c_out) ? to_acc<A>(gout[o * c_out + n]) : A(0);
+          Fs[p][ch4 + u] = (live && c < c_in) ? to_acc<A>(feats[i * c_in + c]) : A(0);
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int pp = 0; pp < WP; ++pp) {
+        A a[TM], b[TN];
+#pragma unroll
+        for (int i = 0; i < TM; ++i) a[i] = Gs[pp][ty * TM + i];
+#pragma unroll
+        for (int j = 0; j < TN; ++j) b[j] = Fs[pp][tx * TN + j];
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+          for (int j = 0; j < TN; ++j) acc[i][j] += a[i] * b[j];
+      }
+      __syncthreads();
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int n = n0 + ty * TM + i;
+    if (n >= c_out) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int c = c0 + tx * TN + j;
+      if (c >= c_in) continue;
+      partial[((static_cast<long long>(split) * c_out + n) * kv + k) * c_in + c] = static_cast<float>(acc[i][j]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+wgrad_reduce_kernel(const float* __restrict__ partial, T* __restrict__ dw, long long elems, int splits) {
+  const long long e = blockIdx.x * 256ll + threadIdx.x;
+  if (e >= elems) return;
+  float s = 0.f;
+  for (int sp = 0; sp < splits; ++sp) s += partial[sp * elems + e];
+  dw[e] = from_acc<T, float>(s);
+}
+
+template <typename T, typename TO>
+int launch_gather(const void* src, const void* w, const void* bias, const int32_t* pairs,
+                  const int32_t* order, void* out, long long m_rows, int n_dim, int r_dim, int kv,
+                  long long s_wk, long long s_wr, long long s_wn, cudaStream_t st) {
+  dim3 grid(static_cast<unsigned>(ceil_div(m_rows, BM)), static_cast<unsigned>(ceil_div(n_dim, BN)));
+  gather_gemm_simt_kernel<T, TO><<<grid, kGemmThreads, 0, st>>>(
+      static_cast<const T*>(src), static_cast<const T*>(w), static_cast<const T*>(bias), pairs, order,
+      static_cast<TO*>(out), m_rows, n_dim, r_dim, kv, s_wk, s_wr, s_wn);
+  SPC_LAUNCH_OK();
+  return SPC_OK;
+}
+
+}  // namespace
+
+int gather_gemm_simt(const void* src, const void* w, const void* bias, const int32_t* pairs,
+                     const int32_t* order, void* out, long long m_rows, int n_dim, int r_dim, int kv,
+                     long long s_wk, long long s_wr, long long s_wn, int dtype, int out_dtype,
+                     cudaStream_t st) {
+#define SPC_GG(T, TO) \
+  return launch_gather<T, TO>(src, w, bias, pairs, order, out, m_rows, n_dim, r_dim, kv, s_wk, s_wr, s_wn, st)
+  if (dtype == SPC_F16 && out_dtype == SPC_F16) SPC_GG(__half, __half);
+  if (dtype == SPC_F16 && out_dtype == SPC_F32) SPC_GG(__half, float);
+  if (dtype == SPC_BF16 && out_dtype == SPC_BF16) SPC_GG(__nv_bfloat16, __nv_bfloat16);
+  if (dtype == SPC_BF16 && out_dtype == SPC_F32) SPC_GG(__nv_bfloat16, float);
+  if (dtype == SPC_F32 && out_dtype == SPC_F32) SPC_GG(float, float);
+  if (dtype == SPC_F32 && out_dtype == SPC_F16) SPC_GG(float, __half);
+#undef SPC_GG
+  return fail(SPC_ERR_UNSUPPORTED, "gather-GEMM: dtype %d -> %d not supported", dtype, out_dtype);
+}
+
+WgradSplit wgrad_split(int64_t n_out, int c_in, int c_out, int kv) {
+  WgradSplit s;
+  const int64_t tiles = static_cast<int64_t>(kv) * ceil_div(c_in, BN) * ceil_div(c_out, BM);
+  int64_t want = ceil_div(2 * 148, std::max<int64_t>(tiles, 1));
+  const int64_t by_len = std::max<int64_t>(1, n_out / 2048);
+  want = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(want, by_len), 64));
+  s.splits = static_cast<int>(want);
+  s.rows_per_split = ceil_div(std::max<int64_t>(n_out, 1), s.splits);
+  s.bytes = static_cast<size_t>(s.splits) * c_out * kv * c_in * sizeof(float);
+  return s;
+}
+
+int wgrad_simt(const void* feats, const void* gout, const int32_t* pair_fwd, void* dw, float* partial,
+               int64_t n_out, int c_in, int c_out, int kv, int dtype, cudaStream_t st) {
+  const WgradSplit s = wgrad_split(n_out, c_in, c_out, kv);
+  dim3 grid(static_cast<unsigned>(kv * s.splits), static_cast<unsigned>(ceil_div(c_in, BN)),
+            static_cast<unsigned>(ceil_div(c_out, BM)));
+  const long long elems = static_cast<long long>(c_out) * kv * c_in;
+  const unsigned rblocks = static_cast<unsigned>(ceil_div(elems, 256));
+#define SPC_WG(T)                                                                                   \
+  do {                                                                                              \
+    wgrad_simt_kernel<T><<<grid, kGemmThreads, 0, st>>>(static_cast<const T*>(feats),               \
+                                                        static_cast<const T*>(gout), pair_fwd,      \
+                                                        partial, n_out, c_in, c_out, kv, s.splits,  \
+                                                        s.rows_per_split);                          \
+    SPC_LAUNCH_OK();                                                                                \
+    wgrad_reduce_kernel<T><<<rblocks, 256, 0, st>>>(partial, static_cast<T*>(dw), elems, s.splits); \
+    SPC_LAUNCH_OK();                                                                                \
+    return SPC_OK;                                                                                  \
+  } while (0)
+  if (dtype == SPC_F16) SPC_WG(__half);
+  if (dtype == SPC_BF16) SPC_WG(__nv_bfloat16);
+  if (dtype == SPC_F32) SPC_WG(float);
+#undef SPC_WG
+  return fail(SPC_ERR_UNSUPPORTED, "wgrad: dtype %d not supported", dtype);
+}
+
+}  // namespace spc

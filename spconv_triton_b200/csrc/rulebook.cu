@@ -1,0 +1,933 @@
+// Rulebook (indice-pair) generation for sparse convolution on B200.
+//
+// Design (differs from the reference on purpose): the reference materialises
+// the kv*N candidate grid (out_lin, valid, out_row) in HBM, sorts the input
+// coordinates, runs kv*N binary searches and scatters into -1 pre-filled
+// tables (spconv_triton/pytorch/_impl/pairs.py:126-426).  Here two open-addressing hash
+// tables keyed by the batch-major linear coordinate replace the sorts and
+// searches, and every table is produced by a GATHER pass with one thread per
+// table column: thread r owns column r of pair_fwd, looks each of the kv
+// neighbour coordinates up (the tables are a few MB and stay in the 126 MB
+// L2), writes pair_fwd[k*n+r] fully coalesced and keeps the row's offset
+// bitmask in a register.  No candidate grid, no pre-fill, no atomics on the
+// tables, and the only ordered step is a radix sort of the n_out unique
+// output coordinates, which reproduces the ascending row numbering that
+// torch.unique gives the reference.
+#include <cub/device/device_radix_sort.cuh>
+
+#include <algorithm>
+#include <climits>
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace spc {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct Geo {
+  int ndim, batch, subm, transpose, kv;
+  int in_shape[SPC_MAX_NDIM], out_shape[SPC_MAX_NDIM];
+  int ksize[SPC_MAX_NDIM], stride[SPC_MAX_NDIM], pad[SPC_MAX_NDIM], dil[SPC_MAX_NDIM];
+};
+
+// ------------------------------------------------------------------------
+// Hash tables.  K64 = false: key < 2^31, slot = (key << 32) | value in one
+// 64-bit word, so a probe is one 8-byte access and an insert one atomicCAS.
+// K64 = true: 64-bit keys with a separate value array.
+// Probing is linear and bounded by the capacity; a full table raises a status
+// flag instead of spinning.
+// ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t mix32(uint32_t h) {
+  h ^= h >> 16;
+  h *= 0x85ebca6bu;
+  h ^= h >> 13;
+  h *= 0xc2b2ae35u;
+  h ^= h >> 16;
+  return h;
+}
+
+template <bool K64>
+struct Table;
+
+template <>
+struct Table<false> {
+  using key_t = uint32_t;
+  unsigned long long* slots;
+  uint32_t cap_mask;
+  static constexpr unsigned long long kEmpty = ~0ull;
+
+  __device__ __forceinline__ uint32_t home(key_t k) const { return mix32(k) & cap_mask; }
+
+  // Keeps the smallest value among equal keys (duplicate coordinates resolve
+  // to the lowest row, as a stable sort + lower bound does in the reference).
+  __device__ bool insert_min(key_t key, uint32_t val) const {
+    const unsigned long long packed = (static_cast<unsigned long long>(key) << 32) | val;
+    uint32_t s = home(key);
+    for (uint32_t probe = 0; probe <= cap_mask; ++probe) {
+      unsigned long long old = atomicCAS(&slots[s], kEmpty, packed);
+      if (old == kEmpty) return true;
+      if (static_cast<key_t>(old >> 32) == key) {
+        atomicMin(&slots[s], packed);
+        return true;
+      }
+      s = (s + 1) & cap_mask;
+    }
+    return false;
+  }
+  // 1: this call inserted the key, 0: already present, -1: table full.
+  __device__ int insert_unique(key_t key) const {
+    const unsigned long long packed = (static_cast<unsigned long long>(key) << 32) | 0x7fffffffu;
+    uint32_t s = home(key);
+    for (uint32_t probe = 0; probe <= cap_mask; ++probe) {
+      unsigned long long old = atomicCAS(&slots[s], kEmpty, packed);
+      if (old == kEmpty) return 1;
+      if (static_cast<key_t>(old >> 32) == key) return 0;
+      s = (s + 1) & cap_mask;
+    }
+    return -1;
+  }
+  __device__ int find(key_t key) const {
+    uint32_t s = home(key);
+    for (uint32_t probe = 0; probe <= cap_mask; ++probe) {
+      const unsigned long long v = __ldg(&slots[s]);
+      if (v == kEmpty) return -1;
+      if (static_cast<key_t>(v >> 32) == key) return static_cast<int>(v & 0xffffffffu);
+      s = (s + 1) & cap_mask;
+    }
+    return -1;
+  }
+  __device__ void set_value(key_t key, uint32_t val) const {
+    uint32_t s = home(key);
+    for (uint32_t probe = 0; probe <= cap_mask; ++probe) {
+      const unsigned long long v = slots[s];
+      if (v == kEmpty) return;
+      if (static_cast<key_t>(v >> 32) == key) {
+        slots[s] = (static_cast<unsigned long long>(key) << 32) | val;
+        return;
+      }
+      s = (s + 1) & cap_mask;
+    }
+  }
+};
+
+template <>
+struct Table<true> {
+  using key_t = unsigned long long;
+  unsigned long long* slots;  // keys
+  int* vals;
+  uint32_t cap_mask;
+  static constexpr unsigned long long kEmpty = ~0ull;
+
+  __device__ __forceinline__ uint32_t home(key_t k) const {
+    return mix32(static_cast<uint32_t>(k) ^ mix32(static_cast<uint32_t>(k >> 32))) & cap_mask;
+  }
+  __device__ bool insert_min(key_t key, uint32_t val) const {
+    uint32_t s = home(key);
+    for (uint32_t probe = 0; probe <= cap_mask; ++probe) {
+      unsigned long long old = atomicCAS(&slots[s], kEmpty, key);
+      if (old == kEmpty || old == key) {
+        atomicMin(&vals[s], static_cast<int>(val));
+        return true;
+      }
+      s = (s + 1) & cap_mask;
+    }
+    return false;
+  }
+  __device__ int insert_unique(key_t key) const {
+    uint32_t s = home(key);
+    for (uint32_t probe = 0; probe <= cap_mask; ++probe) {
+      unsigned long long old = atomicCAS(&slots[s], kEmpty, key);
+      if (old == kEmpty) return 1;
+      if (old == key) return 0;
+      s = (s + 1) & cap_mask;
+    }
+    return -1;
+  }
+  __device__ int find(key_t key) const {
+    uint32_t s = home(key);
+    for (uint32_t probe = 0; probe <= cap_mask; ++probe) {
+      const unsigned long long v = __ldg(&slots[s]);
+      if (v == kEmpty) return -1;
+      if (v == key) return __ldg(&vals[s]);
+      s = (s + 1) & cap_mask;
+    }
+    return -1;
+  }
+  __device__ void set_value(key_t key, uint32_t val) const {
+    uint32_t s = home(key);
+    for (uint32_t probe = 0; probe <= cap_mask; ++probe) {
+      const unsigned long long v = slots[s];
+      if (v == kEmpty) return;
+      if (v == key) {
+        vals[s] = static_cast<int>(val);
+        return;
+      }
+      s = (s + 1) & cap_mask;
+    }
+  }
+};
+
+// ------------------------------------------------------------------------
+// Coordinate arithmetic (follows spconv_triton/pytorch/_impl/pair_kernels.py:66-91).
+// Kernel offsets are enumerated row-major, last dimension fastest, never
+// flipped (spconv_triton/pytorch/_impl/pairs.py:43-48).
+// ------------------------------------------------------------------------
+template <int ND>
+struct Odometer {
+  int pos[ND];
+  __device__ __forceinline__ void reset() {
+#pragma unroll
+    for (int d = 0; d < ND; ++d) pos[d] = 0;
+  }
+  __device__ __forceinline__ void set(const Geo& g, int k) {
+#pragma unroll
+    for (int d = ND - 1; d >= 0; --d) {
+      pos[d] = k % g.ksize[d];
+      k /= g.ksize[d];
+    }
+  }
+  __device__ __forceinline__ void next(const Geo& g) {
+#pragma unroll
+    for (int d = ND - 1; d >= 0; --d) {
+      if (++pos[d] < g.ksize[d]) return;
+      pos[d] = 0;
+    }
+  }
+};
+
+// Output linear coordinate reached from input coordinate `c` through kernel
+// offset `kp`, or -1 if that offset does not produce an output.
+template <int ND>
+__device__ __forceinline__ long long out_key_from_input(const Geo& g, const int* c, const int* kp) {
+  long long lin = c[0];
+#pragma unroll
+  for (int d = 0; d < ND; ++d) {
+    int o;
+    if (g.transpose) {
+      o = c[d + 1] * g.stride[d] + kp[d] * g.dil[d] - g.pad[d];
+    } else {
+      const int num = c[d + 1] + g.pad[d] - kp[d] * g.dil[d];
+      if (num < 0) return -1;
+      o = num / g.stride[d];
+      if (o * g.stride[d] != num) return -1;
+    }
+    if (o < 0 || o >= g.out_shape[d]) return -1;
+    lin = lin * g.out_shape[d] + o;
+  }
+  return lin;
+}
+
+// Input linear coordinate that feeds output coordinate `o` through kernel
+// offset `kp` (the inverse map of out_key_from_input), or -1.
+template <int ND>
+__device__ __forceinline__ long long in_key_from_output(const Geo& g, const int* o, const int* kp) {
+  long long lin = o[0];
+#pragma unroll
+  for (int d = 0; d < ND; ++d) {
+    int x;
+    if (g.transpose) {
+      const int num = o[d + 1] + g.pad[d] - kp[d] * g.dil[d];
+      if (num < 0) return -1;
+      x = num / g.stride[d];
+      if (x * g.stride[d] != num) return -1;
+    } else {
+      x = o[d + 1] * g.stride[d] - g.pad[d] + kp[d] * g.dil[d];
+    }
+    if (x < 0 || x >= g.in_shape[d]) return -1;
+    lin = lin * g.in_shape[d] + x;
+  }
+  return lin;
+}
+
+template <int ND>
+__device__ __forceinline__ void load_coord(const int32_t* __restrict__ idx, long long row, int* c) {
+#pragma unroll
+  for (int d = 0; d <= ND; ++d) c[d] = __ldg(&idx[row * (ND + 1) + d]);
+}
+
+template <int ND>
+__device__ __forceinline__ long long in_key_of(const Geo& g, const int* c) {
+  long long lin = c[0];
+#pragma unroll
+  for (int d = 0; d < ND; ++d) lin = lin * g.in_shape[d] + c[d + 1];
+  return lin;
+}
+
+template <int ND>
+__device__ __forceinline__ void delinearize_out(const Geo& g, long long lin, int* c) {
+#pragma unroll
+  for (int d = ND - 1; d >= 0; --d) {
+    c[d + 1] = static_cast<int>(lin % g.out_shape[d]);
+    lin /= g.out_shape[d];
+  }
+  c[0] = static_cast<int>(lin);
+}
+
+enum Counter { kUniqueCount = 0, kStatus = 1 };
+
+// ------------------------------------------------------------------------
+// Phase 1 kernels
+// ------------------------------------------------------------------------
+template <int ND, bool K64>
+__global__ void __launch_bounds__(kThreads)
+insert_inputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n,
+                     Table<K64> tin, int* counters) {
+  const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  if (j >= n) return;
+  int c[ND + 1];
+  load_coord<ND>(idx, j, c);
+  using key_t = typename Table<K64>::key_t;
+  if (!tin.insert_min(static_cast<key_t>(in_key_of<ND>(g, c)), static_cast<uint32_t>(j)))
+    atomicExch(&counters[kStatus], SPC_ERR_HASH_TABLE_FULL);
+}
+
+// One thread per input row walks the kv offsets and inserts each candidate
+// output coordinate into the output table; first-time inserts are appended to
+// `uniq` through a warp-aggregated counter.
+template <int ND, bool K64>
+__global__ void __launch_bounds__(kThreads)
+enumerate_outputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n,
+                         Table<K64> tout, typename Table<K64>::key_t* __restrict__ uniq,
+                         int* counters) {
+  using key_t = typename Table<K64>::key_t;
+  const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  const bool live = j < n;
+  int c[ND + 1];
+  if (live) load_coord<ND>(idx, j, c);
+  Odometer<ND> od;
+  od.reset();
+  const unsigned lane = threadIdx.x & 31u;
+  for (int k = 0; k < g.kv; ++k) {
+    long long key = live ? out_key_from_input<ND>(g, c, od.pos) : -1;
+    int fresh = 0;
+    if (key >= 0) {
+      const int r = tout.insert_unique(static_cast<key_t>(key));
+      if (r < 0) atomicExch(&counters[kStatus], SPC_ERR_HASH_TABLE_FULL);
+      fresh = r > 0;
+    }
+    const unsigned ballot = __ballot_sync(0xffffffffu, fresh);
+    if (ballot) {
+      int base = 0;
+      const int leader = __ffs(ballot) - 1;
+      if (lane == static_cast<unsigned>(leader)) base = atomicAdd(&counters[kUniqueCount], __popc(ballot));
+      base = __shfl_sync(0xffffffffu, base, leader);
+      if (fresh) uniq[base + __popc(ballot & ((1u << lane) - 1u))] = static_cast<key_t>(key);
+    }
+    od.next(g);
+  }
+}
+
+template <bool K64>
+__global__ void __launch_bounds__(kThreads)
+assign_ranks_kernel(Table<K64> tout, const typename Table<K64>::key_t* __restrict__ sorted,
+                    long long n_out) {
+  const long long r = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  if (r < n_out) tout.set_value(sorted[r], static_cast<uint32_t>(r));
+}
+
+// ------------------------------------------------------------------------
+// Phase 2 kernels (implicit-gemm tables)
+// ------------------------------------------------------------------------
+// Column r of pair_fwd: for each offset the input row that feeds output row r.
+// SUBM_BWD additionally writes pair_bwd, which for a submanifold layer is
+// pair_fwd with the offset axis reversed (offset k seen from the input side is
+// offset kv-1-k seen from the output side).
+template <int ND, bool K64, bool SUBM_BWD>
+__global__ void __launch_bounds__(kThreads)
+fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
+                const typename Table<K64>::key_t* __restrict__ sorted_out, long long n_out,
+                Table<K64> tin, int32_t* __restrict__ out_indices, int32_t* __restrict__ pair_fwd,
+                int32_t* __restrict__ pair_bwd, uint32_t* __restrict__ words, int mic) {
+  using key_t = typename Table<K64>::key_t;
+  const long long r = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  if (r >= n_out) return;
+  int o[ND + 1];
+  if (g.subm) {
+    load_coord<ND>(idx, r, o);
+  } else {
+    delinearize_out<ND>(g, static_cast<long long>(sorted_out[r]), o);
+#pragma unroll
+    for (int d = 0; d <= ND; ++d) out_indices[r * (ND + 1) + d] = o[d];
+  }
+  Odometer<ND> od;
+  od.reset();
+  uint32_t word = 0;
+  for (int k = 0; k < g.kv; ++k) {
+    const long long key = in_key_from_output<ND>(g, o, od.pos);
+    const int j = key >= 0 ? tin.find(static_cast<key_t>(key)) : -1;
+    pair_fwd[static_cast<long long>(k) * n_out + r] = j;
+    if (SUBM_BWD) pair_bwd[static_cast<long long>(g.kv - 1 - k) * n_out + r] = j;
+    word |= static_cast<uint32_t>(j >= 0) << (k & 31);
+    if ((k & 31) == 31 || k == g.kv - 1) {
+      words[r * mic + (k >> 5)] = word;
+      word = 0;
+    }
+    od.next(g);
+  }
+}
+
+// Column j of pair_bwd (strided / transposed layers): for each offset the
+// output row that input row j contributes to.
+template <int ND, bool K64>
+__global__ void __launch_bounds__(kThreads)
+fill_bwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n_in,
+                long long n_out, Table<K64> tout, int32_t* __restrict__ pair_bwd,
+                uint32_t* __restrict__ words, int mic) {
+  using key_t = typename Table<K64>::key_t;
+  const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  if (j >= n_in) return;
+  int c[ND + 1];
+  load_coord<ND>(idx, j, c);
+  Odometer<ND> od;
+  od.reset();
+  uint32_t word = 0;
+  for (int k = 0; k < g.kv; ++k) {
+    const long long key = out_key_from_input<ND>(g, c, od.pos);
+    int r = key >= 0 ? tout.find(static_cast<key_t>(key)) : -1;
+    if (r >= n_out) r = -1;  // rows cut off by num_out_act_bound
+    pair_bwd[static_cast<long long>(k) * n_in + j] = r;
+    if (words != nullptr) {
+      word |= static_cast<uint32_t>(r >= 0) << (k & 31);
+      if ((k & 31) == 31 || k == g.kv - 1) {
+        words[j * mic + (k >> 5)] = word;
+        word = 0;
+      }
+    }
+    od.next(g);
+  }
+}
+
+// keys[i] = words[rows[i], w] & and_mask ; rows == nullptr means identity.
+__global__ void __launch_bounds__(kThreads)
+gather_mask_word_kernel(const uint32_t* __restrict__ words, const int32_t* __restrict__ rows,
+                        long long n, int mic, int w, uint32_t and_mask, uint32_t* __restrict__ keys,
+                        int32_t* __restrict__ iota) {
+  const long long i = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  if (i >= n) return;
+  const long long row = rows ? rows[i] : i;
+  keys[i] = words[row * mic + w] & and_mask;
+  if (iota) iota[i] = static_cast<int32_t>(i);
+}
+
+// mask_out[i, w] = words[rows[i], w] (word 0 ANDed with and_mask); argsort_out[i] = rows[i].
+__global__ void __launch_bounds__(kThreads)
+emit_sorted_masks_kernel(const uint32_t* __restrict__ words, const int32_t* __restrict__ rows,
+                         long long n, int mic, uint32_t and_mask, int32_t* __restrict__ mask_out,
+                         int32_t* __restrict__ argsort_out) {
+  const long long i = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  if (i >= n) return;
+  const long long row = rows ? rows[i] : i;
+  for (int w = 0; w < mic; ++w) {
+    uint32_t v = words[row * mic + w];
+    if (w == 0) v &= and_mask;
+    mask_out[i * mic + w] = static_cast<int32_t>(v);
+  }
+  argsort_out[i] = static_cast<int32_t>(row);
+}
+
+// ------------------------------------------------------------------------
+// Phase 2 kernels (Native format): per offset, a stable compaction of the
+// contributing input rows.  Grid = (row blocks, kv).
+// ------------------------------------------------------------------------
+template <int ND, bool K64>
+__device__ __forceinline__ int native_out_row(const Geo& g, const int32_t* __restrict__ idx,
+                                              long long j, int k, long long n_out,
+                                              const Table<K64>& lookup) {
+  using key_t = typename Table<K64>::key_t;
+  int c[ND + 1];
+  load_coord<ND>(idx, j, c);
+  Odometer<ND> od;
+  od.set(g, k);
+  const long long key = out_key_from_input<ND>(g, c, od.pos);
+  if (key < 0) return -1;
+  const int r = lookup.find(static_cast<key_t>(key));
+  return (r >= n_out) ? -1 : r;
+}
+
+template <int ND, bool K64>
+__global__ void __launch_bounds__(kThreads)
+native_count_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n_in,
+                    long long n_out, Table<K64> lookup, int* __restrict__ block_counts) {
+  const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  const int k = blockIdx.y;
+  const int ok = (j < n_in) && native_out_row<ND, K64>(g, idx, j, k, n_out, lookup) >= 0;
+  const int total = __syncthreads_count(ok);
+  if (threadIdx.x == 0) block_counts[static_cast<long long>(k) * gridDim.x + blockIdx.x] = total;
+}
+
+// One block per offset: exclusive scan of that offset's block counts (in place)
+// and the per-offset total.
+__global__ void __launch_bounds__(kThreads)
+native_scan_kernel(int* __restrict__ block_counts, int n_blocks, int32_t* __restrict__ npl, int kv,
+                   int subm) {
+  __shared__ int warp_sums[kThreads / 32];
+  __shared__ int carry;
+  const int k = blockIdx.x;
+  int* row = block_counts + static_cast<long long>(k) * n_blocks;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int base = 0; base < n_blocks; base += kThreads) {
+    const int i = base + threadIdx.x;
+    const int v = i < n_blocks ? row[i] : 0;
+    int incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, off);
+      if ((threadIdx.x & 31) >= off) incl += t;
+    }
+    if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = incl;
+    __syncthreads();
+    int warp_off = 0;
+    for (int w = 0; w < (threadIdx.x >> 5); ++w) warp_off += warp_sums[w];
+    const int excl = carry + warp_off + incl - v;
+    if (i < n_blocks) row[i] = excl;
+    __syncthreads();
+    if (threadIdx.x == kThreads - 1) carry = excl + v;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    // subm: counts are reported only for offsets before the centre
+    // (spconv_triton/pytorch/_impl/pairs.py:269-277); the pair content is still complete.
+    npl[k] = (subm && k >= kv / 2) ? 0 : carry;
+  }
+}
+
+template <int ND, bool K64>
+__global__ void __launch_bounds__(kThreads)
+native_write_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n_in,
+                    long long n_out, Table<K64> lookup, const int* __restrict__ block_offsets,
+                    int32_t* __restrict__ pair) {
+  __shared__ int warp_sums[kThreads / 32];
+  const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  const int k = blockIdx.y;
+  const int r = (j < n_in) ? native_out_row<ND, K64>(g, idx, j, k, n_out, lookup) : -1;
+  const unsigned ballot = __ballot_sync(0xffffffffu, r >= 0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) warp_sums[warp] = __popc(ballot);
+  __syncthreads();
+  if (r >= 0) {
+    int pos = block_offsets[static_cast<long long>(k) * gridDim.x + blockIdx.x];
+    for (int w = 0; w < warp; ++w) pos += warp_sums[w];
+    pos += __popc(ballot & ((1u << lane) - 1u));
+    pair[static_cast<long long>(k) * n_in + pos] = static_cast<int32_t>(j);
+    pair[(static_cast<long long>(g.kv) + k) * n_in + pos] = r;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+native_to_tables_kernel(const int32_t* __restrict__ pair_in, const int32_t* __restrict__ pair_out,
+                        int kv, long long n_pair, int32_t* __restrict__ pair_fwd, long long n_out,
+                        int32_t* __restrict__ pair_bwd, long long n_in) {
+  const long long p = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  const int k = blockIdx.y;
+  if (p >= n_pair) return;
+  const int i = pair_in[static_cast<long long>(k) * n_pair + p];
+  const int o = pair_out[static_cast<long long>(k) * n_pair + p];
+  if (i < 0 || o < 0) return;
+  if (o < n_out) pair_fwd[static_cast<long long>(k) * n_out + o] = i;
+  if (pair_bwd != nullptr && i < n_in) pair_bwd[static_cast<long long>(k) * n_in + i] = o;
+}
+
+// ------------------------------------------------------------------------
+// Host side: workspace layout
+// ------------------------------------------------------------------------
+struct Layout {
+  bool k64;
+  int key_bits;
+  int mic;
+  int64_t bound;  // upper bound on n_out
+  uint32_t cap_in, cap_out;
+  int64_t n_blocks_native;
+  size_t off_counters, off_tin, off_tin_vals, off_tout, off_tout_vals, off_uniq, off_sorted;
+  size_t off_words, off_keys_a, off_keys_b, off_vals_a, off_vals_b, off_cub, off_native;
+  size_t cub_bytes, total;
+};
+
+uint32_t pow2_at_least(int64_t v) {
+  uint64_t c = 64;
+  while (c < static_cast<uint64_t>(v)) c <<= 1;
+  return static_cast<uint32_t>(std::min<uint64_t>(c, 1ull << 31));
+}
+
+int gcd_int(int a, int b) { return b == 0 ? a : gcd_int(b, a % b); }
+
+bool make_geo(const spc_geometry* s, Geo* g) {
+  if (s == nullptr || s->ndim < 1 || s->ndim > SPC_MAX_NDIM || s->batch_size <= 0) return false;
+  g->ndim = s->ndim;
+  g->batch = s->batch_size;
+  g->subm = s->subm != 0;
+  g->transpose = (!g->subm) && s->transpose != 0;
+  g->kv = 1;
+  for (int d = 0; d < SPC_MAX_NDIM; ++d) {
+    const bool live = d < s->ndim;
+    g->in_shape[d] = live ? s->in_shape[d] : 1;
+    g->ksize[d] = live ? s->ksize[d] : 1;
+    g->dil[d] = live ? s->dilation[d] : 1;
+    if (live && (g->ksize[d] <= 0 || g->in_shape[d] <= 0 || g->dil[d] <= 0)) return false;
+    if (g->subm) {
+      g->out_shape[d] = g->in_shape[d];
+      g->stride[d] = 1;
+      g->pad[d] = (g->ksize[d] / 2) * g->dil[d];
+    } else {
+      g->out_shape[d] = live ? s->out_shape[d] : 1;
+      g->stride[d] = live ? s->stride[d] : 1;
+      g->pad[d] = live ? s->padding[d] : 0;
+      if (live && (g->out_shape[d] <= 0 || g->stride[d] <= 0)) return false;
+    }
+    g->kv *= g->ksize[d];
+  }
+  return true;
+}
+
+Layout make_layout(const Geo& g, int64_t n_in) {
+  Layout L{};
+  double vol_in = g.batch, vol_out = g.batch;
+  for (int d = 0; d < g.ndim; ++d) {
+    vol_in *= g.in_shape[d];
+    vol_out *= g.out_shape[d];
+  }
+  const double max_lin = std::max(vol_in, vol_out);
+  L.k64 = max_lin >= 2147483648.0;
+  L.key_bits = 1;
+  while (L.key_bits < 63 && static_cast<double>(1ull << L.key_bits) < max_lin) ++L.key_bits;
+  L.mic = (g.kv + 31) / 32;
+  double per_input = 1;
+  for (int d = 0; d < g.ndim; ++d) {
+    int m = g.ksize[d];
+    if (!g.transpose && !g.subm && gcd_int(g.dil[d], g.stride[d]) == 1)
+      m = (g.ksize[d] + g.stride[d] - 1) / g.stride[d];
+    per_input *= m;
+  }
+  if (g.subm) {
+    L.bound = n_in;
+  } else {
+    const double b = std::min(static_cast<double>(n_in) * per_input, vol_out);
+    L.bound = static_cast<int64_t>(std::max(b, 1.0));
+  }
+  L.cap_in = pow2_at_least(2 * n_in);
+  L.cap_out = g.subm ? 0 : pow2_at_least(2 * L.bound);
+  const int64_t n_max = std::max<int64_t>(n_in, L.bound);
+  L.n_blocks_native = ceil_div(std::max<int64_t>(n_in, 1), kThreads);
+  const size_t key_sz = L.k64 ? 8 : 4;
+
+  size_t sort_keys_bytes = 0, sort_pairs_bytes = 0;
+  if (L.k64)
+    cub::DeviceRadixSort::SortKeys(nullptr, sort_keys_bytes, static_cast<unsigned long long*>(nullptr),
+                                   static_cast<unsigned long long*>(nullptr), L.bound);
+  else
+    cub::DeviceRadixSort::SortKeys(nullptr, sort_keys_bytes, static_cast<uint32_t*>(nullptr),
+                                   static_cast<uint32_t*>(nullptr), L.bound);
+  cub::DeviceRadixSort::SortPairs(nullptr, sort_pairs_bytes, static_cast<uint32_t*>(nullptr),
+                                  static_cast<uint32_t*>(nullptr), static_cast<int32_t*>(nullptr),
+                                  static_cast<int32_t*>(nullptr), n_max);
+  L.cub_bytes = std::max(sort_keys_bytes, sort_pairs_bytes);
+
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off = align_up(off + bytes, 256);
+    return at;
+  };
+  L.off_counters = take(256);
+  L.off_tin = take(static_cast<size_t>(L.cap_in) * 8);
+  L.off_tin_vals = take(L.k64 ? static_cast<size_t>(L.cap_in) * 4 : 0);
+  L.off_tout = take(static_cast<size_t>(L.cap_out) * 8);
+  L.off_tout_vals = take(L.k64 ? static_cast<size_t>(L.cap_out) * 4 : 0);
+  L.off_uniq = take(g.subm ? 0 : static_cast<size_t>(L.bound) * key_sz);
+  L.off_sorted = take(g.subm ? 0 : static_cast<size_t>(L.bound) * key_sz);
+  L.off_words = take(static_cast<size_t>(n_max) * L.mic * 4);
+  L.off_keys_a = take(static_cast<size_t>(n_max) * 4);
+  L.off_keys_b = take(static_cast<size_t>(n_max) * 4);
+  L.off_vals_a = take(static_cast<size_t>(n_max) * 4);
+  L.off_vals_b = take(static_cast<size_t>(n_max) * 4);
+  L.off_cub = take(L.cub_bytes);
+  L.off_native = take(static_cast<size_t>(L.n_blocks_native) * g.kv * 4);
+  L.total = off;
+  return L;
+}
+
+template <bool K64>
+Table<K64> table_at(char* ws, size_t off_slots, size_t off_vals, uint32_t cap);
+template <>
+Table<false> table_at<false>(char* ws, size_t off_slots, size_t, uint32_t cap) {
+  Table<false> t;
+  t.slots = reinterpret_cast<unsigned long long*>(ws + off_slots);
+  t.cap_mask = cap ? cap - 1 : 0;
+  return t;
+}
+template <>
+Table<true> table_at<true>(char* ws, size_t off_slots, size_t off_vals, uint32_t cap) {
+  Table<true> t;
+  t.slots = reinterpret_cast<unsigned long long*>(ws + off_slots);
+  t.vals = reinterpret_cast<int*>(ws + off_vals);
+  t.cap_mask = cap ? cap - 1 : 0;
+  return t;
+}
+
+inline unsigned blocks_for(int64_t n) { return static_cast<unsigned>(ceil_div(std::max<int64_t>(n, 1), kThreads)); }
+
+// ------------------------------------------------------------------------
+// Phase 1
+// ------------------------------------------------------------------------
+template <int ND, bool K64>
+int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, char* ws,
+                 int64_t* n_out_host, cudaStream_t st) {
+  using key_t = typename Table<K64>::key_t;
+  int* counters = reinterpret_cast<int*>(ws + L.off_counters);
+  SPC_CUDA_OK(cudaMemsetAsync(counters, 0, 256, st));
+  SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin, 0xFF, static_cast<size_t>(L.cap_in) * 8, st));
+  if (K64) SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin_vals, 0x7F, static_cast<size_t>(L.cap_in) * 4, st));
+  Table<K64> tin = table_at<K64>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
+  insert_inputs_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, tin, counters);
+  SPC_LAUNCH_OK();
+  if (g.subm) {
+    *n_out_host = n_in;
+    return SPC_OK;
+  }
+  SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tout, 0xFF, static_cast<size_t>(L.cap_out) * 8, st));
+  if (K64) SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tout_vals, 0x7F, static_cast<size_t>(L.cap_out) * 4, st));
+  Table<K64> tout = table_at<K64>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
+  key_t* uniq = reinterpret_cast<key_t*>(ws + L.off_uniq);
+  key_t* sorted = reinterpret_cast<key_t*>(ws + L.off_sorted);
+  enumerate_outputs_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, tout, uniq, counters);
+  SPC_LAUNCH_OK();
+  int host[2] = {0, 0};
+  SPC_CUDA_OK(cudaMemcpyAsync(host, counters, sizeof(host), cudaMemcpyDeviceToHost, st));
+  SPC_CUDA_OK(cudaStreamSynchronize(st));
+  if (host[kStatus] != 0) return fail(host[kStatus], "rulebook: hash table full (status %d)", host[kStatus]);
+  const int64_t n_out = host[kUniqueCount];
+  *n_out_host = n_out;
+  if (n_out == 0) return SPC_OK;
+  if (n_out > L.bound) return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "rulebook: %lld outputs exceed bound %lld",
+                                   static_cast<long long>(n_out), static_cast<long long>(L.bound));
+  size_t cub_bytes = L.cub_bytes;
+  SPC_CUDA_OK(cub::DeviceRadixSort::SortKeys(ws + L.off_cub, cub_bytes, uniq, sorted, n_out, 0,
+                                              std::min<int>(L.key_bits, sizeof(key_t) * 8), st));
+  assign_ranks_kernel<K64><<<blocks_for(n_out), kThreads, 0, st>>>(tout, sorted, n_out);
+  SPC_LAUNCH_OK();
+  return SPC_OK;
+}
+
+// Sorts the per-row bitmasks (stable, ascending as unsigned, highest word most
+// significant) and emits pair_mask / mask_argsort for every split.
+int emit_masks(const Layout& L, char* ws, int64_t n, int kv, const uint32_t* split_masks, int n_split,
+               int do_sort, int32_t* mask_out, int32_t* argsort_out, cudaStream_t st) {
+  const uint32_t* words = reinterpret_cast<const uint32_t*>(ws + L.off_words);
+  uint32_t* keys_a = reinterpret_cast<uint32_t*>(ws + L.off_keys_a);
+  uint32_t* keys_b = reinterpret_cast<uint32_t*>(ws + L.off_keys_b);
+  int32_t* vals_a = reinterpret_cast<int32_t*>(ws + L.off_vals_a);
+  int32_t* vals_b = reinterpret_cast<int32_t*>(ws + L.off_vals_b);
+  const int mic = L.mic;
+  for (int s = 0; s < n_split; ++s) {
+    const uint32_t and0 = split_masks[s];
+    int32_t* m_out = mask_out + static_cast<int64_t>(s) * n * mic;
+    int32_t* a_out = argsort_out + static_cast<int64_t>(s) * n;
+    const int32_t* rows = nullptr;
+    if (do_sort) {
+      int32_t* cur = vals_a;
+      int32_t* nxt = vals_b;
+      for (int w = 0; w < mic; ++w) {
+        const uint32_t andw = (w == 0) ? and0 : 0xffffffffu;
+        gather_mask_word_kernel<<<blocks_for(n), kThreads, 0, st>>>(
+            words, w == 0 ? nullptr : cur, n, mic, w, andw, keys_a, w == 0 ? cur : nullptr);
+        SPC_LAUNCH_OK();
+        const int bits = std::min(32, kv - 32 * w);
+        size_t cub_bytes = L.cub_bytes;
+        SPC_CUDA_OK(cub::DeviceRadixSort::SortPairs(ws + L.off_cub, cub_bytes, keys_a, keys_b, cur, nxt,
+                                                     n, 0, bits, st));
+        std::swap(cur, nxt);
+      }
+      rows = cur;
+    }
+    emit_sorted_masks_kernel<<<blocks_for(n), kThreads, 0, st>>>(words, rows, n, mic, and0, m_out, a_out);
+    SPC_LAUNCH_OK();
+  }
+  return SPC_OK;
+}
+
+template <int ND, bool K64>
+int igemm_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, int64_t n_out, char* ws,
+               int32_t* out_indices, int32_t* pair_fwd, int32_t* pair_bwd, int32_t* mask_fwd,
+               int32_t* argsort_fwd, int32_t* mask_bwd, int32_t* argsort_bwd,
+               const uint32_t* split_masks, int n_split, int do_sort, cudaStream_t st) {
+  using key_t = typename Table<K64>::key_t;
+  Table<K64> tin = table_at<K64>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
+  Table<K64> tout = table_at<K64>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
+  const key_t* sorted = reinterpret_cast<const key_t*>(ws + L.off_sorted);
+  uint32_t* words = reinterpret_cast<uint32_t*>(ws + L.off_words);
+  if (g.subm && pair_bwd != nullptr)
+    fill_fwd_kernel<ND, K64, true><<<blocks_for(n_out), kThreads, 0, st>>>(
+        g, idx, sorted, n_out, tin, out_indices, pair_fwd, pair_bwd, words, L.mic);
+  else
+    fill_fwd_kernel<ND, K64, false><<<blocks_for(n_out), kThreads, 0, st>>>(
+        g, idx, sorted, n_out, tin, out_indices, pair_fwd, nullptr, words, L.mic);
+  SPC_LAUNCH_OK();
+  int rc = emit_masks(L, ws, n_out, g.kv, split_masks, n_split, do_sort, mask_fwd, argsort_fwd, st);
+  if (rc != SPC_OK) return rc;
+  if (!g.subm && pair_bwd != nullptr) {
+    fill_bwd_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(
+        g, idx, n_in, n_out, tout, pair_bwd, mask_bwd ? words : nullptr, L.mic);
+    SPC_LAUNCH_OK();
+    if (mask_bwd != nullptr) {
+      rc = emit_masks(L, ws, n_in, g.kv, split_masks, n_split, do_sort, mask_bwd, argsort_bwd, st);
+      if (rc != SPC_OK) return rc;
+    }
+  }
+  return SPC_OK;
+}
+
+template <int ND, bool K64>
+int native_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, int64_t n_out, char* ws,
+                int32_t* out_indices, int32_t* pair, int32_t* npl, cudaStream_t st) {
+  using key_t = typename Table<K64>::key_t;
+  Table<K64> tin = table_at<K64>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
+  Table<K64> tout = table_at<K64>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
+  const Table<K64>& lookup = g.subm ? tin : tout;
+  const key_t* sorted = reinterpret_cast<const key_t*>(ws + L.off_sorted);
+  int* block_counts = reinterpret_cast<int*>(ws + L.off_native);
+  const unsigned nb = static_cast<unsigned>(L.n_blocks_native);
+  dim3 grid(nb, static_cast<unsigned>(g.kv));
+  SPC_CUDA_OK(cudaMemsetAsync(pair, 0xFF, static_cast<size_t>(2) * g.kv * n_in * sizeof(int32_t), st));
+  native_count_kernel<ND, K64><<<grid, kThreads, 0, st>>>(g, idx, n_in, n_out, lookup, block_counts);
+  SPC_LAUNCH_OK();
+  native_scan_kernel<<<g.kv, kThreads, 0, st>>>(block_counts, static_cast<int>(nb), npl, g.kv, g.subm);
+  SPC_LAUNCH_OK();
+  native_write_kernel<ND, K64><<<grid, kThreads, 0, st>>>(g, idx, n_in, n_out, lookup, block_counts, pair);
+  SPC_LAUNCH_OK();
+  (void)sorted;
+  (void)out_indices;
+  return SPC_OK;
+}
+
+template <int ND, bool K64>
+__global__ void __launch_bounds__(kThreads)
+write_out_indices_kernel(const __grid_constant__ Geo g,
+                         const typename Table<K64>::key_t* __restrict__ sorted, long long n_out,
+                         int32_t* __restrict__ out_indices) {
+  const long long r = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  if (r >= n_out) return;
+  int o[ND + 1];
+  delinearize_out<ND>(g, static_cast<long long>(sorted[r]), o);
+#pragma unroll
+  for (int d = 0; d <= ND; ++d) out_indices[r * (ND + 1) + d] = o[d];
+}
+
+template <typename F>
+int dispatch(int ndim, bool k64, F&& f) {
+  switch (ndim * 2 + (k64 ? 1 : 0)) {
+    case 2: return f(std::integral_constant<int, 1>{}, std::false_type{});
+    case 3: return f(std::integral_constant<int, 1>{}, std::true_type{});
+    case 4: return f(std::integral_constant<int, 2>{}, std::false_type{});
+    case 5: return f(std::integral_constant<int, 2>{}, std::true_type{});
+    case 6: return f(std::integral_constant<int, 3>{}, std::false_type{});
+    case 7: return f(std::integral_constant<int, 3>{}, std::true_type{});
+    case 8: return f(std::integral_constant<int, 4>{}, std::false_type{});
+    case 9: return f(std::integral_constant<int, 4>{}, std::true_type{});
+    default: return fail(SPC_ERR_INVALID_ARGUMENT, "ndim %d not in 1..4", ndim);
+  }
+}
+
+}  // namespace
+}  // namespace spc
+
+using namespace spc;
+
+extern "C" size_t spc_rulebook_workspace_bytes(const spc_geometry* sg, int64_t n_in) {
+  Geo g;
+  if (!make_geo(sg, &g) || n_in <= 0) return 0;
+  return make_layout(g, n_in).total;
+}
+
+extern "C" int spc_rulebook_prepare(const spc_geometry* sg, const int32_t* indices, int64_t n_in,
+                                    void* workspace, size_t workspace_bytes, int64_t* n_out_host,
+                                    void* stream) {
+  Geo g;
+  if (!make_geo(sg, &g)) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: bad geometry");
+  if (n_in <= 0 || indices == nullptr || n_out_host == nullptr || workspace == nullptr)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: n_in must be > 0 and pointers non-null");
+  if (n_in >= (1ll << 30)) return fail(SPC_ERR_SIZE_LIMIT, "rulebook: n_in %lld too large", (long long)n_in);
+  const Layout L = make_layout(g, n_in);
+  if (workspace_bytes < L.total)
+    return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "rulebook: workspace %zu < %zu bytes", workspace_bytes, L.total);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* ws = static_cast<char*>(workspace);
+  return dispatch(g.ndim, L.k64, [&](auto nd, auto k64) {
+    return prepare_impl<decltype(nd)::value, decltype(k64)::value>(g, L, indices, n_in, ws, n_out_host, st);
+  });
+}
+
+extern "C" int spc_rulebook_igemm(const spc_geometry* sg, const int32_t* indices, int64_t n_in,
+                                  int64_t n_out, void* workspace, size_t workspace_bytes,
+                                  int32_t* out_indices, int32_t* pair_fwd, int32_t* pair_bwd,
+                                  int32_t* mask_fwd, int32_t* argsort_fwd, int32_t* mask_bwd,
+                                  int32_t* argsort_bwd, const uint32_t* split_masks, int n_split,
+                                  int do_sort, void* stream) {
+  Geo g;
+  if (!make_geo(sg, &g)) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: bad geometry");
+  if (n_in <= 0 || n_out <= 0 || !indices || !workspace || !pair_fwd || !mask_fwd || !argsort_fwd ||
+      !split_masks || n_split < 1 || n_split > 2)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: bad arguments");
+  if (!g.subm && out_indices == nullptr)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: out_indices required for non-subm layers");
+  if (g.subm && n_out != n_in) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: subm needs n_out == n_in");
+  if ((mask_bwd == nullptr) != (argsort_bwd == nullptr))
+    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: mask_bwd and argsort_bwd go together");
+  const Layout L = make_layout(g, n_in);
+  if (workspace_bytes < L.total)
+    return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "rulebook: workspace %zu < %zu bytes", workspace_bytes, L.total);
+  if (n_out > L.bound) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: n_out exceeds prepared bound");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* ws = static_cast<char*>(workspace);
+  return dispatch(g.ndim, L.k64, [&](auto nd, auto k64) {
+    return igemm_impl<decltype(nd)::value, decltype(k64)::value>(
+        g, L, indices, n_in, n_out, ws, out_indices, pair_fwd, pair_bwd, mask_fwd, argsort_fwd, mask_bwd,
+        argsort_bwd, split_masks, n_split, do_sort, st);
+  });
+}
+
+extern "C" int spc_rulebook_native(const spc_geometry* sg, const int32_t* indices, int64_t n_in,
+                                   int64_t n_out, void* workspace, size_t workspace_bytes,
+                                   int32_t* out_indices, int32_t* pair, int32_t* indice_num_per_loc,
+                                   void* stream) {
+  Geo g;
+  if (!make_geo(sg, &g)) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: bad geometry");
+  if (n_in <= 0 || n_out <= 0 || !indices || !workspace || !pair || !indice_num_per_loc)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook native: bad arguments");
+  if (!g.subm && out_indices == nullptr)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook native: out_indices required for non-subm layers");
+  const Layout L = make_layout(g, n_in);
+  if (workspace_bytes < L.total)
+    return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "rulebook: workspace %zu < %zu bytes", workspace_bytes, L.total);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* ws = static_cast<char*>(workspace);
+  return dispatch(g.ndim, L.k64, [&](auto nd, auto k64) {
+    constexpr int ND = decltype(nd)::value;
+    constexpr bool K64 = decltype(k64)::value;
+    if (!g.subm) {
+      using key_t = typename Table<K64>::key_t;
+      write_out_indices_kernel<ND, K64><<<blocks_for(n_out), kThreads, 0, st>>>(
+          g, reinterpret_cast<const key_t*>(ws + L.off_sorted), n_out, out_indices);
+      SPC_LAUNCH_OK();
+    }
+    return native_impl<ND, K64>(g, L, indices, n_in, n_out, ws, out_indices, pair, indice_num_per_loc, st);
+  });
+}
+
+extern "C" int spc_native_to_tables(const int32_t* pair, int kv, int64_t n_pair, int inverse,
+                                    int32_t* pair_fwd, int64_t n_out, int32_t* pair_bwd, int64_t n_in,
+                                    void* stream) {
+  if (!pair || !pair_fwd || kv <= 0 || n_pair < 0 || n_out < 0 || n_in < 0)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "native_to_tables: bad arguments");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_out > 0) SPC_CUDA_OK(cudaMemsetAsync(pair_fwd, 0xFF, static_cast<size_t>(kv) * n_out * 4, st));
+  if (pair_bwd && n_in > 0) SPC_CUDA_OK(cudaMemsetAsync(pair_bwd, 0xFF, static_cast<size_t>(kv) * n_in * 4, st));
+  if (n_pair == 0) return SPC_OK;
+  const int32_t* pair_in = pair + static_cast<int64_t>(inverse ? 1 : 0) * kv * n_pair;
+  const int32_t* pair_out = pair + static_cast<int64_t>(inverse ? 0 : 1) * kv * n_pair;
+  dim3 grid(blocks_for(n_pair), static_cast<unsigned>(kv));
+  native_to_tables_kernel<<<grid, kThreads, 0, st>>>(pair_in, pair_out, kv, n_pair, pair_fwd, n_out, pair_bwd, n_in);
+  SPC_LAUNCH_OK();
+  return SPC_OK;
+}

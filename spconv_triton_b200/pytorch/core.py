@@ -1,0 +1,225 @@
+"""SparseConvTensor and the rulebook cache entries kept in its ``indice_dict``.
+
+Attribute names and behaviour follow the reference's
+spconv_triton/pytorch/core.py so that user models run unchanged.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Union
+
+import numpy as np
+import torch
+
+from spconv_triton_b200.constants import SPCONV_FX_TRACE_MODE
+from spconv_triton_b200.core import ConvAlgo
+from spconv_triton_b200.tools import CUDAKernelTimer
+
+try:
+    from torch.fx import ProxyableClassMeta as SpConvTensorMeta
+except Exception:  # pragma: no cover - very old torch
+
+    class SpConvTensorMeta(type):  # type: ignore[no-redef]
+        pass
+
+
+class ThrustSortAllocator:
+    """Constructor-compatible placeholder: scratch memory comes from torch."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.alloced_objs: dict = {}
+        self.device = device
+
+
+class _Record:
+    """Plain attribute bag; subclasses list their fields in ``_fields``."""
+
+    _fields: tuple = ()
+
+    def _assign(self, values: dict):
+        for name in self._fields:
+            setattr(self, name, values[name])
+
+
+class IndiceData(_Record):
+    """Native-format rulebook cached under an ``indice_key`` (reference: core.py:47-76)."""
+
+    _fields = ("out_indices", "indices", "indice_pairs", "indice_pair_num", "spatial_shape",
+               "out_spatial_shape", "is_subm", "algo", "ksize", "stride", "dilation", "padding", "voxel_num")
+
+    def __init__(self, out_indices, indices, indice_pairs, indice_pair_num, spatial_shape, out_spatial_shape,
+                 is_subm: bool, algo: ConvAlgo, ksize, stride, dilation, padding, voxel_num: Any = None):
+        self._assign(locals())
+
+
+class ImplicitGemmIndiceData(_Record):
+    """Implicit-gemm rulebook cached under an ``indice_key`` (reference: core.py:79-120)."""
+
+    _fields = ("out_indices", "indices", "pair_fwd", "pair_bwd", "pair_mask_fwd_splits",
+               "pair_mask_bwd_splits", "mask_argsort_fwd_splits", "mask_argsort_bwd_splits", "masks",
+               "spatial_shape", "out_spatial_shape", "is_subm", "algo", "ksize", "stride", "dilation",
+               "padding", "in_voxel_num", "out_voxel_num")
+
+    def __init__(self, out_indices, indices, pair_fwd, pair_bwd, pair_mask_fwd_splits, pair_mask_bwd_splits,
+                 mask_argsort_fwd_splits, mask_argsort_bwd_splits, masks, spatial_shape, out_spatial_shape,
+                 is_subm: bool, algo: ConvAlgo, ksize, stride, dilation, padding, in_voxel_num: Any = None,
+                 out_voxel_num: Any = None):
+        self._assign(locals())
+
+
+def register_implicit_gemm_indice_data(indice_dict, indice_key, res, indices, *, is_subm, spatial_shape,
+                                       out_spatial_shape, algo, ksize, stride, dilation, padding):
+    """Store the 9-tuple returned by ``ops.get_indice_pairs_implicit_gemm`` under
+    ``indice_key``; a key that already exists is an error (reference: core.py:123-164)."""
+    if indice_key in indice_dict:
+        raise AssertionError(f"your indice key {indice_key} already exists in this sparse tensor.")
+    indice_dict[indice_key] = ImplicitGemmIndiceData(
+        res[0], indices, res[2], res[3], res[4], res[5], res[6], res[7], res[8], spatial_shape,
+        out_spatial_shape, is_subm, algo, ksize, stride, dilation, padding)
+
+
+def scatter_nd(indices, updates, shape):
+    """Dense tensor of ``shape`` with ``updates`` written at ``indices`` (last
+    write wins; reference: core.py:167-178)."""
+    ret = torch.zeros(*shape, dtype=updates.dtype, device=updates.device)
+    ndim = indices.shape[-1]
+    flat = indices.view(-1, ndim)
+    ret[tuple(flat[:, i] for i in range(ndim)) + (Ellipsis,)] = updates.view(
+        *(list(indices.shape[:-1]) + list(shape[ndim:])))
+    return ret
+
+
+class SparseConvTensor(metaclass=SpConvTensorMeta):
+    """features [N, C] + int32 indices [N, ndim+1] (batch index first) +
+    spatial shape + batch size, plus the ``indice_dict`` rulebook cache."""
+
+    def __init__(self, features: torch.Tensor, indices: torch.Tensor, spatial_shape, batch_size: int,
+                 grid: torch.Tensor | None = None, voxel_num: torch.Tensor | None = None,
+                 indice_dict: dict | None = None, benchmark: bool = False,
+                 permanent_thrust_allocator: bool = False, enable_timer: bool = False,
+                 force_algo: ConvAlgo | None = None):
+        if not SPCONV_FX_TRACE_MODE:
+            if features.ndim != 2 or indices.ndim != 2:
+                raise AssertionError
+            if len(spatial_shape) != indices.shape[1] - 1:
+                raise AssertionError("spatial shape must equal to ndim")
+            if indices.dtype != torch.int32:
+                raise AssertionError("only support int32")
+            if batch_size <= 0:
+                raise AssertionError
+        self._features = features
+        self.indices = indices
+        self.spatial_shape = [int(v) for v in spatial_shape]
+        self.batch_size = batch_size
+        self.indice_dict = {} if indice_dict is None else indice_dict
+        self.grid: torch.Tensor | None = torch.Tensor() if grid is None else grid
+        self.voxel_num = voxel_num
+        self.benchmark = benchmark
+        self.benchmark_record: dict = {}
+        self.thrust_allocator = ThrustSortAllocator(features.device) if permanent_thrust_allocator else None
+        self._timer = CUDAKernelTimer(enable_timer)
+        self.force_algo = force_algo
+        self.int8_scale: np.ndarray | None = None
+
+    def __repr__(self):
+        return f"SparseConvTensor[shape={self._features.shape}]"
+
+    # -- features are read-only; replace_feature makes a sibling tensor -------------------------
+    @property
+    def features(self):
+        return self._features
+
+    @features.setter
+    def features(self, val):
+        raise ValueError("you can't set feature directly, use 'x = x.replace_feature(your_new_feature)'"
+                         " to generate new SparseConvTensor instead.")
+
+    def _carry_over(self, other: "SparseConvTensor") -> "SparseConvTensor":
+        other.benchmark_record = self.benchmark_record
+        other.thrust_allocator = self.thrust_allocator
+        other._timer = self._timer
+        other.force_algo = self.force_algo
+        other.int8_scale = self.int8_scale
+        return other
+
+    def replace_feature(self, feature: torch.Tensor):
+        new = SparseConvTensor(feature, self.indices, self.spatial_shape, self.batch_size, self.grid,
+                               self.voxel_num, self.indice_dict)
+        new.benchmark = self.benchmark
+        return self._carry_over(new)
+
+    def shadow_copy(self) -> "SparseConvTensor":
+        """New object sharing every member with this one."""
+        new = SparseConvTensor(self.features, self.indices, self.spatial_shape, self.batch_size, self.grid,
+                               self.voxel_num, self.indice_dict, self.benchmark)
+        return self._carry_over(new)
+
+    def select_by_index(self, valid_indices: torch.Tensor):
+        # assigning to the read-only property raises, as upstream does
+        new = self.shadow_copy()
+        new.indices = self.indices[valid_indices]
+        new.features = self.features[valid_indices]
+        new.indice_dict.clear()
+        return new
+
+    def minus(self):
+        return self.replace_feature(-self.features)
+
+    @property
+    def is_quantized(self):
+        return self.features.dtype == torch.qint8
+
+    def q_scale(self):
+        if self.is_quantized:
+            return self.features.q_scale()
+        raise ValueError("sparse tensor must be quantized")
+
+    def dequantize(self):
+        return self.replace_feature(self.features.dequantize())
+
+    @property
+    def spatial_size(self):
+        return np.prod(self.spatial_shape)
+
+    def find_indice_pair(self, key) -> IndiceData | ImplicitGemmIndiceData | None:
+        return None if key is None else self.indice_dict.get(key)
+
+    @classmethod
+    def from_dense(cls, x: torch.Tensor):
+        """From a channel-last dense tensor [B, *spatial, C]."""
+        sp = x.to_sparse(x.ndim - 1)
+        return cls(sp.values(), sp.indices().permute(1, 0).contiguous().int(), list(sp.shape[1:-1]),
+                   sp.shape[0])
+
+    def dense(self, channels_first: bool = True):
+        shape = [self.batch_size, *self.spatial_shape, self.features.shape[1]]
+        res = scatter_nd(self.indices.to(self.features.device).long(), self.features, shape)
+        if not channels_first:
+            return res
+        ndim = len(self.spatial_shape)
+        return res.permute(0, ndim + 1, *range(1, ndim + 1)).contiguous()
+
+    @staticmethod
+    def _features_of(other):
+        if not isinstance(other, (SparseConvTensor, torch.Tensor)):
+            raise AssertionError
+        return other if isinstance(other, torch.Tensor) else other.features
+
+    def __add__(self, other: Union["SparseConvTensor", torch.Tensor]):
+        return self.replace_feature(self.features + self._features_of(other))
+
+    __radd__ = __add__
+
+    def __iadd__(self, other: Union["SparseConvTensor", torch.Tensor]):
+        self.features += self._features_of(other)
+        return self
+
+
+def expand_nd(ndim: int, val) -> list[int]:
+    if isinstance(val, int):
+        res = [val] * ndim
+    else:
+        res = list(val)
+    if len(res) != ndim:
+        raise AssertionError
+    return [int(v) for v in res]
