@@ -1,0 +1,440 @@
+"""Benchmark of the sparse-convolution hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[2], the configuration its metric is quoted on):
+VoxelNet-style sparse middle encoder, fp16 inference: SubMConv3d 4->16, then
+three stages of [SparseConv3d k3 s2 p1 + 2 x SubMConv3d k3] at 32 / 64 / 64
+channels, BatchNorm + ReLU after every convolution, grid [41, 1600, 1408],
+batch 8, 16k-24k voxels per sample drawn by the seeded plane-plus-clusters
+generator (synthetic stand-in for LiDAR sweeps).  One step = one forward pass
+over one batch; every step sees a different scene, so every step rebuilds its
+seven rulebooks.  Metric: input Mvoxels/s.
+
+With N > 1 (launched by torchrun, one rank per GPU) each rank runs its own
+batches -- the path shards by sample and has no data-path collective -- and
+the value is all ranks' voxels over the slowest rank's device time (weak
+scaling).
+
+``--impl reference`` times the CPU restatement of the reference's algorithm
+(oracle/) on the host cores over a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+GRID = [41, 1600, 1408]
+BATCH = 8
+N_RANGE = (16000, 24000)
+N_SCENES = 4
+
+# kind, c_in, c_out, kernel, stride, padding, indice_key
+LAYERS = [
+    dict(kind="subm", cin=4, cout=16, k=3, s=1, p=1, key="subm0"),
+    dict(kind="conv", cin=16, cout=32, k=3, s=2, p=1, key="down1"),
+    dict(kind="subm", cin=32, cout=32, k=3, s=1, p=1, key="subm1"),
+    dict(kind="subm", cin=32, cout=32, k=3, s=1, p=1, key="subm1"),
+    dict(kind="conv", cin=32, cout=64, k=3, s=2, p=1, key="down2"),
+    dict(kind="subm", cin=64, cout=64, k=3, s=1, p=1, key="subm2"),
+    dict(kind="subm", cin=64, cout=64, k=3, s=1, p=1, key="subm2"),
+    dict(kind="conv", cin=64, cout=64, k=3, s=2, p=1, key="down3"),
+    dict(kind="subm", cin=64, cout=64, k=3, s=1, p=1, key="subm3"),
+    dict(kind="subm", cin=64, cout=64, k=3, s=1, p=1, key="subm3"),
+]
+
+
+def build_backbone():
+    import spconv_triton_b200.pytorch as sp
+
+    mods = []
+    for L in LAYERS:
+        if L["kind"] == "subm":
+            mods.append(sp.SubMConv3d(L["cin"], L["cout"], L["k"], padding=L["p"], bias=False, indice_key=L["key"]))
+        else:
+            mods.append(sp.SparseConv3d(L["cin"], L["cout"], L["k"], stride=L["s"], padding=L["p"], bias=False,
+                                        indice_key=L["key"]))
+        mods.append(torch.nn.BatchNorm1d(L["cout"], eps=1e-3, momentum=0.01))
+        mods.append(torch.nn.ReLU())
+    return sp.SparseSequential(*mods)
+
+
+def init_backbone(net, seed=0):
+    """Random-init weights; BatchNorm gets non-trivial inference statistics."""
+    g = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        for m in net.modules():
+            if isinstance(m, torch.nn.BatchNorm1d):
+                m.weight.copy_(1 + 0.1 * torch.randn(m.num_features, generator=g))
+                m.bias.copy_(0.1 * torch.randn(m.num_features, generator=g))
+                m.running_mean.copy_(0.1 * torch.randn(m.num_features, generator=g))
+                m.running_var.copy_(0.5 + torch.rand(m.num_features, generator=g))
+            elif hasattr(m, "weight_shape"):
+                fan_in = int(np.prod(m.weight_shape[1:]))
+                m.weight.copy_(torch.randn(m.weight_shape, generator=g) * (2.0 / fan_in) ** 0.5)
+    return net
+
+
+def oracle_params(net):
+    """The same weights, as the plain dicts oracle.backbone.run_backbone takes."""
+    mods = list(net._modules.values())
+    params = []
+    for i in range(0, len(mods), 3):
+        conv, bn = mods[i], mods[i + 1]
+        w = conv.weight.detach().float().cpu()
+        params.append(dict(weight=w.reshape(w.shape[0], -1, w.shape[-1]), bn_weight=bn.weight.detach().float().cpu(),
+                           bn_bias=bn.bias.detach().float().cpu(), bn_mean=bn.running_mean.detach().float().cpu(),
+                           bn_var=bn.running_var.detach().float().cpu(), eps=bn.eps))
+    return params
+
+
+def make_scenes(rank, n_scenes=N_SCENES, batch=BATCH):
+    from spconv_triton_b200.scenes import lidar_like_batch
+
+    scenes = []
+    for s in range(n_scenes):
+        idx = lidar_like_batch(1000 * (rank + 1) + s, batch, N_RANGE, tuple(GRID))
+        g = torch.Generator().manual_seed(77 + 1000 * rank + s)
+        feats = torch.rand(idx.shape[0], 4, generator=g).half()
+        scenes.append((torch.from_numpy(idx), feats))
+    return scenes
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons of one GPU every 200 ms."""
+
+    _REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+                0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                bits = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(
+                    nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in self._REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons)}
+
+
+class GemmProfiler:
+    """Wraps the forward gather-GEMM wrapper so that every launch inside the
+    timed region is bracketed by CUDA events on the launching stream and its
+    algorithmic bytes and FLOPs are recorded."""
+
+    def __init__(self):
+        from spconv_triton_b200.pytorch import ops
+
+        self.ops = ops
+        self.records = []
+        self.enabled = False
+        self._pairs_cache = {}
+        self._orig = ops._gemm.conv_forward
+
+    def install(self):
+        orig = self._orig
+
+        def wrapped(features, w, pair_fwd, n_out, *a, **kw):
+            if not self.enabled:
+                return orig(features, w, pair_fwd, n_out, *a, **kw)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = orig(features, w, pair_fwd, n_out, *a, **kw)
+            e1.record()
+            self.records.append((e0, e1, pair_fwd, features.shape[1], w.shape[0], features.element_size(),
+                                 out.element_size()))
+            return out
+
+        self.ops._gemm.conv_forward = wrapped
+
+    def summarize(self):
+        """Aggregate over all recorded launches: algorithmic bytes = gathered
+        rows (pairs*C_in*e) + stored rows (n_out*C_out*e) + table (kv*n_out*4)
+        + weights (kv*C_in*C_out*e); FLOPs = 2*pairs*C_in*C_out."""
+        tot_ms = tot_bytes = tot_flops = 0.0
+        for e0, e1, pf, cin, cout, e_in, e_out in self.records:
+            key = pf.data_ptr()
+            if key not in self._pairs_cache:
+                self._pairs_cache[key] = int((pf >= 0).sum().item())
+            pairs = self._pairs_cache[key]
+            kv, n_out = pf.shape
+            tot_ms += e0.elapsed_time(e1)
+            tot_bytes += pairs * cin * e_in + n_out * cout * e_out + kv * n_out * 4 + kv * cin * cout * e_in
+            tot_flops += 2.0 * pairs * cin * cout
+        n = max(len(self.records), 1)
+        return dict(launches=len(self.records), ms=tot_ms, bytes=tot_bytes, flops=tot_flops,
+                    avg_ms=tot_ms / n)
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d.get("hbm_gbs"), d.get("bf16_tflops"), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def run_reference_arm(args):
+    """CPU restatement of the reference's algorithm on the host cores: each
+    step is one sample (16k-24k voxels) of the workload through the whole
+    backbone; Mvoxels/s over K such steps."""
+    from oracle.backbone import run_backbone
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    net = init_backbone(build_backbone())
+    params = oracle_params(net)
+    scenes = make_scenes(0, n_scenes=max(1, min(args.steps + args.warmup, 4)), batch=1)
+    times, voxels = [], []
+    for i in range(args.warmup + args.steps):
+        idx, feats = scenes[i % len(scenes)]
+        t0 = time.perf_counter()
+        run_backbone(LAYERS, params, idx.numpy(), feats.float(), GRID, 1, acc_dtype=torch.float32)
+        dt = time.perf_counter() - t0
+        if i >= args.warmup:
+            times.append(dt)
+            voxels.append(idx.shape[0])
+    value = sum(voxels) / sum(times) / 1e6
+    line = {
+        "impl": "reference", "metric": "voxelnet_backbone_fwd_mvoxels_per_s", "value": value, "unit": "Mvoxels/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * sum(times) / len(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "BASELINE configs[2]: VoxelNet-style backbone, one sample per step (bounded sample)",
+                   "grid": GRID, "voxels_per_sample": list(N_RANGE)},
+        "cpu_baseline": {"value": value, "unit": "Mvoxels/s", "cores": cores, "kind": "port",
+                         "sample": f"{args.steps} steps of one sample each ({int(np.mean(voxels))} voxels avg), "
+                                   "numpy rulebook + torch CPU fp32 gather-matmul"},
+        "e2e": {"value": value, "unit": "Mvoxels/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-baseline-seconds", type=float, default=20.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        args.steps = min(args.steps, 8)
+        args.warmup = min(args.warmup, 1)
+        run_reference_arm(args)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    args.warmup = max(args.warmup, 3)
+
+    from spconv_triton_b200 import _lib
+    import spconv_triton_b200.pytorch as sp
+
+    lib = _lib.load()
+    net = init_backbone(build_backbone()).half().eval().to(dev)
+    scenes_host = [(i.pin_memory(), f.pin_memory()) for i, f in make_scenes(rank)]
+    scenes_dev = [(i.to(dev), f.to(dev)) for i, f in scenes_host]
+    voxels_per_scene = [int(i.shape[0]) for i, _ in scenes_host]
+    prof = GemmProfiler()
+    prof.install()
+
+    def forward(idx, feats):
+        with torch.no_grad():
+            return net(sp.SparseConvTensor(feats, idx, GRID, BATCH))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    # ---- device-resident arm: inputs already in HBM -------------------------------------
+    for w in range(args.warmup):
+        forward(*scenes_dev[w % N_SCENES])
+    barrier()
+    launches0 = lib.spc_launch_count()
+    prof.enabled = True
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        for s in range(args.steps):
+            out = forward(*scenes_dev[s % N_SCENES])
+        e1.record()
+        barrier()
+    prof.enabled = False
+    launches = lib.spc_launch_count() - launches0
+    dev_ms = max_over_ranks(e0.elapsed_time(e1))
+    voxels = sum(voxels_per_scene[s % N_SCENES] for s in range(args.steps))
+    total_voxels = sum_over_ranks(voxels)
+    value = total_voxels / (dev_ms * 1e-3) / 1e6
+    gemm = prof.summarize()
+
+    # ---- end-to-end arm: pinned host buffers in, checksum out ----------------------------
+    h2d = int(np.mean([i.numel() * 4 + f.numel() * 2 for i, f in scenes_host]))
+    host_result = torch.empty(64, dtype=torch.float32).pin_memory()
+
+    def e2e_step(s):
+        idx_h, feats_h = scenes_host[s % N_SCENES]
+        idx = idx_h.to(dev, non_blocking=True)
+        feats = feats_h.to(dev, non_blocking=True)
+        o = forward(idx, feats)
+        host_result.copy_(o.features.float().sum(0), non_blocking=True)  # per-channel checksum of the output
+        torch.cuda.current_stream().synchronize()  # the caller consumes the result on the host
+
+    for w in range(args.warmup):
+        e2e_step(w)
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for s in range(args.steps):
+        e2e_step(s)
+    e3.record()
+    barrier()
+    e2e_ms = max_over_ranks(e2.elapsed_time(e3))
+    e2e_value = total_voxels / (e2e_ms * 1e-3) / 1e6
+
+    # ---- footprint: shows the per-step working set exceeds L2 ------------------------------
+    idict = out.indice_dict
+    table_bytes = sum(d.pair_fwd.numel() * 4 + (d.pair_bwd.numel() * 4 if d.pair_bwd is not None else 0)
+                      for d in idict.values())
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    achieved_gbs = gemm["bytes"] / (gemm["ms"] * 1e-3) / 1e9 if gemm["ms"] else 0.0
+    achieved_tflops = gemm["flops"] / (gemm["ms"] * 1e-3) / 1e12 if gemm["ms"] else 0.0
+
+    cpu_baseline = None
+    if world == 1:
+        cpu_baseline = cpu_baseline_sample(net, args.cpu_baseline_seconds)
+
+    line = {
+        "metric": "voxelnet_backbone_fwd_mvoxels_per_s", "value": value, "unit": "Mvoxels/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {
+            "workload": "BASELINE configs[2]: VoxelNet-style sparse middle encoder, fp16 inference, "
+                        "grid [41,1600,1408], batch 8 per GPU, 16k-24k voxels/sample, rulebooks rebuilt every step",
+            "voxels_per_step": int(np.mean(voxels_per_scene)), "scenes": N_SCENES,
+            "l2": f"inputs larger than L2: rulebook tables of one step hold {table_bytes / 1e6:.0f} MB "
+                  "and scenes rotate every step",
+            "parallelism": f"replicas x{world} (sharded by sample, no collective)",
+        },
+        "e2e": {"value": e2e_value, "unit": "Mvoxels/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": host_result.numel() * 4, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks.summary(),
+        "roofline": {
+            "kernel": "gather-GEMM forward (all launches of the timed region, aggregated)",
+            "bound": "hbm", "achieved": achieved_gbs, "peak": hbm_peak, "unit": "GB/s",
+            "frac": achieved_gbs / hbm_peak if hbm_peak else None, "traffic": None, "peak_kind": peak_kind,
+            "launches": gemm["launches"], "avg_launch_ms": gemm["avg_ms"],
+            "share_of_step": gemm["ms"] / dev_ms if dev_ms else None,
+            "tflops": achieved_tflops, "tensor_frac": achieved_tflops / tensor_peak if tensor_peak else None,
+        },
+        "cpu_baseline": cpu_baseline,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline_sample(net, budget_s):
+    """The oracle port on the host cores over single samples of the workload,
+    repeated until about ``budget_s`` seconds of CPU work are spent."""
+    from oracle.backbone import run_backbone
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    params = oracle_params(net)
+    scenes = make_scenes(0, n_scenes=2, batch=1)
+    spent, voxels, runs = 0.0, 0, 0
+    while spent < budget_s and runs < 8:
+        idx, feats = scenes[runs % len(scenes)]
+        t0 = time.perf_counter()
+        run_backbone(LAYERS, params, idx.numpy(), feats.float(), GRID, 1, acc_dtype=torch.float32)
+        spent += time.perf_counter() - t0
+        voxels += idx.shape[0]
+        runs += 1
+    return {"value": voxels / spent / 1e6, "unit": "Mvoxels/s", "cores": cores, "kind": "port",
+            "sample": f"{runs} single-sample forwards ({voxels} voxels, {spent:.1f} s) of the same backbone, "
+                      "numpy rulebook + torch CPU fp32 gather-matmul"}
+
+
+if __name__ == "__main__":
+    main()

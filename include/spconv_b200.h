@@ -76,6 +76,10 @@ typedef struct {
 
 int spc_version(void);
 const char* spc_last_error(void);
+/* Number of kernels of this library launched by the process so far (library
+ * sorts are not counted).  No counterpart in the reference; used by benchmarks
+ * to report how many hand-written kernels a timed region ran. */
+long long spc_launch_count(void);
 
 /* ---- output-shape formulas --------------------------------------------- */
 

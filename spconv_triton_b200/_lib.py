@@ -61,6 +61,7 @@ _P = c_void_p
 _PROTOTYPES = {
     "spc_version": (c_int, []),
     "spc_last_error": (c_char_p, []),
+    "spc_launch_count": (ctypes.c_longlong, []),
     "spc_conv_output_size": (c_int, [c_int, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32),
                                      POINTER(c_int32), POINTER(c_int32), POINTER(c_int32)]),
     "spc_deconv_output_size": (c_int, [c_int, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32),

@@ -1,4 +1,6 @@
 // Housekeeping entry points of the C ABI: version, error text, shape formulas.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace spc {
@@ -6,6 +8,8 @@ char* error_buffer() {
   static thread_local char buf[512] = {0};
   return buf;
 }
+static std::atomic<long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 }  // namespace spc
 
 using namespace spc;
@@ -13,6 +17,8 @@ using namespace spc;
 extern "C" int spc_version(void) { return 100; }
 
 extern "C" const char* spc_last_error(void) { return error_buffer(); }
+
+extern "C" long long spc_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int spc_conv_output_size(int ndim, const int32_t* in_shape, const int32_t* ksize,
                                     const int32_t* stride, const int32_t* padding, const int32_t* dilation,

@@ -15,6 +15,8 @@ namespace spc {
 
 // Thread-local text of the last failure, returned by spc_last_error().
 char* error_buffer();
+// Process-wide count of kernels this library has launched (spc_launch_count()).
+void note_launch();
 
 inline int fail(int status, const char* fmt, ...) {
   va_list ap;
@@ -38,6 +40,7 @@ inline int fail(int status, const char* fmt, ...) {
     if (e__ != cudaSuccess)                                                                \
       return ::spc::fail(SPC_ERR_CUDA, "kernel launch failed: %s (%s:%d)",                 \
                          cudaGetErrorString(e__), __FILE__, __LINE__);                     \
+    ::spc::note_launch();                                                                  \
   } while (0)
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }

@@ -1,0 +1,64 @@
+"""Seeded synthetic voxel scenes with the shapes and distributions of the
+benchmark configurations (stand-ins for LiDAR / indoor-scan data sets; no data
+set is read).  numpy only; used by bench.py and by the tests."""
+
+from __future__ import annotations
+
+import numpy as np
+
+
+def _unique_rows(coords, shape):
+    lin = np.ravel_multi_index(tuple(coords.T), shape)
+    _, first = np.unique(lin, return_index=True)
+    return coords[np.sort(first)]
+
+
+def lidar_like_sample(rng, n_target, grid=(41, 1600, 1408), n_clusters=200, sigma=8.0, ground_frac=0.7):
+    """(z, y, x) int32 [n_target, 3], unique: ``ground_frac`` of the voxels on a
+    noisy ground plane z = clamp(round(2 + N(0,1)), 0, 4) with (y, x) uniform,
+    the rest in ``n_clusters`` isotropic Gaussian clusters (sigma in voxels)
+    around centres drawn uniformly in the grid, clamped to the grid."""
+    grid = np.asarray(grid)
+    out = np.zeros((0, 3), dtype=np.int64)
+    centres = np.stack([rng.integers(0, g, n_clusters) for g in grid], 1)
+    while out.shape[0] < n_target:
+        need = n_target - out.shape[0]
+        m = int(need * 1.3) + 64
+        n_g = int(m * ground_frac)
+        ground = np.stack([
+            np.clip(np.rint(2 + rng.standard_normal(n_g)), 0, 4),
+            rng.integers(0, grid[1], n_g),
+            rng.integers(0, grid[2], n_g),
+        ], 1).astype(np.int64)
+        n_c = m - n_g
+        which = rng.integers(0, n_clusters, n_c)
+        cl = np.rint(centres[which] + rng.standard_normal((n_c, 3)) * sigma).astype(np.int64)
+        cl = np.clip(cl, 0, grid - 1)
+        new = np.concatenate([ground, cl], 0)
+        new = new[rng.permutation(new.shape[0])]
+        out = _unique_rows(np.concatenate([out, new], 0), tuple(grid))
+    return out[:n_target].astype(np.int32)
+
+
+def lidar_like_batch(seed, batch, n_range, grid=(41, 1600, 1408), **kw):
+    """int32 indices [N, 4] (batch, z, y, x), rows grouped by sample; the
+    per-sample voxel count is an integer drawn uniformly from ``n_range``."""
+    rng = np.random.default_rng(seed)
+    rows = []
+    for b in range(batch):
+        n = int(rng.integers(n_range[0], n_range[1] + 1))
+        c = lidar_like_sample(rng, n, grid, **kw)
+        rows.append(np.concatenate([np.full((n, 1), b, np.int32), c], 1))
+    return np.concatenate(rows, 0)
+
+
+def uniform_batch(seed, batch, n_per_sample, grid):
+    """Unique coordinates drawn uniformly without replacement."""
+    rng = np.random.default_rng(seed)
+    rows = []
+    vol = int(np.prod(grid))
+    for b in range(batch):
+        lin = rng.choice(vol, size=n_per_sample, replace=False)
+        c = np.stack(np.unravel_index(lin, grid), 1).astype(np.int32)
+        rows.append(np.concatenate([np.full((n_per_sample, 1), b, np.int32), c], 1))
+    return np.concatenate(rows, 0)
