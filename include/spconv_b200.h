@@ -80,6 +80,11 @@ const char* spc_last_error(void);
  * sorts are not counted).  No counterpart in the reference; used by benchmarks
  * to report how many hand-written kernels a timed region ran. */
 long long spc_launch_count(void);
+/* Synchronises `stream` and reports whether any kernel of this library gave up
+ * on a bounded device-side wait since the last call (SPC_ERR_DEVICE_WAIT_EXPIRED);
+ * the flag is cleared.  No counterpart in the reference (its kernels have no
+ * device-side waits). */
+int spc_check_device_status(void* stream);
 
 /* ---- output-shape formulas --------------------------------------------- */
 

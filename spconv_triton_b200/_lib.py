@@ -62,6 +62,7 @@ _PROTOTYPES = {
     "spc_version": (c_int, []),
     "spc_last_error": (c_char_p, []),
     "spc_launch_count": (ctypes.c_longlong, []),
+    "spc_check_device_status": (c_int, [_P]),
     "spc_conv_output_size": (c_int, [c_int, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32),
                                      POINTER(c_int32), POINTER(c_int32), POINTER(c_int32)]),
     "spc_deconv_output_size": (c_int, [c_int, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32),

@@ -7,13 +7,12 @@ using namespace spc;
 
 namespace {
 
-bool is_16bit(int dtype) { return dtype == SPC_F16 || dtype == SPC_BF16; }
-
 // The tensor-core kernels take 16-bit inputs always and fp32 inputs only when
 // the caller allows TF32; IEEE fp32 stays on the CUDA cores.
-bool want_tc(int path, int n_dim, int r_dim, int kv, int dtype, int out_dtype, int precision, int* status) {
+bool want_tc(int path, int n_dim, int r_dim, int kv, int dtype, int out_dtype, int precision, bool transposed,
+             int* status) {
   *status = SPC_OK;
-  const bool ok = gather_gemm_tc_supported(n_dim, r_dim, kv, dtype, out_dtype, precision);
+  const bool ok = gather_gemm_tc_supported(n_dim, r_dim, kv, dtype, out_dtype, precision, transposed);
   if (path == SPC_GEMM_SIMT) return false;
   if (path == SPC_GEMM_TCGEN05) {
     if (!ok) *status = fail(SPC_ERR_UNSUPPORTED, "tcgen05 path does not take this shape/dtype "
@@ -34,7 +33,7 @@ extern "C" int spc_conv_forward(const void* features, const void* weight, const 
   if (n_out == 0) return SPC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int status;
-  if (want_tc(path, c_out, c_in, kv, dtype, out_dtype, precision, &status))
+  if (want_tc(path, c_out, c_in, kv, dtype, out_dtype, precision, false, &status))
     return gather_gemm_tc(features, weight, bias, pair_fwd, mask_argsort, out, n_out, c_out, c_in, kv,
                           /*transposed_weight=*/false, dtype, out_dtype, precision, st);
   if (status != SPC_OK) return status;
@@ -53,7 +52,7 @@ extern "C" int spc_conv_backward_input(const void* grad_out, const void* weight,
   if (n_in == 0) return SPC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int status;
-  if (want_tc(path, c_in, c_out, kv, dtype, dtype, precision, &status))
+  if (want_tc(path, c_in, c_out, kv, dtype, dtype, precision, true, &status))
     return gather_gemm_tc(grad_out, weight, nullptr, pair_bwd, mask_argsort, din, n_in, c_in, c_out, kv,
                           /*transposed_weight=*/true, dtype, dtype, precision, st);
   if (status != SPC_OK) return status;

@@ -27,7 +27,8 @@ int wgrad_simt(const void* feats, const void* gout, const int32_t* pair_fwd, voi
 
 // tcgen05 kernels (gemm_tc.cu).  `transposed_weight` selects the input-gradient
 // view of the KRSC weight.  Return SPC_ERR_UNSUPPORTED for shapes they do not take.
-bool gather_gemm_tc_supported(int n_dim, int r_dim, int kv, int dtype, int out_dtype, int precision);
+bool gather_gemm_tc_supported(int n_dim, int r_dim, int kv, int dtype, int out_dtype, int precision,
+                              bool transposed_weight);
 int gather_gemm_tc(const void* src, const void* w, const void* bias, const int32_t* pairs,
                    const int32_t* order, void* out, long long m_rows, int n_dim, int r_dim, int kv,
                    bool transposed_weight, int dtype, int out_dtype, int precision, cudaStream_t st);

@@ -16,6 +16,14 @@ from spconv_triton_b200 import _lib, constants
 GEMM_PATH = _lib.SPC_GEMM_AUTO
 
 
+def check_device_status(device=None):
+    """Synchronise the current stream and raise if a kernel recorded that one of
+    its bounded device-side waits expired."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().spc_check_device_status(_lib.current_stream(dev)))
+
+
 def _precision(t: torch.Tensor) -> int:
     # TF32 only for fp32 inputs and only while the live flag is set (gemm.py:460-463)
     if t.dtype == torch.float32 and bool(constants.SPCONV_ALLOW_TF32):

@@ -35,6 +35,7 @@ def gemm_path(request):
     g.GEMM_PATH = {"simt": _lib.SPC_GEMM_SIMT, "auto": _lib.SPC_GEMM_AUTO}[request.param]
     yield request.param
     g.GEMM_PATH = old
+    g.check_device_status()  # no tcgen05 kernel may have given up on a wait
 
 
 @pytest.mark.parametrize("name", GEMM_CASES)
