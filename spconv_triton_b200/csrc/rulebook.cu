@@ -284,8 +284,11 @@ insert_inputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ 
 }
 
 // One thread per input row walks the kv offsets and inserts each candidate
-// output coordinate into the output table; first-time inserts are appended to
-// `uniq` through a warp-aggregated counter.
+// output coordinate into the output table.  Offsets are handled in groups of
+// 32: a thread remembers in a bitmask which of its candidates were first-time
+// inserts, the warp reserves room for all of them in `uniq` with ONE atomicAdd
+// per group (a per-insert counter serialises on a single address), and a
+// second walk over the group writes the keys.
 template <int ND, bool K64>
 __global__ void __launch_bounds__(kThreads)
 enumerate_outputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n,
@@ -296,26 +299,43 @@ enumerate_outputs_kernel(const __grid_constant__ Geo g, const int32_t* __restric
   const bool live = j < n;
   int c[ND + 1];
   if (live) load_coord<ND>(idx, j, c);
-  Odometer<ND> od;
-  od.reset();
   const unsigned lane = threadIdx.x & 31u;
-  for (int k = 0; k < g.kv; ++k) {
-    long long key = live ? out_key_from_input<ND>(g, c, od.pos) : -1;
-    int fresh = 0;
-    if (key >= 0) {
-      const int r = tout.insert_unique(static_cast<key_t>(key));
-      if (r < 0) atomicExch(&counters[kStatus], SPC_ERR_HASH_TABLE_FULL);
-      fresh = r > 0;
+  for (int k0 = 0; k0 < g.kv; k0 += 32) {
+    const int gcount = min(32, g.kv - k0);
+    Odometer<ND> od;
+    od.set(g, k0);
+    uint32_t fresh = 0;
+    if (live) {
+      for (int kk = 0; kk < gcount; ++kk) {
+        const long long key = out_key_from_input<ND>(g, c, od.pos);
+        if (key >= 0) {
+          const int r = tout.insert_unique(static_cast<key_t>(key));
+          if (r < 0) atomicExch(&counters[kStatus], SPC_ERR_HASH_TABLE_FULL);
+          fresh |= static_cast<uint32_t>(r > 0) << kk;
+        }
+        od.next(g);
+      }
     }
-    const unsigned ballot = __ballot_sync(0xffffffffu, fresh);
-    if (ballot) {
-      int base = 0;
-      const int leader = __ffs(ballot) - 1;
-      if (lane == static_cast<unsigned>(leader)) base = atomicAdd(&counters[kUniqueCount], __popc(ballot));
-      base = __shfl_sync(0xffffffffu, base, leader);
-      if (fresh) uniq[base + __popc(ballot & ((1u << lane) - 1u))] = static_cast<key_t>(key);
+    // warp-inclusive prefix of the per-thread counts
+    const int mine = __popc(fresh);
+    int incl = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= static_cast<unsigned>(off)) incl += t;
     }
-    od.next(g);
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
+    if (total == 0) continue;
+    int base = 0;
+    if (lane == 31) base = atomicAdd(&counters[kUniqueCount], total);
+    base = __shfl_sync(0xffffffffu, base, 31) + incl - mine;
+    if (fresh) {
+      od.set(g, k0);
+      for (int kk = 0; kk < gcount; ++kk) {
+        if ((fresh >> kk) & 1u) uniq[base++] = static_cast<key_t>(out_key_from_input<ND>(g, c, od.pos));
+        od.next(g);
+      }
+    }
   }
 }
 
