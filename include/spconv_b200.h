@@ -49,10 +49,18 @@ typedef enum { SPC_F16 = 0, SPC_BF16 = 1, SPC_F32 = 2, SPC_F64 = 3 } spc_dtype;
  * exactly and accumulate in fp32. */
 typedef enum { SPC_PREC_IEEE = 0, SPC_PREC_TF32 = 1 } spc_precision;
 
-/* Which implementation a GEMM entry point may use.  AUTO picks the tcgen05
- * kernel whenever the shape allows it and the CUDA-core kernel otherwise;
- * the other two force one of them (SPC_ERR_UNSUPPORTED if impossible). */
-typedef enum { SPC_GEMM_AUTO = 0, SPC_GEMM_SIMT = 1, SPC_GEMM_TCGEN05 = 2 } spc_gemm_path;
+/* Which implementation a GEMM entry point may use.  AUTO picks a tcgen05
+ * kernel whenever the shape allows it (fed by TMA gather4 when the channel
+ * widths fit a swizzle span, by cp.async otherwise) and the CUDA-core kernel
+ * for the rest.  SIMT forces the CUDA-core kernels; TCGEN05 demands a
+ * tensor-core kernel (SPC_ERR_UNSUPPORTED if the shape does not fit);
+ * TCGEN05_CPASYNC behaves like AUTO but never uses the TMA-fed kernel. */
+typedef enum {
+  SPC_GEMM_AUTO = 0,
+  SPC_GEMM_SIMT = 1,
+  SPC_GEMM_TCGEN05 = 2,
+  SPC_GEMM_TCGEN05_CPASYNC = 3
+} spc_gemm_path;
 
 /* Geometry of one rulebook.  in_shape/out_shape are the spatial shapes before
  * and after the layer (the caller computes out_shape with

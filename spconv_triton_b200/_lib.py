@@ -15,7 +15,7 @@ LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libspconv_b200.so"
 SPC_MAX_NDIM = 4
 SPC_F16, SPC_BF16, SPC_F32, SPC_F64 = 0, 1, 2, 3
 SPC_PREC_IEEE, SPC_PREC_TF32 = 0, 1
-SPC_GEMM_AUTO, SPC_GEMM_SIMT, SPC_GEMM_TCGEN05 = 0, 1, 2
+SPC_GEMM_AUTO, SPC_GEMM_SIMT, SPC_GEMM_TCGEN05, SPC_GEMM_TCGEN05_CPASYNC = 0, 1, 2, 3
 
 _I4 = c_int32 * SPC_MAX_NDIM
 

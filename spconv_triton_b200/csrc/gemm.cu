@@ -33,9 +33,14 @@ extern "C" int spc_conv_forward(const void* features, const void* weight, const 
   if (n_out == 0) return SPC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int status;
-  if (want_tc(path, c_out, c_in, kv, dtype, out_dtype, precision, false, &status))
+  if (want_tc(path, c_out, c_in, kv, dtype, out_dtype, precision, false, &status)) {
+    if (path != SPC_GEMM_TCGEN05_CPASYNC &&
+        gather_gemm_tma_supported(c_out, c_in, kv, dtype, out_dtype, precision, false))
+      return gather_gemm_tma(features, weight, bias, pair_fwd, mask_argsort, out, n_in, n_out, c_out, c_in, kv,
+                             /*transposed_weight=*/false, dtype, out_dtype, precision, st);
     return gather_gemm_tc(features, weight, bias, pair_fwd, mask_argsort, out, n_out, c_out, c_in, kv,
                           /*transposed_weight=*/false, dtype, out_dtype, precision, st);
+  }
   if (status != SPC_OK) return status;
   // weight[n, k, c]: reduction index c has stride 1, output channel n stride kv*c_in.
   return gather_gemm_simt(features, weight, bias, pair_fwd, mask_argsort, out, n_out, c_out, c_in, kv,
@@ -52,9 +57,13 @@ extern "C" int spc_conv_backward_input(const void* grad_out, const void* weight,
   if (n_in == 0) return SPC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int status;
-  if (want_tc(path, c_in, c_out, kv, dtype, dtype, precision, true, &status))
+  if (want_tc(path, c_in, c_out, kv, dtype, dtype, precision, true, &status)) {
+    if (path != SPC_GEMM_TCGEN05_CPASYNC && gather_gemm_tma_supported(c_in, c_out, kv, dtype, dtype, precision, true))
+      return gather_gemm_tma(grad_out, weight, nullptr, pair_bwd, mask_argsort, din, n_out, n_in, c_in, c_out, kv,
+                             /*transposed_weight=*/true, dtype, dtype, precision, st);
     return gather_gemm_tc(grad_out, weight, nullptr, pair_bwd, mask_argsort, din, n_in, c_in, c_out, kv,
                           /*transposed_weight=*/true, dtype, dtype, precision, st);
+  }
   if (status != SPC_OK) return status;
   // output channel is c (stride 1), reduction index is n (stride kv*c_in).
   return gather_gemm_simt(grad_out, weight, nullptr, pair_bwd, mask_argsort, din, n_in, c_in, c_out, kv,

@@ -13,7 +13,9 @@
 //              tile, then for every active (offset, reduction chunk) gather
 //              the 128 feature rows and the weight slab into a 128-byte-
 //              swizzled shared-memory stage with 16-byte cp.async (zero fill
-//              for absent rows); afterwards they are the epilogue warps that
+//              for absent rows, completion delivered to the stage's mbarrier by
+//              cp.async.mbarrier.arrive.noinc, so nobody waits for a copy);
+//              afterwards they are the epilogue warps that
 //              read TMEM with tcgen05.ld, add the bias and store the rows
 //   warp 4     one elected lane issues tcgen05.mma (kind::f16 / kind::tf32,
 //              fp32 accumulate) for each filled stage and releases the stage
@@ -33,6 +35,7 @@
 
 #include "common.cuh"
 #include "gemm_internal.cuh"
+#include "tc_common.cuh"
 
 namespace spc {
 
@@ -40,116 +43,7 @@ __device__ int g_device_status = 0;
 
 namespace {
 
-constexpr int kTileM = 128;
-constexpr int kRowBytes = 128;
-constexpr int kAStageBytes = kTileM * kRowBytes;  // 16 KB
-constexpr int kProducers = 128;
-constexpr int kThreadsTc = 160;
-constexpr int kGroup = 32;  // kernel offsets voted on together
-constexpr int kMaxStages = 8;
-constexpr uint32_t kSpinLimit = 1u << 20;
-
-// ---- PTX wrappers --------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait; false means the limit was reached.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_dyn(int pending) {
-  switch (pending) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-  }
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void named_bar_sync(int id, int count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-template <bool TF32>
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                       uint32_t accumulate) {
-  if (TF32) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-  }
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor: start address, leading / stride byte
-// offsets (all >> 4), descriptor version 1, 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
-  d |= 1ull << 46;
-  d |= 2ull << 61;
-  return d;
-}
-
-template <typename T> struct TcType;
-template <> struct TcType<__half> { static constexpr uint32_t fmt = 0; static constexpr bool tf32 = false; };
-template <> struct TcType<__nv_bfloat16> { static constexpr uint32_t fmt = 1; static constexpr bool tf32 = false; };
-template <> struct TcType<float> { static constexpr uint32_t fmt = 2; static constexpr bool tf32 = true; };
+using namespace tc;
 
 struct TcParams {
   const void* src;
@@ -163,42 +57,6 @@ struct TcParams {
   int stages, b_stage_bytes, tmem_cols;
   int* status;
 };
-
-struct StageInfo {
-  int ksteps;
-  int last;
-};
-
-template <typename TO>
-__device__ __forceinline__ void store_row16(TO* dst, const float* v);
-template <>
-__device__ __forceinline__ void store_row16<float>(float* dst, const float* v) {
-#pragma unroll
-  for (int q = 0; q < 4; ++q)
-    reinterpret_cast<float4*>(dst)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-}
-template <>
-__device__ __forceinline__ void store_row16<__half>(__half* dst, const float* v) {
-  uint32_t packed[8];
-#pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    __half2 h = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
-    packed[q] = *reinterpret_cast<uint32_t*>(&h);
-  }
-  reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-  reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-}
-template <>
-__device__ __forceinline__ void store_row16<__nv_bfloat16>(__nv_bfloat16* dst, const float* v) {
-  uint32_t packed[8];
-#pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
-    packed[q] = *reinterpret_cast<uint32_t*>(&h);
-  }
-  reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-  reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-}
 
 template <typename T, typename TO, bool B_MN>
 __global__ void __launch_bounds__(kThreadsTc, 1)
@@ -232,7 +90,7 @@ gather_gemm_tc_kernel(const __grid_constant__ TcParams p) {
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(bar_full + 8 * s, kProducers);
+      mbar_init(bar_full + 8 * s, kProducers + 1);  // 128 copy completions + the header writer
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_accum, 1);
@@ -260,19 +118,7 @@ gather_gemm_tc_kernel(const __grid_constant__ TcParams p) {
     const uint8_t* w_b = static_cast<const uint8_t*>(p.w);
     int stage = 0;
     uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1
-    int issued = 0, signalled = 0;   // stages with copies issued / handed to the MMA warp
-    int ring[4] = {0, 0, 0, 0};      // stage index of the last issued groups (issue order)
-    const int lag = p.stages >= 4 ? 3 : p.stages - 1;  // copy groups kept in flight
     bool ok = true;
-
-    auto hand_over = [&](int upto) {
-      // stages [signalled, upto) have landed for this thread: publish them
-      while (signalled < upto) {
-        fence_proxy_async();
-        mbar_arrive(bar_full + 8 * ring[signalled & 3]);
-        ++signalled;
-      }
-    };
 
     // A thread whose wait expired keeps walking the loops (so that every named
     // barrier is still reached by all 128 producers) but issues nothing more.
@@ -334,16 +180,13 @@ gather_gemm_tc_kernel(const __grid_constant__ TcParams p) {
               }
             }
           }
-          cp_async_commit();
+          // hand-over without waiting: each thread's arrival is delivered by the
+          // copy unit when its copies have landed; thread 0 adds the stage header
+          cp_async_arrive_noinc(bar_full + 8 * stage);
           if (tid == 0) {
             info[stage].ksteps = r_len / UMMA_K;
             info[stage].last = 0;
-          }
-          ring[issued & 3] = stage;
-          ++issued;
-          if (issued - signalled > lag) {
-            cp_async_wait_dyn(lag);
-            hand_over(issued - lag);
+            mbar_arrive(bar_full + 8 * stage);
           }
           if (++stage == p.stages) {
             stage = 0;
@@ -353,21 +196,21 @@ gather_gemm_tc_kernel(const __grid_constant__ TcParams p) {
       }
       named_bar_sync(1, kProducers);  // idx_s may be overwritten by the next group
     }
-    cp_async_wait_dyn(0);
-    hand_over(issued);
     // terminator stage: no data, tells the MMA warp the tile is complete
     if (ok && !mbar_wait(bar_empty + 8 * stage, empty_parity)) ok = false;
     if (ok) {
+      mbar_arrive(bar_full + 8 * stage);
       if (tid == 0) {
         info[stage].ksteps = 0;
         info[stage].last = 1;
+        mbar_arrive(bar_full + 8 * stage);
       }
-      mbar_arrive(bar_full + 8 * stage);
     } else {
       atomicExch(p.status, SPC_ERR_DEVICE_WAIT_EXPIRED);
       atomicExch(abort_flag, 1);
     }
 
+    cp_async_wait_all();
     // ---------------- epilogue ----------------
     bool have_acc = ok && mbar_wait(bar_accum, 0);
     if (ok && !have_acc) atomicExch(p.status, SPC_ERR_DEVICE_WAIT_EXPIRED);
@@ -415,6 +258,9 @@ gather_gemm_tc_kernel(const __grid_constant__ TcParams p) {
           ok = false;
           break;
         }
+        // the stage was written through the generic proxy (cp.async); order those
+        // writes before the tensor core's async-proxy reads
+        fence_proxy_async();
         tc_fence_after();
         const StageInfo si = info[stage];
         const uint32_t a_addr = smem_u32(stage_base + static_cast<size_t>(stage) * stage_bytes);
@@ -469,7 +315,7 @@ TcPlan make_plan(int n_dim, int r_dim, int elem, bool b_mn) {
   const int stage_bytes = kAStageBytes + pl.b_stage_bytes;
   const size_t fixed = 1024 /*alignment slack*/ + kGroup * kTileM * 4 + (2 * kMaxStages + 1) * 8 +
                        kMaxStages * sizeof(StageInfo) + 64;
-  const size_t budget = 100 * 1024;  // two CTAs per SM
+  const size_t budget = 110 * 1024;  // two CTAs per SM
   int stages = static_cast<int>((budget - fixed) / stage_bytes);
   stages = std::max(2, std::min(stages, 6));
   pl.stages = stages;
@@ -500,16 +346,20 @@ int launch_tc(const TcParams& base, cudaStream_t st) {
   return SPC_OK;
 }
 
-int* status_ptr() {
-  static int* ptr = nullptr;
-  if (ptr == nullptr) {
-    void* raw = nullptr;
-    if (cudaGetSymbolAddress(&raw, g_device_status) == cudaSuccess) ptr = static_cast<int*>(raw);
-  }
-  return ptr;
-}
-
 }  // namespace
+
+// Address of the current device's status word (every device that loads the
+// library has its own copy of the symbol).
+int* device_status_ptr() {
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (ptrs[dev] == nullptr) {
+    void* raw = nullptr;
+    if (cudaGetSymbolAddress(&raw, g_device_status) == cudaSuccess) ptrs[dev] = static_cast<int*>(raw);
+  }
+  return ptrs[dev];
+}
 
 bool gather_gemm_tc_supported(int n_dim, int r_dim, int kv, int dtype, int out_dtype, int precision,
                               bool transposed_weight) {
@@ -538,7 +388,7 @@ int gather_gemm_tc(const void* src, const void* w, const void* bias, const int32
   TcParams p{};
   p.src = src; p.w = w; p.bias = bias; p.pairs = pairs; p.order = order; p.out = out;
   p.m_rows = m_rows; p.n_dim = n_dim; p.r_dim = r_dim; p.kv = kv;
-  p.status = status_ptr();
+  p.status = device_status_ptr();
   if (p.status == nullptr) return fail(SPC_ERR_CUDA, "tcgen05 gather-GEMM: no device status word");
 #define SPC_TC(T, TO)                                                        \
   return transposed_weight ? launch_tc<T, TO, true>(p, st) : launch_tc<T, TO, false>(p, st)
@@ -552,7 +402,7 @@ int gather_gemm_tc(const void* src, const void* w, const void* bias, const int32
 }
 
 int read_device_status(cudaStream_t st, int* host_value) {
-  int* ptr = status_ptr();
+  int* ptr = device_status_ptr();
   *host_value = 0;
   if (ptr == nullptr) return SPC_OK;
   SPC_CUDA_OK(cudaMemcpyAsync(host_value, ptr, sizeof(int), cudaMemcpyDeviceToHost, st));

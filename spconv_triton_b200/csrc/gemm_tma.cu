@@ -1,0 +1,502 @@
+// Implicit gather-GEMM on tcgen05: cp.async-gathered feature rows, TMA-loaded
+// weight slabs.
+//
+// Same computation and tiling as gemm_tc.cu (128 output rows per CTA, fp32
+// accumulator in tensor memory).  What differs is how a shared-memory stage is
+// filled:
+//   * the 128 gathered feature rows are copied by EIGHT warps with 16-byte
+//     cp.async (8 lanes per row, zero fill for absent rows); each thread's
+//     completion is delivered to the stage's mbarrier by
+//     cp.async.mbarrier.arrive.noinc, so nobody waits for data;
+//   * the weight slab W[:, k, chunk] arrives through one tiled 3-D TMA load
+//     (one per column block for the input gradient) completing on the same
+//     mbarrier with complete_tx::bytes.
+// The row pitch in shared memory equals the swizzle span (32 / 64 / 128 bytes),
+// so channel counts of 16, 32 and multiples of 64 (16-bit) or 8, 16 and
+// multiples of 32 (TF32) are taken; other widths stay with gemm_tc.cu.
+//
+// Measured alternatives on B200 (64 -> 64 channels, 723k rows, 7.1M pairs):
+// feeding the rows with TMA tile::gather4 (4 rows per instruction) reached
+// 590 us issued by one warp and 400 us issued by four: the gather4 path
+// sustains roughly one 512-byte operation per ~30 cycles per SM, below what
+// the LSU path reaches, so the rows go through cp.async.
+//
+// Warp roles: warps 0-3 load the tile's table entries, vote on the active
+// kernel offsets (32 at a time) and later run the epilogue; warps 0-7 issue the
+// row copies; thread 0 issues the TMA weight loads; warp 8 issues tcgen05.mma.
+// All waits are bounded.
+#include <cuda.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "gemm_internal.cuh"
+#include "tc_common.cuh"
+
+namespace spc {
+namespace {
+
+using namespace tc;
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+#ifdef SPC_TRACE
+// Development aid (not compiled into the library): clock64 stamps of one CTA.
+__device__ long long g_trace[1024];
+#define SPC_STAMP(slot) do { if (blockIdx.x == gridDim.x / 2 && (slot) < 1024) g_trace[(slot)] = clock64(); } while (0)
+#else
+#define SPC_STAMP(slot) do { } while (0)
+#endif
+
+struct TmaParams {
+  const void* src;
+  const void* bias;
+  const int32_t* pairs;
+  const int32_t* order;
+  void* out;
+  long long m_rows;
+  int src_rows;  // rows of the gathered matrix; also the "absent row" index
+  int n_dim, r_dim, kv;
+  int stages, a_stage_bytes, b_stage_bytes, tmem_cols;
+  int a_row_bytes, b_row_bytes;  // swizzle span of the A rows / of the MN-major B rows
+  int* status;
+};
+
+__host__ __device__ inline uint32_t layout_type_for(int row_bytes) {
+  return row_bytes == 128 ? 2u : (row_bytes == 64 ? 4u : 6u);
+}
+
+constexpr int kIssueWarps = 8;                       // warps that issue the feature-row copies
+constexpr int kIssueThreads = kIssueWarps * 32;       // 256
+constexpr int kMmaWarp = kIssueWarps;                 // warp 8
+constexpr int kThreadsHybrid = kIssueThreads + 32;    // 288
+
+template <typename T, typename TO, bool B_MN>
+__global__ void __launch_bounds__(kThreadsHybrid, 1)
+gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constant__ CUtensorMap map_b) {
+  constexpr int ELEM = sizeof(T);
+  constexpr int UMMA_K = 32 / ELEM;
+  constexpr bool TF32 = TcType<T>::tf32;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int stage_bytes = p.a_stage_bytes + p.b_stage_bytes;
+  uint8_t* stage_base = smem;
+  int* idx_s = reinterpret_cast<int*>(smem + static_cast<size_t>(p.stages) * stage_bytes);  // [kGroup][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(idx_s + kGroup * kTileM);
+  StageInfo* info = reinterpret_cast<StageInfo*>(bars + 2 * kMaxStages + 1);
+  uint32_t* vote = reinterpret_cast<uint32_t*>(info + kMaxStages);
+  uint32_t* tmem_slot = vote + 4;
+  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  if (*reinterpret_cast<volatile int*>(p.status) != 0) return;
+  const long long m0 = static_cast<long long>(blockIdx.x) * kTileM;
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = smem_u32(bars + kMaxStages);
+  const uint32_t bar_accum = smem_u32(bars + 2 * kMaxStages);
+
+  if (tid == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(bar_full + 8 * s, kIssueThreads + 1);  // every copy thread + the weight-slab transaction
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_accum, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&map_b);
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(tmem_slot), static_cast<uint32_t>(p.tmem_cols));
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int epr = p.a_row_bytes / ELEM;  // reduction elements per stage
+  const int n_rchunks = (p.r_dim + epr - 1) / epr;
+  const int ksteps = epr / UMMA_K;
+  int real_stages = 0;
+
+  if (warp < kIssueWarps) {
+    const bool tile_warp = warp < 4;  // these also load the table entries and run the epilogue
+    long long my_row = -1;
+    if (tile_warp) {
+      const long long slot = m0 + tid;
+      if (slot < p.m_rows) my_row = p.order ? static_cast<long long>(__ldg(&p.order[slot])) : slot;
+    }
+    int stage = 0;
+    uint32_t empty_parity = 1;
+    bool ok = true;
+    const int b_cols = p.b_row_bytes / ELEM;  // MN-major: output channels per column block
+    const int ncb = B_MN ? (p.n_dim + b_cols - 1) / b_cols : 1;
+    const uint32_t b_bytes = B_MN ? static_cast<uint32_t>(ncb * epr * p.b_row_bytes)
+                                  : static_cast<uint32_t>(p.n_dim * p.a_row_bytes);
+    // this thread copies 16-byte piece `chunk` of rows row_lo, row_lo+32, row_lo+64, row_lo+96
+    const int chunk = tid & 7, row_lo = tid >> 3;
+    const bool copies = chunk < p.a_row_bytes / 16;
+    const uint32_t swz_mask = static_cast<uint32_t>(p.a_row_bytes / 16 - 1);  // 7, 3 or 1
+    uint32_t dst_off[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t lin = static_cast<uint32_t>((row_lo + 32 * i) * p.a_row_bytes + chunk * 16);
+      dst_off[i] = lin ^ (((lin >> 7) & swz_mask) << 4);
+    }
+    const uint8_t* src_chunk = static_cast<const uint8_t*>(p.src) + chunk * 16;
+    const uint32_t src_pitch = static_cast<uint32_t>(p.r_dim) * ELEM;
+
+    int trace_n = 0;
+    (void)trace_n;
+    if (tid == 0) SPC_STAMP(0);
+    for (int k0 = 0; k0 < p.kv; k0 += kGroup) {
+      const int gcount = min(kGroup, p.kv - k0);
+      if (tile_warp) {
+        // all table entries of the group are requested before any is used
+        int jj[kGroup];
+#pragma unroll
+        for (int kk = 0; kk < kGroup; ++kk) {
+          jj[kk] = -1;
+          if (kk < gcount && my_row >= 0)
+            jj[kk] = __ldg(&p.pairs[static_cast<long long>(k0 + kk) * p.m_rows + my_row]);
+        }
+        uint32_t mine = 0;
+#pragma unroll
+        for (int kk = 0; kk < kGroup; ++kk) {
+          mine |= static_cast<uint32_t>(jj[kk] >= 0) << kk;
+          if (kk < gcount) idx_s[kk * kTileM + tid] = jj[kk];
+        }
+        mine = __reduce_or_sync(0xffffffffu, mine);
+        if (lane == 0) vote[warp] = mine;
+      }
+      if (tid == 0) SPC_STAMP(1);
+      named_bar_sync(1, kIssueThreads);
+      const uint32_t active = vote[0] | vote[1] | vote[2] | vote[3];
+      real_stages += __popc(active) * n_rchunks;
+
+      for (uint32_t rest = active; rest != 0; rest &= rest - 1) {
+        const int kk = __ffs(rest) - 1;
+        const int k = k0 + kk;
+        int j[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) j[i] = idx_s[kk * kTileM + row_lo + 32 * i];
+        for (int rc = 0; rc < n_rchunks; ++rc) {
+          if (tid == 0) SPC_STAMP(16 + 2 * trace_n);
+          if (ok && !mbar_wait(bar_empty + 8 * stage, empty_parity)) ok = false;
+          if (ok) {
+            if (tid == 0) SPC_STAMP(17 + 2 * trace_n);
+            ++trace_n;
+            const int r0 = rc * epr;
+            const uint32_t a_dst = smem_u32(stage_base + static_cast<size_t>(stage) * stage_bytes);
+            const uint32_t full = bar_full + 8 * stage;
+            if (copies) {
+              const uint8_t* base = src_chunk + static_cast<long long>(r0) * ELEM;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const bool present = j[i] >= 0;
+                cp_async16(a_dst + dst_off[i],
+                           base + static_cast<unsigned long long>(present ? static_cast<uint32_t>(j[i]) : 0u) * src_pitch,
+                           present ? 16u : 0u);
+              }
+            }
+            // delivered to the barrier by the copy unit once this thread's copies have landed
+            cp_async_arrive_noinc(full);
+            if (tid == 0) {
+              info[stage].ksteps = ksteps;
+              info[stage].last = 0;
+              mbar_expect_tx(full, b_bytes);
+              const uint32_t b_dst = a_dst + p.a_stage_bytes;
+              if (!B_MN) {
+                // weight viewed as [c_out][kv][c_in]: rows n = 0..n_dim-1 of offset k, reduction chunk r0
+                tma_load_3d(b_dst, &map_b, r0, k, 0, full);
+              } else {
+                // weight viewed as [c_out = reduction][kv][c_in]: rows r0.., one load per column block
+                for (int cb = 0; cb < ncb; ++cb)
+                  tma_load_3d(b_dst + cb * epr * p.b_row_bytes, &map_b, cb * b_cols, k, r0, full);
+              }
+            }
+            if (++stage == p.stages) {
+              stage = 0;
+              empty_parity ^= 1;
+            }
+          }
+        }
+      }
+      named_bar_sync(1, kIssueThreads);  // idx_s may be overwritten by the next group
+    }
+    // terminator stage: no data, tells the MMA warp the tile is complete
+    if (ok && !mbar_wait(bar_empty + 8 * stage, empty_parity)) ok = false;
+    if (ok) {
+      mbar_arrive(bar_full + 8 * stage);
+      if (tid == 0) {
+        info[stage].ksteps = 0;
+        info[stage].last = 1;
+        mbar_arrive(bar_full + 8 * stage);
+      }
+    } else {
+      atomicExch(p.status, SPC_ERR_DEVICE_WAIT_EXPIRED);
+      atomicExch(abort_flag, 1);
+    }
+    cp_async_wait_all();
+
+    // ---------------- epilogue (warps 0-3) ----------------
+    if (tile_warp) {
+      if (tid == 0) SPC_STAMP(2);
+      bool have_acc = mbar_wait(bar_accum, 0);
+      if (tid == 0) SPC_STAMP(3);
+      if (!have_acc) atomicExch(p.status, SPC_ERR_DEVICE_WAIT_EXPIRED);
+      have_acc = __all_sync(0xffffffffu, have_acc);
+      tc_fence_after();
+      if (have_acc) {
+        TO* out_row = static_cast<TO*>(p.out) + (my_row >= 0 ? my_row : 0) * p.n_dim;
+        const T* bias = static_cast<const T*>(p.bias);
+        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+        for (int c0 = 0; c0 < p.n_dim; c0 += 16) {
+          float v[16];
+          if (real_stages > 0) {
+            uint32_t raw[16];
+            tmem_ld16(lane_addr + c0, raw);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 16; ++q) v[q] = __uint_as_float(raw[q]);
+          } else {
+#pragma unroll
+            for (int q = 0; q < 16; ++q) v[q] = 0.f;
+          }
+          if (my_row >= 0) {
+            if (bias != nullptr) {
+#pragma unroll
+              for (int q = 0; q < 16; ++q) v[q] += to_float(bias[c0 + q]);
+            }
+            store_row16<TO>(out_row + c0, v);
+          }
+        }
+      }
+      if (tid == 0) SPC_STAMP(4);
+      tc_fence_before();
+    }
+  } else {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (TcType<T>::fmt << 7) | (TcType<T>::fmt << 10) |
+                             ((B_MN ? 1u : 0u) << 16) | (static_cast<uint32_t>(p.n_dim >> 3) << 17) |
+                             (static_cast<uint32_t>(kTileM >> 4) << 24);
+      const uint32_t a_type = layout_type_for(p.a_row_bytes);
+      const uint32_t b_type = B_MN ? layout_type_for(p.b_row_bytes) : a_type;
+      int stage = 0;
+      uint32_t full_parity = 0;
+      uint32_t accumulate = 0;
+      bool ok = true;
+      int mma_n = 0;
+      (void)mma_n;
+      while (true) {
+        // a wait that expires here is either a real failure or the producers having aborted
+        if (!mbar_wait(bar_full + 8 * stage, full_parity)) {
+          ok = false;
+          break;
+        }
+        // the feature rows were written through the generic proxy (cp.async): order
+        // those writes before the tensor core's async-proxy reads
+        fence_proxy_async();
+        tc_fence_after();
+        SPC_STAMP(512 + mma_n);
+        ++mma_n;
+        const StageInfo si = info[stage];
+        const uint32_t a_addr = smem_u32(stage_base + static_cast<size_t>(stage) * stage_bytes);
+        const uint32_t b_addr = a_addr + p.a_stage_bytes;
+        const uint64_t a_desc = make_desc(a_addr, 16, 8 * p.a_row_bytes, a_type);
+        const uint64_t b_desc = B_MN ? make_desc(b_addr, epr * p.b_row_bytes, 8 * p.b_row_bytes, b_type)
+                                     : make_desc(b_addr, 16, 8 * p.a_row_bytes, a_type);
+        for (int ks = 0; ks < si.ksteps; ++ks) {
+          const uint64_t a_step = static_cast<uint64_t>(ks * 2);
+          const uint64_t b_step = static_cast<uint64_t>(B_MN ? ks * (UMMA_K * p.b_row_bytes / 16) : ks * 2);
+          tc_mma<TF32>(tmem_base, a_desc + a_step, b_desc + b_step, idesc, accumulate);
+          accumulate = 1;
+        }
+        if (si.last) {
+          tc_commit(bar_accum);
+          break;
+        }
+        tc_commit(bar_empty + 8 * stage);
+        if (++stage == p.stages) {
+          stage = 0;
+          full_parity ^= 1;
+        }
+      }
+      if (!ok) {
+        atomicExch(p.status, SPC_ERR_DEVICE_WAIT_EXPIRED);
+        // release the epilogue warps: nothing more will be accumulated
+        mbar_arrive(bar_accum);
+      }
+    }
+    __syncwarp();
+  }
+
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+  }
+}
+
+// ---- host side ------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* raw = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &raw, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(raw);
+  }
+  return fn;
+}
+
+CUtensorMapSwizzle swizzle_for(int row_bytes) {
+  return row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+CUtensorMapDataType tma_dtype(int dtype) {
+  return dtype == SPC_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                          : (dtype == SPC_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
+}
+
+// Swizzle span of rows holding `elems` contiguous elements: 32, 64 or 128 bytes
+// (the latter for any multiple of 128 bytes); 0 if the width does not fit.
+int row_span(int elems, int elem_size) {
+  const int bytes = elems * elem_size;
+  if (bytes == 32 || bytes == 64) return bytes;
+  if (bytes >= 128 && bytes % 128 == 0) return 128;
+  return 0;
+}
+
+template <typename T, typename TO, bool B_MN>
+int launch_tma(TmaParams p, const CUtensorMap& map_b, size_t smem_bytes, cudaStream_t st) {
+  static bool configured = false;
+  if (!configured) {
+    SPC_CUDA_OK(cudaFuncSetAttribute(gather_gemm_tma_kernel<T, TO, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     200 * 1024));
+    configured = true;
+  }
+  const unsigned grid = static_cast<unsigned>(ceil_div(p.m_rows, kTileM));
+  gather_gemm_tma_kernel<T, TO, B_MN><<<grid, kThreadsHybrid, smem_bytes, st>>>(p, map_b);
+  SPC_LAUNCH_OK();
+  return SPC_OK;
+}
+
+}  // namespace
+
+bool gather_gemm_tma_supported(int n_dim, int r_dim, int kv, int dtype, int out_dtype, int precision,
+                               bool transposed_weight) {
+  if (!gather_gemm_tc_supported(n_dim, r_dim, kv, dtype, out_dtype, precision, transposed_weight)) return false;
+  const int elem = (dtype == SPC_F32) ? 4 : 2;
+  if (row_span(r_dim, elem) == 0) return false;
+  if (transposed_weight && row_span(n_dim, elem) == 0) return false;
+  return encode_fn() != nullptr;
+}
+
+int gather_gemm_tma(const void* src, const void* w, const void* bias, const int32_t* pairs,
+                    const int32_t* order, void* out, long long src_rows, long long m_rows, int n_dim, int r_dim,
+                    int kv, bool transposed_weight, int dtype, int out_dtype, int precision, cudaStream_t st) {
+  if (!gather_gemm_tma_supported(n_dim, r_dim, kv, dtype, out_dtype, precision, transposed_weight))
+    return fail(SPC_ERR_UNSUPPORTED, "TMA gather-GEMM: unsupported shape");
+  if (src_rows <= 0 || src_rows >= (1ll << 31) - 1)
+    return fail(SPC_ERR_SIZE_LIMIT, "TMA gather-GEMM: %lld source rows", static_cast<long long>(src_rows));
+  if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15u)
+    return fail(SPC_ERR_UNSUPPORTED, "TMA gather-GEMM: operands must be 16-byte aligned");
+  const int elem = (dtype == SPC_F32) ? 4 : 2;
+  EncodeTiledFn encode = encode_fn();
+
+  TmaParams p{};
+  p.src = src; p.bias = bias; p.pairs = pairs; p.order = order; p.out = out;
+  p.m_rows = m_rows; p.src_rows = static_cast<int>(src_rows);
+  p.n_dim = n_dim; p.r_dim = r_dim; p.kv = kv;
+  p.a_row_bytes = row_span(r_dim, elem);
+  p.b_row_bytes = transposed_weight ? row_span(n_dim, elem) : p.a_row_bytes;
+  const int epr = p.a_row_bytes / elem;
+  p.a_stage_bytes = static_cast<int>(align_up(static_cast<size_t>(kTileM) * p.a_row_bytes, 1024));
+  if (transposed_weight) {
+    const int b_cols = p.b_row_bytes / elem;
+    const int ncb = (n_dim + b_cols - 1) / b_cols;
+    p.b_stage_bytes = ncb * epr * p.b_row_bytes;
+  } else {
+    p.b_stage_bytes = n_dim * p.a_row_bytes;
+  }
+  p.b_stage_bytes = static_cast<int>(align_up(p.b_stage_bytes, 1024));
+  const int stage_bytes = p.a_stage_bytes + p.b_stage_bytes;
+  const size_t fixed = 1024 + kGroup * kTileM * 4 + (2 * kMaxStages + 1) * 8 + kMaxStages * sizeof(StageInfo) + 64;
+  const size_t budget = 110 * 1024;  // two CTAs per SM
+  p.stages = std::max(2, std::min<int>(kMaxStages, static_cast<int>((budget - fixed) / stage_bytes)));
+  const size_t smem_bytes = fixed + static_cast<size_t>(p.stages) * stage_bytes;
+  int cols = 32;
+  while (cols < n_dim) cols <<= 1;
+  p.tmem_cols = cols;
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return fail(SPC_ERR_CUDA, "TMA gather-GEMM: no device status word");
+
+  CUtensorMap map_b;
+  // B: the KRSC weight [c_out][kv][c_in] as a 3-D tensor (c_in innermost)
+  {
+    const int c_in = transposed_weight ? n_dim : r_dim;
+    const int c_out = transposed_weight ? r_dim : n_dim;
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(c_in), static_cast<cuuint64_t>(kv),
+                                static_cast<cuuint64_t>(c_out)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(c_in) * elem, static_cast<cuuint64_t>(kv) * c_in * elem};
+    cuuint32_t box[3];
+    if (transposed_weight) {
+      box[0] = static_cast<cuuint32_t>(p.b_row_bytes / elem);  // output channels of one column block
+      box[1] = 1;
+      box[2] = static_cast<cuuint32_t>(epr);                   // reduction rows of one stage
+    } else {
+      box[0] = static_cast<cuuint32_t>(epr);
+      box[1] = 1;
+      box[2] = static_cast<cuuint32_t>(n_dim);
+    }
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = encode(&map_b, tma_dtype(dtype), 3, const_cast<void*>(w), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(p.b_row_bytes),
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SPC_ERR_CUDA, "cuTensorMapEncodeTiled(B) failed: %d", static_cast<int>(r));
+  }
+
+#define SPC_TMA(T, TO)                                                                                   \
+  return transposed_weight ? launch_tma<T, TO, true>(p, map_b, smem_bytes, st)                    \
+                           : launch_tma<T, TO, false>(p, map_b, smem_bytes, st)
+  if (dtype == SPC_F16 && out_dtype == SPC_F16) SPC_TMA(__half, __half);
+  if (dtype == SPC_F16 && out_dtype == SPC_F32) SPC_TMA(__half, float);
+  if (dtype == SPC_BF16 && out_dtype == SPC_BF16) SPC_TMA(__nv_bfloat16, __nv_bfloat16);
+  if (dtype == SPC_BF16 && out_dtype == SPC_F32) SPC_TMA(__nv_bfloat16, float);
+  if (dtype == SPC_F32 && out_dtype == SPC_F32) SPC_TMA(float, float);
+#undef SPC_TMA
+  return fail(SPC_ERR_UNSUPPORTED, "TMA gather-GEMM: dtype combination");
+}
+
+}  // namespace spc
+
+#ifdef SPC_TRACE
+extern "C" int spc_dev_read_trace(long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, spc::g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : 1;
+}
+#endif

@@ -26,13 +26,15 @@ def _gemm():
     return gemm
 
 
-@pytest.fixture(params=["simt", "auto"])
+@pytest.fixture(params=["simt", "cpasync", "auto"])
 def gemm_path(request):
     from spconv_triton_b200 import _lib
 
     g = _gemm()
     old = g.GEMM_PATH
-    g.GEMM_PATH = {"simt": _lib.SPC_GEMM_SIMT, "auto": _lib.SPC_GEMM_AUTO}[request.param]
+    # "cpasync": like auto, but the tcgen05 kernels are fed by cp.async, never by TMA
+    g.GEMM_PATH = {"simt": _lib.SPC_GEMM_SIMT, "auto": _lib.SPC_GEMM_AUTO,
+                   "cpasync": _lib.SPC_GEMM_TCGEN05_CPASYNC}[request.param]
     yield request.param
     g.GEMM_PATH = old
     g.check_device_status()  # no tcgen05 kernel may have given up on a wait

@@ -1,0 +1,109 @@
+"""Drop-in protocol of the layer classes, against the reference's frozen
+`golden_proto.pt` cases: seeded initialisation bit for bit, state_dict keys and
+shapes, extra_repr, pickling, checkpoint hooks, constructor signatures."""
+
+import inspect
+import pickle
+
+import pytest
+import torch
+
+from frozen_cases import frozen, frozen_ids
+
+import spconv_triton_b200.pytorch as sp
+
+
+def _cases(kind):
+    return [i for i in frozen_ids("golden_proto.pt") if frozen("golden_proto.pt", i)["kind"] == kind]
+
+
+@pytest.mark.parametrize("case_id", _cases("init"))
+def test_seeded_init_bitwise(case_id):
+    case = frozen("golden_proto.pt", case_id)
+    torch.manual_seed(case["seed"])
+    layer = getattr(sp, case["cls"])(**case["ctor"])
+    assert list(layer.weight.shape) == case["expect"]["weight_shape"]
+    assert torch.equal(layer.weight.detach(), case["expect"]["weight"])
+    if case["expect"]["bias"] is None:
+        assert layer.bias is None
+    else:
+        assert torch.equal(layer.bias.detach(), case["expect"]["bias"])
+
+
+@pytest.mark.parametrize("case_id", _cases("state_dict_keys"))
+def test_state_dict_keys(case_id):
+    case = frozen("golden_proto.pt", case_id)
+    sd = getattr(sp, case["cls"])(**case["ctor"]).state_dict()
+    assert sorted(sd.keys()) == case["expect"]["keys"]
+    for k, shape in case["expect"]["shapes"].items():
+        assert list(sd[k].shape) == shape
+
+
+@pytest.mark.parametrize("case_id", _cases("repr"))
+def test_extra_repr(case_id):
+    case = frozen("golden_proto.pt", case_id)
+    assert getattr(sp, case["cls"])(**case["ctor"]).extra_repr() == case["expect"]["extra_repr"]
+
+
+def test_pickle_roundtrip():
+    layer = sp.SubMConv3d(4, 8, 3)
+    assert torch.equal(layer.weight, pickle.loads(pickle.dumps(layer)).weight)
+    x = sp.SparseConvTensor(torch.randn(5, 3), torch.zeros(5, 4, dtype=torch.int32), [4, 4, 4], 1)
+    y = pickle.loads(pickle.dumps(x))
+    assert torch.equal(x.features, y.features) and y.spatial_shape == [4, 4, 4]
+
+
+def test_record_voxel_count_checkpoint_injection():
+    sd = sp.SparseConv3d(4, 8, 3).state_dict()
+    rvc = sp.SparseConv3d(4, 8, 3, record_voxel_count=True)
+    missing, unexpected = rvc.load_state_dict(sd, strict=True)
+    assert not missing and not unexpected
+    assert "max_num_voxels_during_training" in [n for n, _ in rvc.named_buffers()]
+    assert sp.SparseConv3d(4, 8, 3).get_max_num_voxels() is None
+
+
+CTOR = {
+    "conv": ["in_channels", "out_channels", "kernel_size", "stride", "padding", "dilation", "groups", "bias",
+             "indice_key", "algo", "fp32_accum", "record_voxel_count", "large_kernel_fast_algo", "name"],
+    "inverse": ["in_channels", "out_channels", "kernel_size", "indice_key", "bias", "algo", "fp32_accum",
+                "large_kernel_fast_algo", "name"],
+    "subm": ["in_channels", "out_channels", "kernel_size", "stride", "padding", "dilation", "groups", "bias",
+             "indice_key", "algo", "fp32_accum", "large_kernel_fast_algo", "name"],
+    "pool": ["kernel_size", "stride", "padding", "dilation", "indice_key", "algo", "record_voxel_count", "name"],
+}
+
+
+def test_constructor_signatures():
+    """Parameter names and order of the public layer classes (the reference pins
+    them in tests/data/golden_api.json)."""
+    def names(cls):
+        return [p for p in inspect.signature(cls.__init__).parameters if p != "self"]
+
+    for d in (1, 2, 3, 4):
+        assert names(getattr(sp, f"SparseConv{d}d")) == CTOR["conv"]
+        assert names(getattr(sp, f"SparseConvTranspose{d}d")) == CTOR["conv"]
+        assert names(getattr(sp, f"SparseInverseConv{d}d")) == CTOR["inverse"]
+        assert names(getattr(sp, f"SubMConv{d}d")) == CTOR["subm"]
+        assert names(getattr(sp, f"SparseMaxPool{d}d")) == CTOR["pool"]
+    for d in (1, 2, 3):
+        assert names(getattr(sp, f"SparseAvgPool{d}d")) == CTOR["pool"]
+
+
+def test_edge_behaviour_of_constructors_and_tensor():
+    from spconv_triton_b200.core import ConvAlgo
+
+    with pytest.raises(AssertionError):
+        sp.SparseConv3d(4, 8, 3, groups=2)
+    assert sp.SubMConv3d(4, 8, 5).algo == ConvAlgo.Native  # kv = 125 > 32
+    assert sp.SubMConv3d(4, 8, 5, large_kernel_fast_algo=True).algo == ConvAlgo.MaskImplicitGemm
+    assert sp.SparseConv3d(4, 8, 1).conv1x1 and not sp.SparseConv3d(4, 8, 1, stride=2).conv1x1
+    with pytest.raises(AssertionError):
+        sp.SparseAvgPool3d([4, 4, 4])  # kv = 64 > 32
+    assert sp.SparseMaxPool3d(2).stride == [2, 2, 2]  # stride=None -> kernel size
+    with pytest.raises(AssertionError, match="int32"):
+        sp.SparseConvTensor(torch.randn(2, 3), torch.zeros(2, 4, dtype=torch.int64), [4, 4, 4], 1)
+    x = sp.SparseConvTensor(torch.randn(2, 3), torch.zeros(2, 4, dtype=torch.int32), [4, 4, 4], 1)
+    with pytest.raises(ValueError):
+        x.features = torch.zeros(2, 3)
+    y = x.replace_feature(x.features * 2)
+    assert y.indice_dict is x.indice_dict and y.indices is x.indices
