@@ -193,6 +193,25 @@ int spc_conv_backward_weight(const void* features, const void* grad_out,
                              int c_out, int kv, int dtype, int precision, int path,
                              void* stream);
 
+/* Weight gradient for callers that cannot provide a workspace and must not
+ * allocate: same result as spc_conv_backward_weight, but the fp32 partial sums
+ * of the split reduction live in a 16 MiB array built into the library (held
+ * by every GPU that loads it, until the process exits).  It has no counterpart
+ * in the reference.
+ *   - shapes whose partial sums exceed spc_conv_backward_weight_noalloc_max_bytes()
+ *     are rejected with SPC_ERR_SIZE_LIMIT (compare with
+ *     spc_conv_backward_weight_workspace_bytes() for the same arguments);
+ *   - the first call on a device looks up the array's device address; make that
+ *     call before any stream capture on the device;
+ *   - all calls on a device share the array: calls that overlap on the GPU race,
+ *     so issue them on one stream or order them yourself;
+ *   - neither this call nor anything it launches allocates or frees memory. */
+size_t spc_conv_backward_weight_noalloc_max_bytes(void);
+int spc_conv_backward_weight_noalloc(const void* features, const void* grad_out,
+                                     const int32_t* pair_fwd, void* dweight, int64_t n_in,
+                                     int64_t n_out, int c_in, int c_out, int kv, int dtype,
+                                     void* stream);
+
 /* ---- sparse pooling ---------------------------------------------------- */
 
 /* replaces maxpool_forward, _impl/pool.py:260-288: accumulator starts at 0. */

@@ -80,6 +80,8 @@ _PROTOTYPES = {
     "spc_conv_backward_weight_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int]),
     "spc_conv_backward_weight": (c_int, [_P, _P, _P, _P, _P, c_size_t, c_int64, c_int64, c_int, c_int, c_int,
                                          c_int, c_int, c_int, _P]),
+    "spc_conv_backward_weight_noalloc_max_bytes": (c_size_t, []),
+    "spc_conv_backward_weight_noalloc": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, _P]),
     "spc_maxpool_forward": (c_int, [_P, _P, _P, c_int64, c_int, c_int, c_int, _P]),
     "spc_maxpool_backward": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, _P]),
     "spc_avgpool_forward": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int, c_int, _P]),

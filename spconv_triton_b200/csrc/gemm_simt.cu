@@ -295,3 +295,77 @@ int wgrad_simt(const void* feats, const void* gout, const int32_t* pair_fwd, voi
 }
 
 }  // namespace spc
+
+// ---------------------------------------------------------------------------
+// Weight gradient without any workspace from the caller.
+//
+// Some hosts can give this library nothing but the tensors of the operation
+// itself: a C/C++ inference or training runtime that embeds the library as a
+// plugin, plans every byte of device memory up front, forbids cudaMalloc from
+// plugin code and has no workspace argument in its operator interface.  For
+// them the fp32 partial sums of the split reduction live in the fixed array
+// below instead of a caller-provided buffer.
+//
+// The array is part of the library image: every GPU that loads the library
+// holds these 16 MiB until the process exits.  All calls on a device share it,
+// so two calls that overlap on the GPU (different streams, or graphs launched
+// concurrently) race on it; callers must serialise them.  Nothing in it has to
+// start at zero: the partial-sum kernel writes every element the reduction
+// kernel reads, so contents left by an earlier call are never observed.
+// ---------------------------------------------------------------------------
+namespace spc {
+namespace {
+
+constexpr size_t kNoAllocScratchFloats = size_t(4) << 20;  // 4 Mi floats = 16 MiB
+static __device__ __align__(256) float g_wgrad_scratch[kNoAllocScratchFloats];
+
+// In host code `g_wgrad_scratch` is only a handle for the symbol, not an
+// address a kernel could use; the device address is looked up once per device
+// (with that device current) and remembered.
+int wgrad_scratch_address(float** out) {
+  static float* per_device[64] = {nullptr};
+  int dev = 0;
+  SPC_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(SPC_ERR_SIZE_LIMIT, "device ordinal %d out of range", dev);
+  if (per_device[dev] == nullptr) {
+    void* raw = nullptr;
+    SPC_CUDA_OK(cudaGetSymbolAddress(&raw, g_wgrad_scratch));
+    per_device[dev] = static_cast<float*>(raw);
+  }
+  *out = per_device[dev];
+  return SPC_OK;
+}
+
+}  // namespace
+}  // namespace spc
+
+extern "C" size_t spc_conv_backward_weight_noalloc_max_bytes(void) {
+  return spc::kNoAllocScratchFloats * sizeof(float);
+}
+
+extern "C" int spc_conv_backward_weight_noalloc(const void* features, const void* grad_out,
+                                                const int32_t* pair_fwd, void* dweight, int64_t n_in,
+                                                int64_t n_out, int c_in, int c_out, int kv, int dtype,
+                                                void* stream) {
+  using namespace spc;
+  (void)n_in;
+  if (!features || !grad_out || !pair_fwd || !dweight || n_out < 0 || c_in <= 0 || c_out <= 0 || kv <= 0)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "conv_backward_weight_noalloc: bad arguments");
+  if (dtype != SPC_F16 && dtype != SPC_BF16 && dtype != SPC_F32)
+    return fail(SPC_ERR_UNSUPPORTED, "conv_backward_weight_noalloc: dtype %d not supported", dtype);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_out == 0) {
+    SPC_CUDA_OK(cudaMemsetAsync(dweight, 0, static_cast<size_t>(c_out) * kv * c_in * dtype_size(dtype), st));
+    return SPC_OK;
+  }
+  const WgradSplit s = wgrad_split(n_out, c_in, c_out, kv);
+  if (s.bytes > kNoAllocScratchFloats * sizeof(float))
+    return fail(SPC_ERR_SIZE_LIMIT,
+                "conv_backward_weight_noalloc: this shape needs %zu bytes of partial sums (%d splits x %d x %d x %d "
+                "fp32) but the built-in scratch holds %zu; use spc_conv_backward_weight with a workspace",
+                s.bytes, s.splits, c_out, kv, c_in, kNoAllocScratchFloats * sizeof(float));
+  float* scratch = nullptr;
+  const int rc = wgrad_scratch_address(&scratch);
+  if (rc != SPC_OK) return rc;
+  return wgrad_simt(features, grad_out, pair_fwd, dweight, scratch, n_out, c_in, c_out, kv, dtype, st);
+}
