@@ -350,10 +350,11 @@ def main():
     for s in range(N_SCENES):  # untimed: algorithmic pair counts of every (scene, layer)
         out = forward(*scenes_dev[s], scene=s)
     prof.count_pairs = False
-    # warm-up with the timed loop's own allocation pattern (the previous step's
-    # output stays alive while the next one runs), so that the caching allocator
-    # makes no cudaMalloc inside the timed region
-    for w in range(max(args.warmup, 2 * N_SCENES)):
+    # warm-up with the timed loop's own allocation pattern (each step's output is
+    # released before the next step starts), over every scene, so that the caching
+    # allocator makes no cudaMalloc inside the timed region
+    for w in range(max(args.warmup, 3 * N_SCENES)):
+        out = None
         out = forward(*scenes_dev[w % N_SCENES], scene=w % N_SCENES)
     prof.records.clear()
     barrier()
@@ -364,6 +365,7 @@ def main():
     dbg = []
     for s in range(args.steps):
         t_a = time.perf_counter()
+        out = None
         out = forward(*scenes_dev[s % N_SCENES], scene=s % N_SCENES)
         if os.environ.get("BENCH_DEBUG"):
             st = torch.cuda.memory_stats()

@@ -134,13 +134,23 @@ int spc_rulebook_prepare(const spc_geometry* g, const int32_t* indices, int64_t 
  *   split_masks  n_split host words ANDed into mask word 0 (0xFFFFFFFF for
  *                MaskImplicitGemm; the two MaskSplit halves otherwise)
  *   n_out may be smaller than the prepared count (num_out_act_bound): rows
- *   beyond it are dropped, as _impl/pairs.py:318-323 does. */
+ *   beyond it are dropped, as _impl/pairs.py:318-323 does.
+ *   pair_fwd_rowmajor [n_out, kvp] / pair_bwd_rowmajor [n_in, kvp] (kvp = kv
+ *   rounded up to 4, padding -1; NULL to skip): the same tables with the kv
+ *   entries of a row contiguous.  The GEMM kernels read a tile's entries from
+ *   these with a few 16-byte loads per row instead of kv scattered 4-byte
+ *   loads; they have no counterpart in the reference. */
 int spc_rulebook_igemm(const spc_geometry* g, const int32_t* indices, int64_t n_in,
                        int64_t n_out, void* workspace, size_t workspace_bytes,
                        int32_t* out_indices, int32_t* pair_fwd, int32_t* pair_bwd,
                        int32_t* mask_fwd, int32_t* argsort_fwd, int32_t* mask_bwd,
                        int32_t* argsort_bwd, const uint32_t* split_masks, int n_split,
-                       int do_sort, void* stream);
+                       int do_sort, int32_t* pair_fwd_rowmajor, int32_t* pair_bwd_rowmajor,
+                       void* stream);
+
+/* Row-major copy [n, kvp] of a pair table [kv, n] that was not produced by
+ * spc_rulebook_igemm (tables converted from the Native format, user tables). */
+int spc_pairs_to_rowmajor(const int32_t* pairs, int kv, int64_t n, int32_t* out, void* stream);
 
 /* Phase 2, Native format: replaces native_pairs, _impl/pairs.py:223-278.
  *   pair [2, kv, n_in] (-1 fill): per offset the contributing input rows in
@@ -163,9 +173,12 @@ int spc_native_to_tables(const int32_t* pair, int kv, int64_t n_pair, int invers
  *   features [n_in, c_in] dtype; weight [c_out, kv, c_in] dtype (KRSC);
  *   bias [c_out] dtype or NULL; out [n_out, c_out] out_dtype;
  *   mask_argsort [n_out] or NULL: the order in which rows are grouped into
- *   tiles (rows with equal offset bitmasks become neighbours). */
+ *   tiles (rows with equal offset bitmasks become neighbours);
+ *   pair_fwd_rowmajor [n_out, kvp] or NULL: the row-major copy of pair_fwd
+ *   (spc_rulebook_igemm / spc_pairs_to_rowmajor); optional, only faster. */
 int spc_conv_forward(const void* features, const void* weight, const void* bias,
-                     const int32_t* pair_fwd, const int32_t* mask_argsort, void* out,
+                     const int32_t* pair_fwd, const int32_t* pair_fwd_rowmajor,
+                     const int32_t* mask_argsort, void* out,
                      int64_t n_in, int64_t n_out, int c_in, int c_out, int kv, int dtype,
                      int out_dtype, int precision, int path, void* stream);
 
@@ -173,7 +186,8 @@ int spc_conv_forward(const void* features, const void* weight, const void* bias,
  *   din[j, c] = sum_k sum_n grad_out[pair_bwd[k, j], n] * weight[n, k, c]
  *   grad_out [n_out, c_out]; din [n_in, c_in], both `dtype`. */
 int spc_conv_backward_input(const void* grad_out, const void* weight,
-                            const int32_t* pair_bwd, const int32_t* mask_argsort, void* din,
+                            const int32_t* pair_bwd, const int32_t* pair_bwd_rowmajor,
+                            const int32_t* mask_argsort, void* din,
                             int64_t n_in, int64_t n_out, int c_in, int c_out, int kv,
                             int dtype, int precision, int path, void* stream);
 

@@ -25,7 +25,8 @@ bool want_tc(int path, int n_dim, int r_dim, int kv, int dtype, int out_dtype, i
 }  // namespace
 
 extern "C" int spc_conv_forward(const void* features, const void* weight, const void* bias,
-                                const int32_t* pair_fwd, const int32_t* mask_argsort, void* out,
+                                const int32_t* pair_fwd, const int32_t* pair_fwd_rowmajor,
+                                const int32_t* mask_argsort, void* out,
                                 int64_t n_in, int64_t n_out, int c_in, int c_out, int kv, int dtype,
                                 int out_dtype, int precision, int path, void* stream) {
   if (!features || !weight || !pair_fwd || !out || n_in < 0 || n_out < 0 || c_in <= 0 || c_out <= 0 || kv <= 0)
@@ -36,7 +37,7 @@ extern "C" int spc_conv_forward(const void* features, const void* weight, const 
   if (want_tc(path, c_out, c_in, kv, dtype, out_dtype, precision, false, &status)) {
     if (path != SPC_GEMM_TCGEN05_CPASYNC &&
         gather_gemm_tma_supported(c_out, c_in, kv, dtype, out_dtype, precision, false))
-      return gather_gemm_tma(features, weight, bias, pair_fwd, mask_argsort, out, n_in, n_out, c_out, c_in, kv,
+      return gather_gemm_tma(features, weight, bias, pair_fwd, pair_fwd_rowmajor, mask_argsort, out, n_in, n_out, c_out, c_in, kv,
                              /*transposed_weight=*/false, dtype, out_dtype, precision, st);
     return gather_gemm_tc(features, weight, bias, pair_fwd, mask_argsort, out, n_out, c_out, c_in, kv,
                           /*transposed_weight=*/false, dtype, out_dtype, precision, st);
@@ -49,7 +50,7 @@ extern "C" int spc_conv_forward(const void* features, const void* weight, const 
 }
 
 extern "C" int spc_conv_backward_input(const void* grad_out, const void* weight, const int32_t* pair_bwd,
-                                       const int32_t* mask_argsort, void* din, int64_t n_in, int64_t n_out,
+                                       const int32_t* pair_bwd_rowmajor, const int32_t* mask_argsort, void* din, int64_t n_in, int64_t n_out,
                                        int c_in, int c_out, int kv, int dtype, int precision, int path,
                                        void* stream) {
   if (!grad_out || !weight || !pair_bwd || !din || n_in < 0 || n_out < 0 || c_in <= 0 || c_out <= 0 || kv <= 0)
@@ -59,7 +60,7 @@ extern "C" int spc_conv_backward_input(const void* grad_out, const void* weight,
   int status;
   if (want_tc(path, c_in, c_out, kv, dtype, dtype, precision, true, &status)) {
     if (path != SPC_GEMM_TCGEN05_CPASYNC && gather_gemm_tma_supported(c_in, c_out, kv, dtype, dtype, precision, true))
-      return gather_gemm_tma(grad_out, weight, nullptr, pair_bwd, mask_argsort, din, n_out, n_in, c_in, c_out, kv,
+      return gather_gemm_tma(grad_out, weight, nullptr, pair_bwd, pair_bwd_rowmajor, mask_argsort, din, n_out, n_in, c_in, c_out, kv,
                              /*transposed_weight=*/true, dtype, dtype, precision, st);
     return gather_gemm_tc(grad_out, weight, nullptr, pair_bwd, mask_argsort, din, n_in, c_in, c_out, kv,
                           /*transposed_weight=*/true, dtype, dtype, precision, st);

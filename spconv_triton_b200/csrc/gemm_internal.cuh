@@ -40,7 +40,7 @@ int* device_status_ptr();
 bool gather_gemm_tma_supported(int n_dim, int r_dim, int kv, int dtype, int out_dtype, int precision,
                                bool transposed_weight);
 int gather_gemm_tma(const void* src, const void* w, const void* bias, const int32_t* pairs,
-                    const int32_t* order, void* out, long long src_rows, long long m_rows, int n_dim, int r_dim,
+                    const int32_t* pairs_rowmajor, const int32_t* order, void* out, long long src_rows, long long m_rows, int n_dim, int r_dim,
                     int kv, bool transposed_weight, int dtype, int out_dtype, int precision, cudaStream_t st);
 
 }  // namespace spc

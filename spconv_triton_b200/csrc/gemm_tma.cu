@@ -65,9 +65,11 @@ struct TmaParams {
   const void* src;
   const void* bias;
   const int32_t* pairs;
+  const int32_t* pairs_rm;  // optional row-major copy [m_rows, kvp]
   const int32_t* order;
   void* out;
   long long m_rows;
+  int kvp;
   int src_rows;  // rows of the gathered matrix; also the "absent row" index
   int n_dim, r_dim, kv;
   int stages, a_stage_bytes, b_stage_bytes, tmem_cols;
@@ -169,11 +171,22 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
       if (tile_warp) {
         // all table entries of the group are requested before any is used
         int jj[kGroup];
+        if (p.pairs_rm != nullptr) {
+          // the row's entries are contiguous: 16-byte loads
+          const int4* rowp = reinterpret_cast<const int4*>(p.pairs_rm + (my_row >= 0 ? my_row : 0) * p.kvp + k0);
 #pragma unroll
-        for (int kk = 0; kk < kGroup; ++kk) {
-          jj[kk] = -1;
-          if (kk < gcount && my_row >= 0)
-            jj[kk] = __ldg(&p.pairs[static_cast<long long>(k0 + kk) * p.m_rows + my_row]);
+          for (int q = 0; q < kGroup / 4; ++q) {
+            int4 v = make_int4(-1, -1, -1, -1);
+            if (4 * q < gcount && my_row >= 0) v = __ldg(rowp + q);
+            jj[4 * q] = v.x; jj[4 * q + 1] = v.y; jj[4 * q + 2] = v.z; jj[4 * q + 3] = v.w;
+          }
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < kGroup; ++kk) {
+            jj[kk] = -1;
+            if (kk < gcount && my_row >= 0)
+              jj[kk] = __ldg(&p.pairs[static_cast<long long>(k0 + kk) * p.m_rows + my_row]);
+          }
         }
         uint32_t mine = 0;
 #pragma unroll
@@ -418,7 +431,7 @@ bool gather_gemm_tma_supported(int n_dim, int r_dim, int kv, int dtype, int out_
 }
 
 int gather_gemm_tma(const void* src, const void* w, const void* bias, const int32_t* pairs,
-                    const int32_t* order, void* out, long long src_rows, long long m_rows, int n_dim, int r_dim,
+                    const int32_t* pairs_rowmajor, const int32_t* order, void* out, long long src_rows, long long m_rows, int n_dim, int r_dim,
                     int kv, bool transposed_weight, int dtype, int out_dtype, int precision, cudaStream_t st) {
   if (!gather_gemm_tma_supported(n_dim, r_dim, kv, dtype, out_dtype, precision, transposed_weight))
     return fail(SPC_ERR_UNSUPPORTED, "TMA gather-GEMM: unsupported shape");
@@ -430,7 +443,7 @@ int gather_gemm_tma(const void* src, const void* w, const void* bias, const int3
   EncodeTiledFn encode = encode_fn();
 
   TmaParams p{};
-  p.src = src; p.bias = bias; p.pairs = pairs; p.order = order; p.out = out;
+  p.src = src; p.bias = bias; p.pairs = pairs; p.pairs_rm = pairs_rowmajor; p.kvp = (kv + 3) & ~3; p.order = order; p.out = out;
   p.m_rows = m_rows; p.src_rows = static_cast<int>(src_rows);
   p.n_dim = n_dim; p.r_dim = r_dim; p.kv = kv;
   p.a_row_bytes = row_span(r_dim, elem);

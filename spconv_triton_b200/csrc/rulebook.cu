@@ -359,11 +359,13 @@ __global__ void __launch_bounds__(kThreads)
 fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
                 const typename Table<K64>::key_t* __restrict__ sorted_out, long long n_out,
                 Table<K64> tin, int32_t* __restrict__ out_indices, int32_t* __restrict__ pair_fwd,
-                int32_t* __restrict__ pair_bwd, uint32_t* __restrict__ words, int mic) {
+                int32_t* __restrict__ pair_bwd, uint32_t* __restrict__ words, int mic,
+                int32_t* __restrict__ fwd_rm, int32_t* __restrict__ bwd_rm, int kvp) {
   using key_t = typename Table<K64>::key_t;
   const long long r = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
   if (r >= n_out) return;
   int o[ND + 1];
+  int quad[4] = {-1, -1, -1, -1};  // four consecutive offsets of the row-major copy
   if (g.subm) {
     load_coord<ND>(idx, r, o);
   } else {
@@ -378,7 +380,17 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
     const long long key = in_key_from_output<ND>(g, o, od.pos);
     const int j = key >= 0 ? tin.find(static_cast<key_t>(key)) : -1;
     pair_fwd[static_cast<long long>(k) * n_out + r] = j;
-    if (SUBM_BWD) pair_bwd[static_cast<long long>(g.kv - 1 - k) * n_out + r] = j;
+    if (SUBM_BWD) {
+      pair_bwd[static_cast<long long>(g.kv - 1 - k) * n_out + r] = j;
+      if (bwd_rm != nullptr) bwd_rm[r * kvp + (g.kv - 1 - k)] = j;
+    }
+    if (fwd_rm != nullptr) {
+      quad[k & 3] = j;
+      if ((k & 3) == 3 || k == g.kv - 1) {
+        *reinterpret_cast<int4*>(&fwd_rm[r * kvp + (k & ~3)]) = make_int4(quad[0], quad[1], quad[2], quad[3]);
+        quad[0] = quad[1] = quad[2] = quad[3] = -1;
+      }
+    }
     word |= static_cast<uint32_t>(j >= 0) << (k & 31);
     if ((k & 31) == 31 || k == g.kv - 1) {
       words[r * mic + (k >> 5)] = word;
@@ -386,6 +398,8 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
     }
     od.next(g);
   }
+  if (SUBM_BWD && bwd_rm != nullptr)
+    for (int k = g.kv; k < kvp; ++k) bwd_rm[r * kvp + k] = -1;
 }
 
 // Column j of pair_bwd (strided / transposed layers): for each offset the
@@ -394,10 +408,11 @@ template <int ND, bool K64>
 __global__ void __launch_bounds__(kThreads)
 fill_bwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n_in,
                 long long n_out, Table<K64> tout, int32_t* __restrict__ pair_bwd,
-                uint32_t* __restrict__ words, int mic) {
+                uint32_t* __restrict__ words, int mic, int32_t* __restrict__ bwd_rm, int kvp) {
   using key_t = typename Table<K64>::key_t;
   const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
   if (j >= n_in) return;
+  int quad[4] = {-1, -1, -1, -1};
   int c[ND + 1];
   load_coord<ND>(idx, j, c);
   Odometer<ND> od;
@@ -408,6 +423,13 @@ fill_bwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, 
     int r = key >= 0 ? tout.find(static_cast<key_t>(key)) : -1;
     if (r >= n_out) r = -1;  // rows cut off by num_out_act_bound
     pair_bwd[static_cast<long long>(k) * n_in + j] = r;
+    if (bwd_rm != nullptr) {
+      quad[k & 3] = r;
+      if ((k & 3) == 3 || k == g.kv - 1) {
+        *reinterpret_cast<int4*>(&bwd_rm[j * kvp + (k & ~3)]) = make_int4(quad[0], quad[1], quad[2], quad[3]);
+        quad[0] = quad[1] = quad[2] = quad[3] = -1;
+      }
+    }
     if (words != nullptr) {
       word |= static_cast<uint32_t>(r >= 0) << (k & 31);
       if ((k & 31) == 31 || k == g.kv - 1) {
@@ -534,6 +556,22 @@ native_write_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ i
     pair[static_cast<long long>(k) * n_in + pos] = static_cast<int32_t>(j);
     pair[(static_cast<long long>(g.kv) + k) * n_in + pos] = r;
   }
+}
+
+// out[row, 4q..4q+3] = pairs[4q..4q+3, row]; one thread per (row, q), q fastest, so
+// that the 16-byte stores of a row are contiguous.
+__global__ void __launch_bounds__(kThreads)
+pairs_to_rowmajor_kernel(const int32_t* __restrict__ pairs, int kv, int kvp, long long n,
+                         int32_t* __restrict__ out) {
+  const long long e = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  const int quads = kvp / 4;
+  const long long row = e / quads;
+  if (row >= n) return;
+  const int k0 = static_cast<int>(e % quads) * 4;
+  int v[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) v[u] = (k0 + u < kv) ? __ldg(&pairs[static_cast<long long>(k0 + u) * n + row]) : -1;
+  *reinterpret_cast<int4*>(&out[row * kvp + k0]) = make_int4(v[0], v[1], v[2], v[3]);
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -771,24 +809,26 @@ template <int ND, bool K64>
 int igemm_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, int64_t n_out, char* ws,
                int32_t* out_indices, int32_t* pair_fwd, int32_t* pair_bwd, int32_t* mask_fwd,
                int32_t* argsort_fwd, int32_t* mask_bwd, int32_t* argsort_bwd,
-               const uint32_t* split_masks, int n_split, int do_sort, cudaStream_t st) {
+               const uint32_t* split_masks, int n_split, int do_sort, int32_t* fwd_rm, int32_t* bwd_rm,
+               cudaStream_t st) {
   using key_t = typename Table<K64>::key_t;
+  const int kvp = (g.kv + 3) & ~3;
   Table<K64> tin = table_at<K64>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
   Table<K64> tout = table_at<K64>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
   const key_t* sorted = reinterpret_cast<const key_t*>(ws + L.off_sorted);
   uint32_t* words = reinterpret_cast<uint32_t*>(ws + L.off_words);
   if (g.subm && pair_bwd != nullptr)
     fill_fwd_kernel<ND, K64, true><<<blocks_for(n_out), kThreads, 0, st>>>(
-        g, idx, sorted, n_out, tin, out_indices, pair_fwd, pair_bwd, words, L.mic);
+        g, idx, sorted, n_out, tin, out_indices, pair_fwd, pair_bwd, words, L.mic, fwd_rm, bwd_rm, kvp);
   else
     fill_fwd_kernel<ND, K64, false><<<blocks_for(n_out), kThreads, 0, st>>>(
-        g, idx, sorted, n_out, tin, out_indices, pair_fwd, nullptr, words, L.mic);
+        g, idx, sorted, n_out, tin, out_indices, pair_fwd, nullptr, words, L.mic, fwd_rm, nullptr, kvp);
   SPC_LAUNCH_OK();
   int rc = emit_masks(L, ws, n_out, g.kv, split_masks, n_split, do_sort, mask_fwd, argsort_fwd, st);
   if (rc != SPC_OK) return rc;
   if (!g.subm && pair_bwd != nullptr) {
     fill_bwd_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(
-        g, idx, n_in, n_out, tout, pair_bwd, mask_bwd ? words : nullptr, L.mic);
+        g, idx, n_in, n_out, tout, pair_bwd, mask_bwd ? words : nullptr, L.mic, bwd_rm, kvp);
     SPC_LAUNCH_OK();
     if (mask_bwd != nullptr) {
       rc = emit_masks(L, ws, n_in, g.kv, split_masks, n_split, do_sort, mask_bwd, argsort_bwd, st);
@@ -883,7 +923,8 @@ extern "C" int spc_rulebook_igemm(const spc_geometry* sg, const int32_t* indices
                                   int32_t* out_indices, int32_t* pair_fwd, int32_t* pair_bwd,
                                   int32_t* mask_fwd, int32_t* argsort_fwd, int32_t* mask_bwd,
                                   int32_t* argsort_bwd, const uint32_t* split_masks, int n_split,
-                                  int do_sort, void* stream) {
+                                  int do_sort, int32_t* pair_fwd_rowmajor, int32_t* pair_bwd_rowmajor,
+                                  void* stream) {
   Geo g;
   if (!make_geo(sg, &g)) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: bad geometry");
   if (n_in <= 0 || n_out <= 0 || !indices || !workspace || !pair_fwd || !mask_fwd || !argsort_fwd ||
@@ -903,7 +944,7 @@ extern "C" int spc_rulebook_igemm(const spc_geometry* sg, const int32_t* indices
   return dispatch(g.ndim, L.k64, [&](auto nd, auto k64) {
     return igemm_impl<decltype(nd)::value, decltype(k64)::value>(
         g, L, indices, n_in, n_out, ws, out_indices, pair_fwd, pair_bwd, mask_fwd, argsort_fwd, mask_bwd,
-        argsort_bwd, split_masks, n_split, do_sort, st);
+        argsort_bwd, split_masks, n_split, do_sort, pair_fwd_rowmajor, pair_bwd_rowmajor, st);
   });
 }
 
@@ -933,6 +974,16 @@ extern "C" int spc_rulebook_native(const spc_geometry* sg, const int32_t* indice
     }
     return native_impl<ND, K64>(g, L, indices, n_in, n_out, ws, out_indices, pair, indice_num_per_loc, st);
   });
+}
+
+extern "C" int spc_pairs_to_rowmajor(const int32_t* pairs, int kv, int64_t n, int32_t* out, void* stream) {
+  if (!pairs || !out || kv <= 0 || n < 0) return fail(SPC_ERR_INVALID_ARGUMENT, "pairs_to_rowmajor: bad arguments");
+  if (n == 0) return SPC_OK;
+  const int kvp = (kv + 3) & ~3;
+  pairs_to_rowmajor_kernel<<<blocks_for(n * (kvp / 4)), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      pairs, kv, kvp, n, out);
+  SPC_LAUNCH_OK();
+  return SPC_OK;
 }
 
 extern "C" int spc_native_to_tables(const int32_t* pair, int kv, int64_t n_pair, int inverse,

@@ -11,6 +11,8 @@ import torch
 
 from spconv_triton_b200 import _lib, constants
 
+from .pairs import rowmajor_of
+
 # Which kernels the GEMM entry points may use: SPC_GEMM_AUTO (tcgen05 whenever
 # the shape allows), SPC_GEMM_SIMT or SPC_GEMM_TCGEN05.  Tests flip this.
 GEMM_PATH = _lib.SPC_GEMM_AUTO
@@ -29,6 +31,15 @@ def _precision(t: torch.Tensor) -> int:
     if t.dtype == torch.float32 and bool(constants.SPCONV_ALLOW_TF32):
         return _lib.SPC_PREC_TF32
     return _lib.SPC_PREC_IEEE
+
+
+def _rowmajor(pair_table, t):
+    """Row-major table copy for the tensor-core kernels (the CUDA-core kernels,
+    which serve IEEE fp32, do not use it, so none is built for them)."""
+    rm = getattr(pair_table, "_spc_rowmajor", None)
+    if rm is None and (t.dtype in (torch.float16, torch.bfloat16) or _precision(t) == _lib.SPC_PREC_TF32):
+        rm = rowmajor_of(pair_table)
+    return rm
 
 
 def _order(kv, pair_mask, mask_argsort):
@@ -67,7 +78,8 @@ def conv_forward(features, filters_krsc, pair_fwd, n_out, bias=None, out_dtype=N
         pf = pair_fwd if pair_fwd.is_contiguous() else pair_fwd.contiguous()
         order = _order(kv, pair_mask, mask_argsort)
         _lib.check(_lib.load().spc_conv_forward(
-            _lib.ptr(feats), _lib.ptr(w), _lib.ptr(b), _lib.ptr(pf), _lib.ptr(order), _lib.ptr(out),
+            _lib.ptr(feats), _lib.ptr(w), _lib.ptr(b), _lib.ptr(pf), _lib.ptr(_rowmajor(pair_fwd, feats)), _lib.ptr(order),
+            _lib.ptr(out),
             feats.shape[0], n_out, c_in, k_out, kv, _lib.dtype_code(feats.dtype), _lib.dtype_code(out_dtype),
             _precision(feats), GEMM_PATH, _lib.current_stream(dev)))
     return out
@@ -89,7 +101,7 @@ def conv_backward_input(grad_out, filters_krsc, pair_bwd, n_in, pair_mask=None, 
         pb = pair_bwd if pair_bwd.is_contiguous() else pair_bwd.contiguous()
         order = _order(kv, pair_mask, mask_argsort)
         _lib.check(_lib.load().spc_conv_backward_input(
-            _lib.ptr(g), _lib.ptr(w), _lib.ptr(pb), _lib.ptr(order), _lib.ptr(din), n_in, g.shape[0], c_in,
+            _lib.ptr(g), _lib.ptr(w), _lib.ptr(pb), _lib.ptr(_rowmajor(pair_bwd, g)), _lib.ptr(order), _lib.ptr(din), n_in, g.shape[0], c_in,
             k_out, kv, _lib.dtype_code(g.dtype), _precision(g), GEMM_PATH, _lib.current_stream(dev)))
     return din
 

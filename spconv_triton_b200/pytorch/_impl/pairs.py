@@ -166,13 +166,21 @@ def igemm_pairs(indices, batch_size, spatial_shape, ksize, stride, padding, dila
         if want_bwd_masks:
             pm_bwd = torch.empty((n_split, p.n_in, mic), dtype=torch.int32, device=dev)
             ma_bwd = torch.empty((n_split, p.n_in), dtype=torch.int32, device=dev)
+        # row-major copies for the GEMM kernels, carried as attributes of the tables
+        kvp = (kv + 3) // 4 * 4
+        fwd_rm = torch.empty((n_out, kvp), dtype=torch.int32, device=dev)
+        bwd_rm = torch.empty((p.n_in, kvp), dtype=torch.int32, device=dev) if want_bwd else None
         split_words = (ctypes.c_uint32 * n_split)(*[int(m[0]) for m in masks])
         _lib.check(_lib.load().spc_rulebook_igemm(
             ctypes.byref(p.geom), _lib.ptr(p.indices), p.n_in, n_out, _lib.ptr(p.workspace),
             p.workspace.numel(), None if subm else _lib.ptr(out_inds), _lib.ptr(pair_fwd),
             _lib.ptr(pair_bwd), _lib.ptr(pm_fwd), _lib.ptr(ma_fwd), _lib.ptr(pm_bwd), _lib.ptr(ma_bwd),
-            split_words, n_split, int(bool(do_sort)), _lib.current_stream(dev)))
+            split_words, n_split, int(bool(do_sort)), _lib.ptr(fwd_rm), _lib.ptr(bwd_rm),
+            _lib.current_stream(dev)))
         npl = torch.zeros(kv, dtype=torch.int32, device=dev)
+        pair_fwd._spc_rowmajor = fwd_rm
+        if want_bwd:
+            pair_bwd._spc_rowmajor = bwd_rm
     pb = pair_bwd if want_bwd else torch.Tensor()
     pm_fwd_splits = [pm_fwd[s] for s in range(n_split)]
     ma_fwd_splits = [ma_fwd[s] for s in range(n_split)]
@@ -205,3 +213,21 @@ def native_pair_to_tables(pair, indice_pair_num, n_in, n_out, inverse, need_bwd=
                 int(n_in), _lib.current_stream(dev)))
         cache[key] = (pf, pb)
     return pf, pb
+
+
+def rowmajor_of(pair_table):
+    """Row-major copy [n, kvp] of a pair table [kv, n] for the GEMM kernels:
+    the one the rulebook attached, or one built (and memoised on the tensor) now."""
+    rm = getattr(pair_table, "_spc_rowmajor", None)
+    if rm is None:
+        kv, n = int(pair_table.shape[0]), int(pair_table.shape[1])
+        dev = pair_table.device
+        src = pair_table if pair_table.is_contiguous() else pair_table.contiguous()
+        with torch.cuda.device(dev):
+            rm = torch.empty((n, (kv + 3) // 4 * 4), dtype=torch.int32, device=dev)
+            _lib.check(_lib.load().spc_pairs_to_rowmajor(_lib.ptr(src), kv, n, _lib.ptr(rm), _lib.current_stream(dev)))
+        try:
+            pair_table._spc_rowmajor = rm
+        except AttributeError:
+            pass
+    return rm
