@@ -1,5 +1,7 @@
 // C-ABI entry points of the implicit gather-GEMM and the choice between the
 // tcgen05 kernels and the CUDA-core kernels.
+#include <algorithm>
+
 #include "common.cuh"
 #include "gemm_internal.cuh"
 
@@ -74,7 +76,8 @@ extern "C" int spc_conv_backward_input(const void* grad_out, const void* weight,
 
 extern "C" size_t spc_conv_backward_weight_workspace_bytes(int64_t n_out, int c_in, int c_out, int kv) {
   if (n_out < 0 || c_in <= 0 || c_out <= 0 || kv <= 0) return 0;
-  return wgrad_split(n_out, c_in, c_out, kv).bytes;
+  // enough for whichever kernel the call ends up using
+  return std::max(wgrad_split(n_out, c_in, c_out, kv).bytes, wgrad_tc_split(n_out, c_in, c_out, kv).bytes);
 }
 
 extern "C" int spc_conv_backward_weight(const void* features, const void* grad_out, const int32_t* pair_fwd,
@@ -90,8 +93,20 @@ extern "C" int spc_conv_backward_weight(const void* features, const void* grad_o
     SPC_CUDA_OK(cudaMemsetAsync(dweight, 0, static_cast<size_t>(c_out) * kv * c_in * dtype_size(dtype), st));
     return SPC_OK;
   }
+  if (path != SPC_GEMM_SIMT && wgrad_tc_supported(c_in, c_out, kv, dtype)) {
+    const WgradSplit ts = wgrad_tc_split(n_out, c_in, c_out, kv);
+    if (!workspace || workspace_bytes < ts.bytes)
+      return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "conv_backward_weight: workspace %zu < %zu bytes", workspace_bytes,
+                  ts.bytes);
+    const int rc = wgrad_tc(features, grad_out, pair_fwd, static_cast<float*>(workspace), n_out, c_in, c_out, kv,
+                            dtype, ts, st);
+    if (rc != SPC_OK) return rc;
+    return wgrad_reduce(static_cast<const float*>(workspace), dweight, static_cast<long long>(c_out) * kv * c_in,
+                        ts.splits, dtype, st);
+  }
   if (path == SPC_GEMM_TCGEN05)
-    return fail(SPC_ERR_UNSUPPORTED, "conv_backward_weight: no tcgen05 kernel for this op yet");
+    return fail(SPC_ERR_UNSUPPORTED, "conv_backward_weight: the tcgen05 kernel does not take this shape/dtype "
+                "(c_in=%d c_out=%d dtype=%d)", c_in, c_out, dtype);
   const WgradSplit s = wgrad_split(n_out, c_in, c_out, kv);
   if (!workspace || workspace_bytes < s.bytes)
     return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "conv_backward_weight: workspace %zu < %zu bytes", workspace_bytes,

@@ -33,6 +33,15 @@ int gather_gemm_tc(const void* src, const void* w, const void* bias, const int32
                    const int32_t* order, void* out, long long m_rows, int n_dim, int r_dim, int kv,
                    bool transposed_weight, int dtype, int out_dtype, int precision, cudaStream_t st);
 
+// dw[e] = sum over splits of partial[s, e], added in split order (deterministic).
+int wgrad_reduce(const float* partial, void* dw, long long elems, int splits, int dtype, cudaStream_t st);
+
+// tcgen05 weight gradient (gemm_wgrad_tc.cu): fp32 partial tiles, to be followed by wgrad_reduce.
+bool wgrad_tc_supported(int c_in, int c_out, int kv, int dtype);
+WgradSplit wgrad_tc_split(int64_t n_out, int c_in, int c_out, int kv);
+int wgrad_tc(const void* feats, const void* gout, const int32_t* pair_fwd, float* partial, int64_t n_out, int c_in,
+             int c_out, int kv, int dtype, const WgradSplit& split, cudaStream_t st);
+
 int* device_status_ptr();
 
 // TMA-fed variant of the tcgen05 kernel (gemm_tma.cu): feature rows arrive by

@@ -269,6 +269,17 @@ WgradSplit wgrad_split(int64_t n_out, int c_in, int c_out, int kv) {
   return s;
 }
 
+int wgrad_reduce(const float* partial, void* dw, long long elems, int splits, int dtype, cudaStream_t st) {
+  const unsigned rblocks = static_cast<unsigned>(ceil_div(elems, 256));
+  if (dtype == SPC_F16) wgrad_reduce_kernel<__half><<<rblocks, 256, 0, st>>>(partial, static_cast<__half*>(dw), elems, splits);
+  else if (dtype == SPC_BF16)
+    wgrad_reduce_kernel<__nv_bfloat16><<<rblocks, 256, 0, st>>>(partial, static_cast<__nv_bfloat16*>(dw), elems, splits);
+  else if (dtype == SPC_F32) wgrad_reduce_kernel<float><<<rblocks, 256, 0, st>>>(partial, static_cast<float*>(dw), elems, splits);
+  else return fail(SPC_ERR_UNSUPPORTED, "wgrad reduce: dtype %d not supported", dtype);
+  SPC_LAUNCH_OK();
+  return SPC_OK;
+}
+
 int wgrad_simt(const void* feats, const void* gout, const int32_t* pair_fwd, void* dw, float* partial,
                int64_t n_out, int c_in, int c_out, int kv, int dtype, cudaStream_t st) {
   const WgradSplit s = wgrad_split(n_out, c_in, c_out, kv);
