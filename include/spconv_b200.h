@@ -62,6 +62,10 @@ typedef enum {
   SPC_GEMM_TCGEN05_CPASYNC = 3
 } spc_gemm_path;
 
+/* Activation fused into the forward GEMM's store (the reference applies
+ * act_type after its kernel, spconv_triton/pytorch/ops.py:63-73). */
+typedef enum { SPC_ACT_NONE = 0, SPC_ACT_RELU = 1, SPC_ACT_SIGMOID = 2, SPC_ACT_LEAKY_RELU = 3 } spc_activation;
+
 /* Geometry of one rulebook.  in_shape/out_shape are the spatial shapes before
  * and after the layer (the caller computes out_shape with
  * spc_conv_output_size / spc_deconv_output_size).  For subm the library
@@ -175,12 +179,17 @@ int spc_native_to_tables(const int32_t* pair, int kv, int64_t n_pair, int invers
  *   mask_argsort [n_out] or NULL: the order in which rows are grouped into
  *   tiles (rows with equal offset bitmasks become neighbours);
  *   pair_fwd_rowmajor [n_out, kvp] or NULL: the row-major copy of pair_fwd
- *   (spc_rulebook_igemm / spc_pairs_to_rowmajor); optional, only faster. */
+ *   (spc_rulebook_igemm / spc_pairs_to_rowmajor); optional, only faster;
+ *   out_scale, out_shift: fp32 [c_out] or both NULL; when given the store is
+ *   out = act((acc + bias) * out_scale + out_shift), i.e. an inference
+ *   BatchNorm folded into the layer; act / act_alpha: spc_activation and the
+ *   LeakyReLU slope. */
 int spc_conv_forward(const void* features, const void* weight, const void* bias,
                      const int32_t* pair_fwd, const int32_t* pair_fwd_rowmajor,
                      const int32_t* mask_argsort, void* out,
                      int64_t n_in, int64_t n_out, int c_in, int c_out, int kv, int dtype,
-                     int out_dtype, int precision, int path, void* stream);
+                     int out_dtype, int precision, int path, const float* out_scale,
+                     const float* out_shift, int act, float act_alpha, void* stream);
 
 /* Input gradient: replaces conv_backward_input, _impl/gemm.py:571-631.
  *   din[j, c] = sum_k sum_n grad_out[pair_bwd[k, j], n] * weight[n, k, c]

@@ -15,6 +15,7 @@ LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libspconv_b200.so"
 SPC_MAX_NDIM = 4
 SPC_F16, SPC_BF16, SPC_F32, SPC_F64 = 0, 1, 2, 3
 SPC_PREC_IEEE, SPC_PREC_TF32 = 0, 1
+SPC_ACT_NONE, SPC_ACT_RELU, SPC_ACT_SIGMOID, SPC_ACT_LEAKY_RELU = 0, 1, 2, 3
 SPC_GEMM_AUTO, SPC_GEMM_SIMT, SPC_GEMM_TCGEN05, SPC_GEMM_TCGEN05_CPASYNC = 0, 1, 2, 3
 
 _I4 = c_int32 * SPC_MAX_NDIM
@@ -75,7 +76,7 @@ _PROTOTYPES = {
     "spc_rulebook_native": (c_int, [POINTER(Geometry), _P, c_int64, c_int64, _P, c_size_t, _P, _P, _P, _P]),
     "spc_native_to_tables": (c_int, [_P, c_int, c_int64, c_int, _P, c_int64, _P, c_int64, _P]),
     "spc_conv_forward": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
-                                 c_int, c_int, _P]),
+                                 c_int, c_int, _P, _P, c_int, ctypes.c_float, _P]),
     "spc_conv_backward_input": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int,
                                         c_int, c_int, _P]),
     "spc_conv_backward_weight_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int]),

@@ -57,6 +57,18 @@ inline int sm_count() {
   return cached;
 }
 
+// What happens to an accumulator row before it is stored:
+//   v = acc (+ bias[n]);  v = v * scale[n] + shift[n] (if scale);  v = act(v)
+// bias has the dtype of the inputs; scale and shift are fp32 (a folded
+// inference BatchNorm); act is an spc_activation.
+struct Epilogue {
+  const void* bias = nullptr;
+  const float* scale = nullptr;
+  const float* shift = nullptr;
+  int act = 0;
+  float alpha = 0.f;
+};
+
 inline size_t dtype_size(int dtype) {
   switch (dtype) {
     case SPC_F16:
@@ -89,5 +101,60 @@ template <>
 __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T>
+__device__ __forceinline__ float apply_epilogue(float v, const Epilogue& e, int n) {
+  if (e.bias != nullptr) v += to_float(static_cast<const T*>(e.bias)[n]);
+  if (e.scale != nullptr) v = fmaf(v, __ldg(&e.scale[n]), __ldg(&e.shift[n]));
+  if (e.act == SPC_ACT_RELU) v = fmaxf(v, 0.f);
+  else if (e.act == SPC_ACT_LEAKY_RELU) v = v > 0.f ? v : v * e.alpha;
+  else if (e.act == SPC_ACT_SIGMOID) v = 1.f / (1.f + __expf(-v));
+  return v;
+}
+
+// The same epilogue with bias, scale and shift pre-combined per channel in
+// shared memory by stage_epilogue(): v = act(v * sc[n] + sh[n]).
+template <typename T>
+__device__ __forceinline__ void stage_epilogue(const Epilogue& e, int n_dim, float* sc, float* sh, int tid,
+                                               int n_threads) {
+  for (int n = tid; n < n_dim; n += n_threads) {
+    const float scale = e.scale != nullptr ? e.scale[n] : 1.f;
+    float shift = e.shift != nullptr ? e.shift[n] : 0.f;
+    if (e.bias != nullptr) shift = fmaf(to_float(static_cast<const T*>(e.bias)[n]), scale, shift);
+    sc[n] = scale;
+    sh[n] = shift;
+  }
+}
+// 16 consecutive channels at once; sc / sh point to 16-byte aligned shared memory.
+__device__ __forceinline__ void finish_epilogue16(float* v, const float* sc, const float* sh, int act, float alpha) {
+  float s[16], t[16];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float4 a = reinterpret_cast<const float4*>(sc)[q];
+    const float4 b = reinterpret_cast<const float4*>(sh)[q];
+    s[4 * q] = a.x; s[4 * q + 1] = a.y; s[4 * q + 2] = a.z; s[4 * q + 3] = a.w;
+    t[4 * q] = b.x; t[4 * q + 1] = b.y; t[4 * q + 2] = b.z; t[4 * q + 3] = b.w;
+  }
+  if (act == SPC_ACT_RELU) {
+#pragma unroll
+    for (int q = 0; q < 16; ++q) v[q] = fmaxf(fmaf(v[q], s[q], t[q]), 0.f);
+  } else if (act == SPC_ACT_NONE) {
+#pragma unroll
+    for (int q = 0; q < 16; ++q) v[q] = fmaf(v[q], s[q], t[q]);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {
+      const float x = fmaf(v[q], s[q], t[q]);
+      v[q] = act == SPC_ACT_LEAKY_RELU ? (x > 0.f ? x : x * alpha) : 1.f / (1.f + __expf(-x));
+    }
+  }
+}
+__device__ __forceinline__ float finish_epilogue(float v, float sc, float sh, int act, float alpha) {
+  v = fmaf(v, sc, sh);
+  if (act == SPC_ACT_RELU) v = fmaxf(v, 0.f);
+  else if (act == SPC_ACT_LEAKY_RELU) v = v > 0.f ? v : v * alpha;
+  else if (act == SPC_ACT_SIGMOID) v = 1.f / (1.f + __expf(-v));
+  return v;
+}
 
 }  // namespace spc

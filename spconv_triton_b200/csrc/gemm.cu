@@ -30,23 +30,28 @@ extern "C" int spc_conv_forward(const void* features, const void* weight, const 
                                 const int32_t* pair_fwd, const int32_t* pair_fwd_rowmajor,
                                 const int32_t* mask_argsort, void* out,
                                 int64_t n_in, int64_t n_out, int c_in, int c_out, int kv, int dtype,
-                                int out_dtype, int precision, int path, void* stream) {
+                                int out_dtype, int precision, int path, const float* out_scale,
+                                const float* out_shift, int act, float act_alpha, void* stream) {
   if (!features || !weight || !pair_fwd || !out || n_in < 0 || n_out < 0 || c_in <= 0 || c_out <= 0 || kv <= 0)
     return fail(SPC_ERR_INVALID_ARGUMENT, "conv_forward: bad arguments");
+  if ((out_scale == nullptr) != (out_shift == nullptr))
+    return fail(SPC_ERR_INVALID_ARGUMENT, "conv_forward: out_scale and out_shift go together");
   if (n_out == 0) return SPC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Epilogue epi;
+  epi.bias = bias; epi.scale = out_scale; epi.shift = out_shift; epi.act = act; epi.alpha = act_alpha;
   int status;
   if (want_tc(path, c_out, c_in, kv, dtype, out_dtype, precision, false, &status)) {
     if (path != SPC_GEMM_TCGEN05_CPASYNC &&
         gather_gemm_tma_supported(c_out, c_in, kv, dtype, out_dtype, precision, false))
-      return gather_gemm_tma(features, weight, bias, pair_fwd, pair_fwd_rowmajor, mask_argsort, out, n_in, n_out, c_out, c_in, kv,
+      return gather_gemm_tma(features, weight, epi, pair_fwd, pair_fwd_rowmajor, mask_argsort, out, n_in, n_out, c_out, c_in, kv,
                              /*transposed_weight=*/false, dtype, out_dtype, precision, st);
-    return gather_gemm_tc(features, weight, bias, pair_fwd, mask_argsort, out, n_out, c_out, c_in, kv,
+    return gather_gemm_tc(features, weight, epi, pair_fwd, mask_argsort, out, n_out, c_out, c_in, kv,
                           /*transposed_weight=*/false, dtype, out_dtype, precision, st);
   }
   if (status != SPC_OK) return status;
   // weight[n, k, c]: reduction index c has stride 1, output channel n stride kv*c_in.
-  return gather_gemm_simt(features, weight, bias, pair_fwd, mask_argsort, out, n_out, c_out, c_in, kv,
+  return gather_gemm_simt(features, weight, epi, pair_fwd, mask_argsort, out, n_out, c_out, c_in, kv,
                           /*s_wk=*/c_in, /*s_wr=*/1, /*s_wn=*/static_cast<long long>(kv) * c_in, dtype,
                           out_dtype, st);
 }
@@ -62,14 +67,14 @@ extern "C" int spc_conv_backward_input(const void* grad_out, const void* weight,
   int status;
   if (want_tc(path, c_in, c_out, kv, dtype, dtype, precision, true, &status)) {
     if (path != SPC_GEMM_TCGEN05_CPASYNC && gather_gemm_tma_supported(c_in, c_out, kv, dtype, dtype, precision, true))
-      return gather_gemm_tma(grad_out, weight, nullptr, pair_bwd, pair_bwd_rowmajor, mask_argsort, din, n_out, n_in, c_in, c_out, kv,
+      return gather_gemm_tma(grad_out, weight, Epilogue{}, pair_bwd, pair_bwd_rowmajor, mask_argsort, din, n_out, n_in, c_in, c_out, kv,
                              /*transposed_weight=*/true, dtype, dtype, precision, st);
-    return gather_gemm_tc(grad_out, weight, nullptr, pair_bwd, mask_argsort, din, n_in, c_in, c_out, kv,
+    return gather_gemm_tc(grad_out, weight, Epilogue{}, pair_bwd, mask_argsort, din, n_in, c_in, c_out, kv,
                           /*transposed_weight=*/true, dtype, dtype, precision, st);
   }
   if (status != SPC_OK) return status;
   // output channel is c (stride 1), reduction index is n (stride kv*c_in).
-  return gather_gemm_simt(grad_out, weight, nullptr, pair_bwd, mask_argsort, din, n_in, c_in, c_out, kv,
+  return gather_gemm_simt(grad_out, weight, Epilogue{}, pair_bwd, mask_argsort, din, n_in, c_in, c_out, kv,
                           /*s_wk=*/c_in, /*s_wr=*/static_cast<long long>(kv) * c_in, /*s_wn=*/1, dtype, dtype,
                           st);
 }

@@ -6,11 +6,13 @@
 #include <cstddef>
 #include <cstdint>
 
+#include "common.cuh"
+
 namespace spc {
 
 // out[rm, n] = sum_k sum_r src[pairs[k, rm], r] * w[n*s_wn + k*s_wk + r*s_wr] (+ bias[n]),
 // rm = order ? order[slot] : slot.  CUDA-core kernel, any channel counts.
-int gather_gemm_simt(const void* src, const void* w, const void* bias, const int32_t* pairs,
+int gather_gemm_simt(const void* src, const void* w, const Epilogue& epi, const int32_t* pairs,
                      const int32_t* order, void* out, long long m_rows, int n_dim, int r_dim, int kv,
                      long long s_wk, long long s_wr, long long s_wn, int dtype, int out_dtype,
                      cudaStream_t st);
@@ -29,7 +31,7 @@ int wgrad_simt(const void* feats, const void* gout, const int32_t* pair_fwd, voi
 // view of the KRSC weight.  Return SPC_ERR_UNSUPPORTED for shapes they do not take.
 bool gather_gemm_tc_supported(int n_dim, int r_dim, int kv, int dtype, int out_dtype, int precision,
                               bool transposed_weight);
-int gather_gemm_tc(const void* src, const void* w, const void* bias, const int32_t* pairs,
+int gather_gemm_tc(const void* src, const void* w, const Epilogue& epi, const int32_t* pairs,
                    const int32_t* order, void* out, long long m_rows, int n_dim, int r_dim, int kv,
                    bool transposed_weight, int dtype, int out_dtype, int precision, cudaStream_t st);
 
@@ -48,7 +50,7 @@ int* device_status_ptr();
 // cp.async.bulk.tensor tile::gather4, weight slabs by tiled TMA loads.
 bool gather_gemm_tma_supported(int n_dim, int r_dim, int kv, int dtype, int out_dtype, int precision,
                                bool transposed_weight);
-int gather_gemm_tma(const void* src, const void* w, const void* bias, const int32_t* pairs,
+int gather_gemm_tma(const void* src, const void* w, const Epilogue& epi, const int32_t* pairs,
                     const int32_t* pairs_rowmajor, const int32_t* order, void* out, long long src_rows, long long m_rows, int n_dim, int r_dim,
                     int kv, bool transposed_weight, int dtype, int out_dtype, int precision, cudaStream_t st);
 

@@ -35,7 +35,7 @@ constexpr int kGemmThreads = (BM / TM) * (BN / TN);  // 256
 // out[rm, n] = sum_k sum_r src[pairs[k, rm], r] * w[n*s_wn + k*s_wk + r*s_wr] (+ bias[n])
 template <typename T, typename TO>
 __global__ void __launch_bounds__(kGemmThreads)
-gather_gemm_simt_kernel(const T* __restrict__ src, const T* __restrict__ w, const T* __restrict__ bias,
+gather_gemm_simt_kernel(const T* __restrict__ src, const T* __restrict__ w, const Epilogue epi,
                         const int32_t* __restrict__ pairs, const int32_t* __restrict__ order,
                         TO* __restrict__ out, long long m_rows, int n_dim, int r_dim, int kv,
                         long long s_wk, long long s_wr, long long s_wn) {
@@ -116,9 +116,7 @@ gather_gemm_simt_kernel(const T* __restrict__ src, const T* __restrict__ w, cons
     for (int j = 0; j < TN; ++j) {
       const int n = n0 + tx * TN + j;
       if (n >= n_dim) continue;
-      A v = acc[i][j];
-      if (bias != nullptr) v += to_acc<A>(bias[n]);
-      out[rm * n_dim + n] = from_acc<TO>(v);
+      out[rm * n_dim + n] = from_acc<TO>(apply_epilogue<T>(acc[i][j], epi, n));
     }
   }
 }
@@ -228,12 +226,12 @@ wgrad_reduce_kernel(const float* __restrict__ partial, T* __restrict__ dw, long 
 }
 
 template <typename T, typename TO>
-int launch_gather(const void* src, const void* w, const void* bias, const int32_t* pairs,
+int launch_gather(const void* src, const void* w, const Epilogue& epi, const int32_t* pairs,
                   const int32_t* order, void* out, long long m_rows, int n_dim, int r_dim, int kv,
                   long long s_wk, long long s_wr, long long s_wn, cudaStream_t st) {
   dim3 grid(static_cast<unsigned>(ceil_div(m_rows, BM)), static_cast<unsigned>(ceil_div(n_dim, BN)));
   gather_gemm_simt_kernel<T, TO><<<grid, kGemmThreads, 0, st>>>(
-      static_cast<const T*>(src), static_cast<const T*>(w), static_cast<const T*>(bias), pairs, order,
+      static_cast<const T*>(src), static_cast<const T*>(w), epi, pairs, order,
       static_cast<TO*>(out), m_rows, n_dim, r_dim, kv, s_wk, s_wr, s_wn);
   SPC_LAUNCH_OK();
   return SPC_OK;
@@ -241,12 +239,12 @@ int launch_gather(const void* src, const void* w, const void* bias, const int32_
 
 }  // namespace
 
-int gather_gemm_simt(const void* src, const void* w, const void* bias, const int32_t* pairs,
+int gather_gemm_simt(const void* src, const void* w, const Epilogue& epi, const int32_t* pairs,
                      const int32_t* order, void* out, long long m_rows, int n_dim, int r_dim, int kv,
                      long long s_wk, long long s_wr, long long s_wn, int dtype, int out_dtype,
                      cudaStream_t st) {
 #define SPC_GG(T, TO) \
-  return launch_gather<T, TO>(src, w, bias, pairs, order, out, m_rows, n_dim, r_dim, kv, s_wk, s_wr, s_wn, st)
+  return launch_gather<T, TO>(src, w, epi, pairs, order, out, m_rows, n_dim, r_dim, kv, s_wk, s_wr, s_wn, st)
   if (dtype == SPC_F16 && out_dtype == SPC_F16) SPC_GG(__half, __half);
   if (dtype == SPC_F16 && out_dtype == SPC_F32) SPC_GG(__half, float);
   if (dtype == SPC_BF16 && out_dtype == SPC_BF16) SPC_GG(__nv_bfloat16, __nv_bfloat16);

@@ -48,7 +48,7 @@ using namespace tc;
 struct TcParams {
   const void* src;
   const void* w;
-  const void* bias;
+  Epilogue epi;
   const int32_t* pairs;
   const int32_t* order;
   void* out;
@@ -78,6 +78,8 @@ gather_gemm_tc_kernel(const __grid_constant__ TcParams p) {
   uint32_t* vote = reinterpret_cast<uint32_t*>(info + kMaxStages);  // [4]
   uint32_t* tmem_slot = vote + 4;
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  float* epi_scale = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(abort_flag + 1) + 15) & ~uintptr_t(15));  // [256]
+  float* epi_shift = epi_scale + 256;                             // [256] per-channel shift (bias folded in)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -101,6 +103,8 @@ gather_gemm_tc_kernel(const __grid_constant__ TcParams p) {
     tmem_alloc(smem_u32(tmem_slot), static_cast<uint32_t>(p.tmem_cols));
     tmem_relinquish();
   }
+  const bool has_epilogue = p.epi.bias != nullptr || p.epi.scale != nullptr || p.epi.act != SPC_ACT_NONE;
+  if (has_epilogue) stage_epilogue<T>(p.epi, p.n_dim, epi_scale, epi_shift, tid, kThreadsTc);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -219,7 +223,6 @@ gather_gemm_tc_kernel(const __grid_constant__ TcParams p) {
     tc_fence_after();
     if (have_acc) {
       TO* out_row = static_cast<TO*>(p.out) + (my_row >= 0 ? my_row : 0) * p.n_dim;
-      const T* bias = static_cast<const T*>(p.bias);
       const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
       for (int c0 = 0; c0 < p.n_dim; c0 += 16) {
         float v[16];
@@ -234,10 +237,7 @@ gather_gemm_tc_kernel(const __grid_constant__ TcParams p) {
           for (int q = 0; q < 16; ++q) v[q] = 0.f;
         }
         if (my_row >= 0) {
-          if (bias != nullptr) {
-#pragma unroll
-            for (int q = 0; q < 16; ++q) v[q] += to_float(bias[c0 + q]);
-          }
+if (has_epilogue) finish_epilogue16(v, epi_scale + c0, epi_shift + c0, p.epi.act, p.epi.alpha);
           store_row16<TO>(out_row + c0, v);
         }
       }
@@ -314,7 +314,7 @@ TcPlan make_plan(int n_dim, int r_dim, int elem, bool b_mn) {
   pl.b_stage_bytes = static_cast<int>(align_up(pl.b_stage_bytes, 1024));
   const int stage_bytes = kAStageBytes + pl.b_stage_bytes;
   const size_t fixed = 1024 /*alignment slack*/ + kGroup * kTileM * 4 + (2 * kMaxStages + 1) * 8 +
-                       kMaxStages * sizeof(StageInfo) + 64;
+                       kMaxStages * sizeof(StageInfo) + 64 + 2 * 256 * sizeof(float) + 16;
   const size_t budget = 110 * 1024;  // two CTAs per SM
   int stages = static_cast<int>((budget - fixed) / stage_bytes);
   stages = std::max(2, std::min(stages, 6));
@@ -378,7 +378,7 @@ bool gather_gemm_tc_supported(int n_dim, int r_dim, int kv, int dtype, int out_d
   return true;
 }
 
-int gather_gemm_tc(const void* src, const void* w, const void* bias, const int32_t* pairs,
+int gather_gemm_tc(const void* src, const void* w, const Epilogue& epi, const int32_t* pairs,
                    const int32_t* order, void* out, long long m_rows, int n_dim, int r_dim, int kv,
                    bool transposed_weight, int dtype, int out_dtype, int precision, cudaStream_t st) {
   if (!gather_gemm_tc_supported(n_dim, r_dim, kv, dtype, out_dtype, precision, transposed_weight))
@@ -386,7 +386,7 @@ int gather_gemm_tc(const void* src, const void* w, const void* bias, const int32
   if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15u)
     return fail(SPC_ERR_UNSUPPORTED, "tcgen05 gather-GEMM: operands must be 16-byte aligned");
   TcParams p{};
-  p.src = src; p.w = w; p.bias = bias; p.pairs = pairs; p.order = order; p.out = out;
+  p.src = src; p.w = w; p.epi = epi; p.pairs = pairs; p.order = order; p.out = out;
   p.m_rows = m_rows; p.n_dim = n_dim; p.r_dim = r_dim; p.kv = kv;
   p.status = device_status_ptr();
   if (p.status == nullptr) return fail(SPC_ERR_CUDA, "tcgen05 gather-GEMM: no device status word");

@@ -63,7 +63,7 @@ __device__ long long g_trace[1024];
 
 struct TmaParams {
   const void* src;
-  const void* bias;
+  Epilogue epi;
   const int32_t* pairs;
   const int32_t* pairs_rm;  // optional row-major copy [m_rows, kvp]
   const int32_t* order;
@@ -87,7 +87,7 @@ constexpr int kMmaWarp = kIssueWarps;                 // warp 8
 constexpr int kThreadsHybrid = kIssueThreads + 32;    // 288
 
 template <typename T, typename TO, bool B_MN>
-__global__ void __launch_bounds__(kThreadsHybrid, 1)
+__global__ void __maxnreg__(80)
 gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constant__ CUtensorMap map_b) {
   constexpr int ELEM = sizeof(T);
   constexpr int UMMA_K = 32 / ELEM;
@@ -103,6 +103,8 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
   uint32_t* vote = reinterpret_cast<uint32_t*>(info + kMaxStages);
   uint32_t* tmem_slot = vote + 4;
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  float* epi_scale = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(abort_flag + 1) + 15) & ~uintptr_t(15));  // [256]
+  float* epi_shift = epi_scale + 256;                             // [256] per-channel shift (bias folded in)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -126,6 +128,8 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
     tmem_alloc(smem_u32(tmem_slot), static_cast<uint32_t>(p.tmem_cols));
     tmem_relinquish();
   }
+  const bool has_epilogue = p.epi.bias != nullptr || p.epi.scale != nullptr || p.epi.act != SPC_ACT_NONE;
+  if (has_epilogue) stage_epilogue<T>(p.epi, p.n_dim, epi_scale, epi_shift, tid, kThreadsHybrid);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -277,8 +281,7 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
       tc_fence_after();
       if (have_acc) {
         TO* out_row = static_cast<TO*>(p.out) + (my_row >= 0 ? my_row : 0) * p.n_dim;
-        const T* bias = static_cast<const T*>(p.bias);
-        const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+          const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
         for (int c0 = 0; c0 < p.n_dim; c0 += 16) {
           float v[16];
           if (real_stages > 0) {
@@ -292,10 +295,7 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
             for (int q = 0; q < 16; ++q) v[q] = 0.f;
           }
           if (my_row >= 0) {
-            if (bias != nullptr) {
-#pragma unroll
-              for (int q = 0; q < 16; ++q) v[q] += to_float(bias[c0 + q]);
-            }
+if (has_epilogue) finish_epilogue16(v, epi_scale + c0, epi_shift + c0, p.epi.act, p.epi.alpha);
             store_row16<TO>(out_row + c0, v);
           }
         }
@@ -430,7 +430,7 @@ bool gather_gemm_tma_supported(int n_dim, int r_dim, int kv, int dtype, int out_
   return encode_fn() != nullptr;
 }
 
-int gather_gemm_tma(const void* src, const void* w, const void* bias, const int32_t* pairs,
+int gather_gemm_tma(const void* src, const void* w, const Epilogue& epi, const int32_t* pairs,
                     const int32_t* pairs_rowmajor, const int32_t* order, void* out, long long src_rows, long long m_rows, int n_dim, int r_dim,
                     int kv, bool transposed_weight, int dtype, int out_dtype, int precision, cudaStream_t st) {
   if (!gather_gemm_tma_supported(n_dim, r_dim, kv, dtype, out_dtype, precision, transposed_weight))
@@ -443,7 +443,7 @@ int gather_gemm_tma(const void* src, const void* w, const void* bias, const int3
   EncodeTiledFn encode = encode_fn();
 
   TmaParams p{};
-  p.src = src; p.bias = bias; p.pairs = pairs; p.pairs_rm = pairs_rowmajor; p.kvp = (kv + 3) & ~3; p.order = order; p.out = out;
+  p.src = src; p.epi = epi; p.pairs = pairs; p.pairs_rm = pairs_rowmajor; p.kvp = (kv + 3) & ~3; p.order = order; p.out = out;
   p.m_rows = m_rows; p.src_rows = static_cast<int>(src_rows);
   p.n_dim = n_dim; p.r_dim = r_dim; p.kv = kv;
   p.a_row_bytes = row_span(r_dim, elem);
@@ -459,7 +459,7 @@ int gather_gemm_tma(const void* src, const void* w, const void* bias, const int3
   }
   p.b_stage_bytes = static_cast<int>(align_up(p.b_stage_bytes, 1024));
   const int stage_bytes = p.a_stage_bytes + p.b_stage_bytes;
-  const size_t fixed = 1024 + kGroup * kTileM * 4 + (2 * kMaxStages + 1) * 8 + kMaxStages * sizeof(StageInfo) + 64;
+  const size_t fixed = 1024 + kGroup * kTileM * 4 + (2 * kMaxStages + 1) * 8 + kMaxStages * sizeof(StageInfo) + 64 + 2 * 256 * sizeof(float) + 16;
   const size_t budget = 110 * 1024;  // two CTAs per SM
   p.stages = std::max(2, std::min<int>(kMaxStages, static_cast<int>((budget - fixed) / stage_bytes)));
   const size_t smem_bytes = fixed + static_cast<size_t>(p.stages) * stage_bytes;

@@ -78,7 +78,7 @@ __device__ __forceinline__ void copy_rows(uint32_t dst_base, const uint8_t* src,
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kWgThreads, 1)
+__global__ void __maxnreg__(80)
 wgrad_tc_kernel(const __grid_constant__ WgParams p) {
   constexpr int ELEM = sizeof(T);
   constexpr int UMMA_K = 32 / ELEM;  // 16 pairs per MMA

@@ -50,8 +50,13 @@ def _order(kv, pair_mask, mask_argsort):
 
 
 def conv_forward(features, filters_krsc, pair_fwd, n_out, bias=None, out_dtype=None, pair_mask=None,
-                 mask_argsort=None, fp32_accum=None):
+                 mask_argsort=None, fp32_accum=None, epilogue=None):
     """out [n_out, K] = gather-GEMM of features [N, C] with filters [K, kv, C].
+
+    ``epilogue`` (not in the reference): ``(scale, shift, act, alpha)`` applied
+    while the rows are stored -- out = act((acc + bias) * scale + shift) with
+    fp32 ``scale``/``shift`` of shape [K] (or both None) and ``act`` one of the
+    ``_lib.SPC_ACT_*`` codes.
 
     ``fp32_accum`` is accepted for signature parity: 16-bit inputs always
     accumulate in fp32 here, which the reference treats as the accurate
@@ -77,11 +82,16 @@ def conv_forward(features, filters_krsc, pair_fwd, n_out, bias=None, out_dtype=N
                 b = b.to(feats.dtype)
         pf = pair_fwd if pair_fwd.is_contiguous() else pair_fwd.contiguous()
         order = _order(kv, pair_mask, mask_argsort)
+        scale = shift = None
+        act, alpha = _lib.SPC_ACT_NONE, 0.0
+        if epilogue is not None:
+            scale, shift, act, alpha = epilogue
         _lib.check(_lib.load().spc_conv_forward(
             _lib.ptr(feats), _lib.ptr(w), _lib.ptr(b), _lib.ptr(pf), _lib.ptr(_rowmajor(pair_fwd, feats)), _lib.ptr(order),
             _lib.ptr(out),
             feats.shape[0], n_out, c_in, k_out, kv, _lib.dtype_code(feats.dtype), _lib.dtype_code(out_dtype),
-            _precision(feats), GEMM_PATH, _lib.current_stream(dev)))
+            _precision(feats), GEMM_PATH, _lib.ptr(scale), _lib.ptr(shift), int(act), float(alpha),
+            _lib.current_stream(dev)))
     return out
 
 

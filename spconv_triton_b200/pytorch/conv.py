@@ -198,7 +198,7 @@ class SparseConvolutionBase:
                       bias: torch.Tensor | None, add_input: SparseConvTensor | None = None,
                       channel_scale: torch.Tensor | None = None, output_scale: float | None = None,
                       name: str | None = None, act_type: Activation = _NO_ACT, act_alpha: float = 0,
-                      act_beta: float = 0):
+                      act_beta: float = 0, bn_fold=None):
         if x.is_quantized and weight.is_quantized:
             raise NotImplementedError("int8 is not supported by spconv_triton")
         if x.features.shape[1] != self.in_channels:
@@ -263,7 +263,7 @@ class SparseConvolutionBase:
                     self.fp32_accum, bias_fused, act_alpha, act_beta, act_type,
                     1.0 if output_scale is None else output_scale, channel_scale,
                     output_add=add_input.features if add_input is not None else None, output_add_scale=0.0,
-                    output_dtype=weight.dtype if output_scale is None else None)
+                    output_dtype=weight.dtype if output_scale is None else None, _bn_fold=bn_fold)
         if bias_after is not None:
             out_features += bias_after
         if x.benchmark:
@@ -409,10 +409,27 @@ class SparseConvolution(SparseConvolutionBase, SparseModule):
             init.uniform_(self.bias, -bound, bound)
 
     # data-dependent shapes and raw CUDA launches: keep torch.compile out of here
+    def can_fold_epilogue(self) -> bool:
+        """True if an inference BatchNorm (and ReLU) that follows this layer can be
+        applied inside its GEMM kernel: evaluation mode, implicit-gemm algorithm,
+        a real convolution (not the 1x1 matrix-product shortcut), no activation of
+        its own."""
+        return (not self.training and not self.conv1x1 and self.algo != ConvAlgo.Native
+                and self.act_type == _NO_ACT)
+
     @torch.compiler.disable
-    def forward(self, x: SparseConvTensor, add_input: SparseConvTensor | None = None):
+    def forward(self, x: SparseConvTensor, add_input: SparseConvTensor | None = None, _fold=None):
+        """``_fold = (scale, shift, relu)`` is used by SparseSequential to hand the
+        layer a folded BatchNorm + ReLU (see modules.py)."""
+        act_type, bn_fold = self.act_type, None
+        if _fold is not None:
+            scale, shift, relu = _fold
+            bn_fold = (scale, shift)
+            if relu:
+                act_type = tv.gemm.Activation.ReLU
         return self._conv_forward(self.training, x, self.weight, self.bias, add_input, name=self.name,
-                                  act_type=self.act_type, act_alpha=self.act_alpha, act_beta=self.act_beta)
+                                  act_type=act_type, act_alpha=self.act_alpha, act_beta=self.act_beta,
+                                  bn_fold=bn_fold)
 
 
 def _leaf(name: str, ndim: int, flavour: str):

@@ -64,7 +64,14 @@ class SparseSequential(SparseModule):
         self.add_module(name, module)
 
     def forward(self, x):
-        for module in self._modules.values():
+        mods = list(self._modules.values())
+        i = 0
+        while i < len(mods):
+            module = mods[i]
+            fused = _try_fold_bn_relu(mods, i, x)
+            if fused is not None:
+                x, i = fused
+                continue
             if is_spconv_module(module):
                 x = module(x)
             elif isinstance(x, SparseConvTensor):
@@ -72,7 +79,59 @@ class SparseSequential(SparseModule):
                     x = x.replace_feature(module(x.features))
             else:
                 x = module(x)
+            i += 1
         return x
+
+
+def _folded_bn(bn: nn.BatchNorm1d):
+    """fp32 (scale, shift) with bn(x) == x * scale + shift in evaluation mode;
+    memoised on the module until one of its tensors changes."""
+    tensors = (bn.weight, bn.bias, bn.running_mean, bn.running_var)
+    key = tuple((t._version, t.data_ptr()) if t is not None else None for t in tensors) + (bn.eps,)
+    cached = getattr(bn, "_spc_folded", None)
+    if cached is not None and cached[0] == key:
+        return cached[1], cached[2]
+    with torch.no_grad():
+        scale = torch.rsqrt(bn.running_var.float() + bn.eps)
+        if bn.weight is not None:
+            scale = scale * bn.weight.float()
+        shift = -bn.running_mean.float() * scale
+        if bn.bias is not None:
+            shift = shift + bn.bias.float()
+        scale, shift = scale.contiguous(), shift.contiguous()
+    bn._spc_folded = (key, scale, shift)
+    return scale, shift
+
+
+def _try_fold_bn_relu(mods, i, x):
+    """In evaluation mode a sparse convolution followed by BatchNorm1d (and
+    optionally ReLU) runs as ONE kernel: the normalisation becomes a per-channel
+    scale and shift applied, with the ReLU, while the GEMM stores its rows.  This
+    removes two passes over the activations; the result differs from the
+    separate modules only by fp16 rounding order.  Switch:
+    ``spconv_triton_b200.constants.SPCONV_FOLD_BN_RELU``.  Returns
+    ``(new_x, next_index)`` or None when the pattern does not apply."""
+    from spconv_triton_b200 import constants
+
+    from .conv import SparseConvolution
+
+    if not constants.SPCONV_FOLD_BN_RELU or i + 1 >= len(mods) or not isinstance(x, SparseConvTensor):
+        return None
+    conv, bn = mods[i], mods[i + 1]
+    if not (isinstance(conv, SparseConvolution) and conv.can_fold_epilogue()):
+        return None
+    if not (type(bn) in (nn.BatchNorm1d, SparseBatchNorm) and not bn.training and bn.track_running_stats
+            and bn.running_mean is not None and bn.num_features == conv.out_channels):
+        return None
+    if not x.features.is_cuda or x.features.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        return None
+    if x.benchmark or x.indices.shape[0] == 0:
+        return None
+    relu = i + 2 < len(mods) and type(mods[i + 2]) in (nn.ReLU, SparseReLU)
+    scale, shift = _folded_bn(bn)
+    if scale.device != x.features.device:
+        return None
+    return conv(x, _fold=(scale, shift, relu)), i + 2 + int(relu)
 
 
 def assign_name_for_sparse_modules(module: nn.Module):

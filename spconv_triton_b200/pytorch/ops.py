@@ -65,6 +65,14 @@ def _apply_act_inplace(out: torch.Tensor, act_type, act_alpha: float, act_beta: 
     raise NotImplementedError(f"activation {name} not supported")
 
 
+def _act_code(act_type) -> int:
+    name = getattr(act_type, "name", "None_")
+    try:
+        return {"None_": 0, "ReLU": 1, "Sigmoid": 2, "LeakyReLU": 3}[name]
+    except KeyError:
+        raise NotImplementedError(f"activation {name} not supported") from None
+
+
 def _filters_krsc(filters: torch.Tensor):
     """[K, *ksize, C] -> contiguous [K, kv, C]."""
     return filters.reshape(filters.shape[0], -1, filters.shape[-1]).contiguous()
@@ -147,17 +155,20 @@ def implicit_gemm(features, filters, pair_fwd, pair_mask_fwd_splits, mask_argsor
                   bias: torch.Tensor | None = None, act_alpha: float = 0.0, act_beta: float = 0.0,
                   act_type=_NO_ACT, output_scale: float = 1.0, scale: torch.Tensor | None = None,
                   output_add: torch.Tensor | None = None, output_add_scale: float = 0.0,
-                  output_dtype: torch.dtype | None = None):
+                  output_dtype: torch.dtype | None = None, _bn_fold=None):
     """Implicit-gemm forward -> ``(out, mask_output_fwd, mask_width)``
-    (reference: ops.py:259-305)."""
+    (reference: ops.py:259-305).  The activation is applied inside the kernel's
+    store; ``_bn_fold = (scale, shift)`` (fp32 [K], not in the reference) folds
+    an inference BatchNorm in front of it."""
     if output_add is not None and features.dtype != torch.qint8:
         raise AssertionError("fused residual add only support int8")
     _reject_int8(features)
     features = features.contiguous()
     pm, ar = _single_split_mask(pair_mask_fwd_splits, mask_argsort_fwd_splits, masks)
+    scale, shift = _bn_fold if _bn_fold is not None else (None, None)
     out = _gemm.conv_forward(features, _filters_krsc(filters), pair_fwd, num_activate_out, bias=bias,
-                             out_dtype=output_dtype, pair_mask=pm, mask_argsort=ar, fp32_accum=fp32_accum)
-    _apply_act_inplace(out, act_type, act_alpha, act_beta)
+                             out_dtype=output_dtype, pair_mask=pm, mask_argsort=ar, fp32_accum=fp32_accum,
+                             epilogue=(scale, shift, _act_code(act_type), float(act_alpha)))
     return out, torch.Tensor(), -1
 
 

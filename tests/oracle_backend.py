@@ -41,9 +41,20 @@ def _native_pair_to_tables(pair, indice_pair_num, n_in, n_out, inverse, need_bwd
 
 
 def _conv_forward(features, w, pair_fwd, n_out, bias=None, out_dtype=None, pair_mask=None, mask_argsort=None,
-                  fp32_accum=None):
-    return of.conv_forward(features.detach(), w.detach(), pair_fwd, n_out, bias=None if bias is None else bias.detach(),
-                           out_dtype=out_dtype)
+                  fp32_accum=None, epilogue=None):
+    scale, shift, act, alpha = epilogue if epilogue is not None else (None, None, 0, 0.0)
+    out_dtype = out_dtype or features.dtype
+    out = of.conv_forward(features.detach(), w.detach(), pair_fwd, n_out, bias=None if bias is None else bias.detach(),
+                          out_dtype=torch.float64)
+    if scale is not None:
+        out = out * scale.double() + shift.double()
+    if act == 1:
+        out = torch.relu(out)
+    elif act == 2:
+        out = torch.sigmoid(out)
+    elif act == 3:
+        out = torch.nn.functional.leaky_relu(out, alpha)
+    return out.to(out_dtype)
 
 
 def _conv_backward_input(grad_out, w, pair_bwd, n_in, pair_mask=None, mask_argsort=None, fp32_accum=None):
