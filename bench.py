@@ -284,6 +284,108 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def blob_scene(seed, batch, n_per_sample, grid=256):
+    """Dense-ish random blobs (BASELINE configs[4]): union of Gaussian blobs in a
+    grid^3 volume, n_per_sample unique voxels per sample."""
+    rng = np.random.default_rng(seed)
+    rows = []
+    for b in range(batch):
+        pts = np.zeros((0, 3), dtype=np.int64)
+        while pts.shape[0] < n_per_sample:
+            centres = rng.integers(grid // 8, grid - grid // 8, size=(64, 3))
+            new = np.concatenate([c + np.rint(rng.standard_normal((12000, 3)) * grid / 24) for c in centres])
+            pts = np.unique(np.concatenate([pts, np.clip(new, 0, grid - 1).astype(np.int64)]), axis=0)
+        pts = pts[rng.permutation(pts.shape[0])[:n_per_sample]]
+        rows.append(np.concatenate([np.full((n_per_sample, 1), b), pts], 1))
+    return torch.from_numpy(np.concatenate(rows).astype(np.int32))
+
+
+def run_op_bench(args):
+    """Single-operator timings at the other BASELINE configurations (not the
+    headline line): ``--op pool`` = configs[4] SparseMaxPool3d k2 s2 and
+    SparseAvgPool3d k3 s1 at C = 256 fp16, 4 x 400k voxels in 256^3;
+    ``--op conv_s2`` = configs[1] SparseConv3d k3 s2 64 -> 128 fp16, 4 x 120k
+    voxels.  One JSON line per kernel with algorithmic GB/s (and TFLOP/s)."""
+    from spconv_triton_b200.pytorch._impl import gemm as G
+    from spconv_triton_b200.pytorch._impl import pairs as P
+    from spconv_triton_b200.pytorch._impl import pool as PL
+    from spconv_triton_b200.scenes import lidar_like_batch
+
+    dev = torch.device("cuda", 0)
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    def emit(name, ms, nbytes, flops=None, **extra):
+        line = {"op": name, "ms": ms, "algorithmic_GBps": nbytes / ms / 1e6, "hbm_frac": nbytes / ms / 1e6 / hbm_peak,
+                "peak_kind": peak_kind, **extra}
+        if flops:
+            line["TFLOPs"] = flops / ms / 1e9
+            line["tensor_frac"] = flops / ms / 1e9 / tensor_peak
+        print(json.dumps(line), flush=True)
+
+    iters = max(args.steps, 5)
+    if args.op == "pool":
+        batch, c = 4, 256
+        idx = blob_scene(7, batch, 400000)
+        if args.voxel_order == "sorted":   # the order every rulebook of this library emits its outputs in
+            key = ((idx[:, 0].long() * 256 + idx[:, 1]) * 256 + idx[:, 2]) * 256 + idx[:, 3]
+            idx = idx[torch.argsort(key)]
+        idx = idx.to(dev)
+        feats = torch.randn(idx.shape[0], c, device=dev).half()
+        for name, k, s in (("maxpool_k2s2", 2, 2), ("avgpool_k3s1", 3, 1)):
+            res = P.igemm_pairs(idx, batch, [256] * 3, [k] * 3, [s] * 3, [0] * 3, [1] * 3, [0] * 3, False, False, True, False)
+            pf, pb = res[2], res[3]
+            n_out, kv = pf.shape[1], pf.shape[0]
+            pairs = int((pf >= 0).sum())
+            fwd_bytes = pairs * c * 2 + n_out * c * 2 + kv * n_out * 4
+            if name.startswith("max"):
+                out = PL.maxpool_forward(feats, pf, n_out)
+                g = torch.randn_like(out)
+                emit(name + "_fwd", timed(lambda: PL.maxpool_forward(feats, pf, n_out), iters), fwd_bytes,
+                     voxels=int(idx.shape[0]), n_out=n_out, pairs=pairs, voxel_order=args.voxel_order)
+                bwd_bytes = idx.shape[0] * c * 2 * 2 + pairs * c * 2 * 2 + kv * idx.shape[0] * 4
+                emit(name + "_bwd", timed(lambda: PL.maxpool_backward(feats, out, g, pb), iters), bwd_bytes)
+            else:
+                out, cnt = PL.avgpool_forward(feats, pf, n_out)
+                g = torch.randn_like(out)
+                emit(name + "_fwd", timed(lambda: PL.avgpool_forward(feats, pf, n_out), iters), fwd_bytes + 4 * n_out,
+                     voxels=int(idx.shape[0]), n_out=n_out, pairs=pairs, voxel_order=args.voxel_order)
+                bwd_bytes = idx.shape[0] * c * 2 + pairs * (c * 2 + 4) + kv * idx.shape[0] * 4
+                emit(name + "_bwd", timed(lambda: PL.avgpool_backward(g, pb, cnt), iters), bwd_bytes)
+    else:
+        batch = 4
+        idx = torch.from_numpy(lidar_like_batch(100, batch, (120000, 120000), tuple(GRID))).to(dev)
+        n_in = idx.shape[0]
+        args_rb = (idx, batch, GRID, [3] * 3, [2] * 3, [1] * 3, [1] * 3, [0] * 3, False, False, True, False)
+        res = P.igemm_pairs(*args_rb)
+        out_inds, _, pf, pb, pmf, pmb, maf, mab, _ = res
+        n_out, kv = pf.shape[1], pf.shape[0]
+        pairs = int((pf >= 0).sum())
+        rb_bytes = n_in * 16 + n_out * 16 + kv * n_out * 4 + kv * n_in * 4 + 8 * n_out + 8 * n_in
+        emit("rulebook_k3s2", timed(lambda: P.igemm_pairs(*args_rb), iters), rb_bytes, voxels=n_in, n_out=n_out, pairs=pairs)
+        x = torch.randn(n_in, 64, device=dev).half()
+        w = (torch.randn(128, kv, 64, device=dev) * 0.02).half()
+        g = torch.randn(n_out, 128, device=dev).half()
+        flops = 2.0 * pairs * 64 * 128
+        emit("conv_fwd_64_128", timed(lambda: G.conv_forward(x, w, pf, n_out, pair_mask=pmf[0][:, 0], mask_argsort=maf[0]), iters),
+             pairs * 64 * 2 + n_out * 128 * 2 + kv * n_out * 4, flops)
+        emit("conv_dgrad_64_128", timed(lambda: G.conv_backward_input(g, w, pb, n_in, pair_mask=pmb[0][:, 0], mask_argsort=mab[0]), iters),
+             pairs * 128 * 2 + n_in * 64 * 2 + kv * n_in * 4, flops)
+        emit("conv_wgrad_64_128", timed(lambda: G.conv_backward_weight(x, g, pf, (128, kv, 64)), iters),
+             pairs * (64 + 128) * 2 + kv * n_out * 4, flops)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -291,7 +393,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-baseline-seconds", type=float, default=20.0)
+    ap.add_argument("--op", default=None, choices=["pool", "conv_s2"],
+                    help="single-operator timings at the other configurations instead of the headline benchmark")
+    ap.add_argument("--voxel-order", default="random", choices=["random", "sorted"],
+                    help="--op pool: input voxel order (random = as a voxeliser emits them, sorted = as a previous layer's rulebook emits them)")
     args = ap.parse_args()
+    if args.op is not None:
+        run_op_bench(args)
+        return
     if args.impl == "reference":
         args.steps = min(args.steps, 8)
         args.warmup = min(args.warmup, 1)

@@ -1,9 +1,9 @@
 // Sparse max / average pooling over implicit-gemm pair tables.
 //
 // HBM-bound gather-reduce: one thread owns one 16-byte channel vector of one
-// output row, walks the kv table entries of that row (pair[k*n + row] is
-// shared by the threads of the row and served from L1), loads the gathered
-// rows with 16-byte accesses and writes the result with one 16-byte store.
+// output row, walks the entries of that row that are present (compacted per
+// CTA in shared memory), loads the gathered rows with 16-byte accesses, four
+// independent rows in flight, and writes the result with one 16-byte store.
 // Algorithmic bytes per output row: kv*4 (table) + pairs*C*e (gathered
 // rows) + C*e (store).
 //
@@ -39,103 +39,227 @@ __device__ __forceinline__ void store_pack(T* p, const Pack<T, VEC>& v) {
   *reinterpret_cast<Pack<T, VEC>*>(p) = v;
 }
 
-enum PoolOp { kMaxFwd, kAvgFwd };
+enum PoolOp { kMaxFwd = 0, kAvgFwd = 1, kAvgBwd = 2, kMaxBwd = 3 };
+// Independent 16-byte gathers one thread keeps in flight, and 16-byte vectors of
+// a row one thread owns.  Max backward reads two rows per table entry and keeps
+// its own row in registers, so it runs with half of each (measured best on B200:
+// 116 registers and 2 CTAs per SM for the others, 80 and 3 for max backward).
+template <int OP> struct PoolTune { static constexpr int in_flight = 8, max_u = 4; };
+template <> struct PoolTune<3> { static constexpr int in_flight = 2, max_u = 2; };
+constexpr int kChunk = 32;    // table entries of one row compacted per pass (one per lane)
+constexpr int kMaxRows = 64;  // rows per CTA
 
-template <typename T, int VEC, int OP>
-__global__ void __launch_bounds__(256)
-pool_fwd_kernel(const T* __restrict__ feats, const int32_t* __restrict__ pairs, T* __restrict__ out,
-                int32_t* __restrict__ count, long long n_out, int channels, int kv) {
+// What the four operators do with the rows their table names:
+//   kMaxFwd : dst[row] = max(0, src[j])                        table = pair_fwd
+//   kAvgFwd : dst[row] = sum(src[j]) / max(1, #j), aux_out=#j  table = pair_fwd
+//   kMaxBwd : dst[row] = sum(src[o] where own[row]==ref[o])    table = pair_bwd, src = grad_out, ref = pooled
+//   kAvgBwd : dst[row] = sum(src[o] * aux_in[o])               table = pair_bwd, src = grad_out
+//
+// One thread owns U 16-byte channel vectors of one row, spaced so that the
+// threads of a row read contiguous 16*nt bytes per load; a random 512-byte
+// row needs several loads in flight per thread to cover HBM latency, and the
+// table walk is paid once per U vectors.
+template <typename T, int VEC, int U, int OP>
+struct PoolRow {
   using A = typename PoolAcc<T>::type;
-  const int tpr = channels / VEC;
-  const long long e = blockIdx.x * 256ll + threadIdx.x;
-  const long long row = e / tpr;
-  if (row >= n_out) return;
-  const int c0 = static_cast<int>(e % tpr) * VEC;
-  A acc[VEC];
+  A acc[U][VEC];
+  Pack<T, VEC> f[U];
+  int total = 0;
+
+  __device__ __forceinline__ void begin(const T* own, long long row, int channels, int c0, int cstep) {
 #pragma unroll
-  for (int u = 0; u < VEC; ++u) acc[u] = A(0);
-  int cnt = 0;
-  for (int k = 0; k < kv; ++k) {
-    const int j = __ldg(&pairs[static_cast<long long>(k) * n_out + row]);
-    if (j < 0) continue;
-    const Pack<T, VEC> p = load_pack<T, VEC>(feats + static_cast<long long>(j) * channels + c0);
-    ++cnt;
+    for (int u = 0; u < U; ++u) {
 #pragma unroll
-    for (int u = 0; u < VEC; ++u) {
-      const A v = up<T>(p.v[u]);
-      if (OP == kMaxFwd) acc[u] = v > acc[u] ? v : acc[u];
-      else acc[u] += v;
+      for (int v = 0; v < VEC; ++v) acc[u][v] = A(0);
+      if (OP == kMaxBwd) f[u] = load_pack<T, VEC>(own + row * channels + c0 + u * cstep);
     }
   }
-  Pack<T, VEC> o;
-  if (OP == kAvgFwd) {
-    const A d = static_cast<A>(cnt > 1 ? cnt : 1);
+
+  // B rows at once (entries < 0 are skipped); B * U loads are issued before the first use.
+  template <int B>
+  __device__ __forceinline__ void gather(const int (&j)[B], const T* src, const T* ref, const int32_t* aux_in,
+                                         int channels, int c0, int cstep) {
+    Pack<T, VEC> pk[B][U], rk[B][U];
+    A w[B];
 #pragma unroll
-    for (int u = 0; u < VEC; ++u) o.v[u] = down<T>(acc[u] / d);
-    if (count != nullptr && c0 == 0) count[row] = cnt;
-  } else {
+    for (int b = 0; b < B; ++b) {
+      if (j[b] < 0) continue;
+      const long long off = static_cast<long long>(j[b]) * channels + c0;
 #pragma unroll
-    for (int u = 0; u < VEC; ++u) o.v[u] = down<T>(acc[u]);
+      for (int u = 0; u < U; ++u) {
+        pk[b][u] = load_pack<T, VEC>(src + off + u * cstep);
+        if (OP == kMaxBwd) rk[b][u] = load_pack<T, VEC>(ref + off + u * cstep);
+      }
+      if (OP == kAvgBwd) w[b] = static_cast<A>(__ldg(&aux_in[j[b]]));
+    }
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      if (j[b] < 0) continue;
+      ++total;
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          const A x = up<T>(pk[b][u].v[v]);
+          if (OP == kMaxFwd) acc[u][v] = x > acc[u][v] ? x : acc[u][v];
+          else if (OP == kAvgFwd) acc[u][v] += x;
+          else if (OP == kMaxBwd) { if (up<T>(rk[b][u].v[v]) == up<T>(f[u].v[v])) acc[u][v] += x; }
+          else acc[u][v] += x * w[b];
+        }
+    }
   }
-  store_pack<T, VEC>(out + row * channels + c0, o);
+
+  __device__ __forceinline__ void finish(T* dst, int32_t* aux_out, long long row, int channels, int c0,
+                                         int cstep) {
+    const A d = static_cast<A>(total > 1 ? total : 1);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      Pack<T, VEC> o;
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) o.v[v] = down<T>(OP == kAvgFwd ? acc[u][v] / d : acc[u][v]);
+      store_pack<T, VEC>(dst + row * channels + c0 + u * cstep, o);
+    }
+    if (OP == kAvgFwd && aux_out != nullptr && c0 == 0) aux_out[row] = total;
+  }
+};
+
+// Launch geometry of the shared-memory kernel: `nt` threads per row (U vectors
+// each), of which a CTA holds `tpb` (grid.y covers the rest), `rpb` rows per CTA.
+struct PoolGeom { int nt, tpb, rpb; };
+
+// Rows whose nt threads are a power of two between 4 and 32 (every channel count
+// from 128 bytes to 2 KiB that is a multiple of 64 bytes): the nt lanes of a row
+// read up to 32 table entries of the row with ONE round of loads (lane l takes
+// entries l, l+nt, ...), a ballot per load builds the row's 32-bit presence
+// mask, and the lanes then walk only the set bits, fetching each index from its
+// owner lane by shuffle.  No shared memory, no CTA barrier.
+// Each warp takes kGroupIters consecutive row groups and loads the table entries
+// of the next group before it gathers for the current one, so a table latency is
+// exposed once per warp and gathers are in flight the rest of the time.
+constexpr int kGroupMaxE = 8;   // table entries per lane per round (32 / nt)
+constexpr int kGroupIters = 8;  // row groups per warp
+
+template <typename T, int VEC, int U, int OP>
+__global__ void __launch_bounds__(256)
+pool_group_kernel(const T* __restrict__ src, const T* __restrict__ own, const T* __restrict__ ref,
+                  const int32_t* __restrict__ table, const int32_t* __restrict__ aux_in, T* __restrict__ dst,
+                  int32_t* __restrict__ aux_out, long long n_rows, int channels, int kv, int lg_nt) {
+  constexpr int B = PoolTune<OP>::in_flight / U > 0 ? PoolTune<OP>::in_flight / U : 1;
+  constexpr unsigned kFull = 0xffffffffu;
+  const int nt = 1 << lg_nt;
+  const int lane = threadIdx.x & 31;
+  const int kl = lane & (nt - 1), gbase = lane - kl;
+  const unsigned gmask = nt == 32 ? kFull : ((1u << nt) - 1u);
+  const int c0 = kl * VEC, cstep = nt * VEC;
+  const int per_lane = 32 >> lg_nt;  // table entries per lane per round == rows per warp
+  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long row_first = warp_id * kGroupIters * per_lane + (lane >> lg_nt);
+
+  auto load_entries = [&](long long row, int k0, int (&v)[kGroupMaxE]) {
+#pragma unroll
+    for (int e = 0; e < kGroupMaxE; ++e) {
+      const int k = k0 + e * nt + kl;
+      v[e] = (row < n_rows && e < per_lane && k < kv) ? __ldg(&table[static_cast<long long>(k) * n_rows + row]) : -1;
+    }
+  };
+
+  int vn[kGroupMaxE];
+  load_entries(row_first, 0, vn);
+#pragma unroll 1
+  for (int it = 0; it < kGroupIters; ++it) {
+    const long long row = row_first + static_cast<long long>(it) * per_lane;
+    if (row - (lane >> lg_nt) >= n_rows) break;  // warp-uniform: the whole group is past the end
+    const bool live = row < n_rows;
+    int v[kGroupMaxE];
+#pragma unroll
+    for (int e = 0; e < kGroupMaxE; ++e) v[e] = vn[e];
+    if (it + 1 < kGroupIters) load_entries(row + per_lane, 0, vn);
+
+    PoolRow<T, VEC, U, OP> pr;
+    if (live) pr.begin(own, row, channels, c0, cstep);
+    for (int k0 = 0; k0 < kv; k0 += 32) {
+      if (k0 != 0) load_entries(row, k0, v);
+      unsigned gm = 0;
+#pragma unroll
+      for (int e = 0; e < kGroupMaxE; ++e) {
+        if (e < per_lane) {  // warp-uniform
+          const unsigned m = __ballot_sync(kFull, v[e] >= 0);
+          gm |= ((m >> gbase) & gmask) << (e * nt);
+        }
+      }
+      while (__any_sync(kFull, gm != 0)) {
+        int j[B];
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const int p = gm ? __ffs(gm) - 1 : 0;
+          const int e = p >> lg_nt;
+          int mine = v[0];
+#pragma unroll
+          for (int q = 1; q < kGroupMaxE; ++q) mine = e == q ? v[q] : mine;
+          const int got = __shfl_sync(kFull, mine, gbase + (p & (nt - 1)));
+          j[b] = gm ? got : -1;
+          gm &= gm - 1;
+        }
+        pr.template gather<B>(j, src, ref, aux_in, channels, c0, cstep);
+      }
+    }
+    if (live) pr.finish(dst, aux_out, row, channels, c0, cstep);
+  }
 }
 
-template <typename T, int VEC>
+// Every other channel count.  Tables are mostly -1 (a 3^3 stride-1 pool over a
+// LiDAR scene has about 3 of 27 entries present), so walking them per thread costs
+// far more instructions than the gathers.  The CTA stages the [kv, rpb] tile of the
+// table with coalesced loads, one warp per row compacts the entries that are
+// present with a ballot (order of k preserved, so sums are formed in the same
+// order as a plain walk), and every thread then reads only the compacted list.
+template <typename T, int VEC, int U, int OP>
 __global__ void __launch_bounds__(256)
-maxpool_bwd_kernel(const T* __restrict__ feats, const T* __restrict__ outf, const T* __restrict__ gout,
-                   const int32_t* __restrict__ pair_bwd, T* __restrict__ din, long long n_in,
-                   int channels, int kv) {
-  using A = typename PoolAcc<T>::type;
-  const int tpr = channels / VEC;
-  const long long e = blockIdx.x * 256ll + threadIdx.x;
-  const long long row = e / tpr;
-  if (row >= n_in) return;
-  const int c0 = static_cast<int>(e % tpr) * VEC;
-  const Pack<T, VEC> f = load_pack<T, VEC>(feats + row * channels + c0);
-  A acc[VEC];
-#pragma unroll
-  for (int u = 0; u < VEC; ++u) acc[u] = A(0);
-  for (int k = 0; k < kv; ++k) {
-    const int o = __ldg(&pair_bwd[static_cast<long long>(k) * n_in + row]);
-    if (o < 0) continue;
-    const Pack<T, VEC> ov = load_pack<T, VEC>(outf + static_cast<long long>(o) * channels + c0);
-    const Pack<T, VEC> gv = load_pack<T, VEC>(gout + static_cast<long long>(o) * channels + c0);
-#pragma unroll
-    for (int u = 0; u < VEC; ++u)
-      if (up<T>(ov.v[u]) == up<T>(f.v[u])) acc[u] += up<T>(gv.v[u]);
-  }
-  Pack<T, VEC> r;
-#pragma unroll
-  for (int u = 0; u < VEC; ++u) r.v[u] = down<T>(acc[u]);
-  store_pack<T, VEC>(din + row * channels + c0, r);
-}
+pool_compact_kernel(const T* __restrict__ src, const T* __restrict__ own, const T* __restrict__ ref,
+                    const int32_t* __restrict__ table, const int32_t* __restrict__ aux_in, T* __restrict__ dst,
+                    int32_t* __restrict__ aux_out, long long n_rows, int channels, int kv, PoolGeom g) {
+  constexpr int B = PoolTune<OP>::in_flight / U > 0 ? PoolTune<OP>::in_flight / U : 1;
+  __shared__ int32_t tab[kChunk][kMaxRows + 1];
+  __shared__ int32_t lst[kMaxRows][kChunk];
+  __shared__ int32_t cnt[kMaxRows];
+  const int t = threadIdx.x, nthr = blockDim.x;
+  const int lane = t & 31, warp = t >> 5, nwarps = nthr >> 5;
+  const long long row0 = static_cast<long long>(blockIdx.x) * g.rpb;
+  const int rl = t / g.tpb;
+  const int ct = t - rl * g.tpb + static_cast<int>(blockIdx.y) * g.tpb;
+  const long long row = row0 + rl;
+  const bool live = rl < g.rpb && row < n_rows && ct < g.nt;
+  const int c0 = ct * VEC, cstep = g.nt * VEC;
 
-template <typename T, int VEC>
-__global__ void __launch_bounds__(256)
-avgpool_bwd_kernel(const T* __restrict__ gout, const int32_t* __restrict__ pair_bwd,
-                   const int32_t* __restrict__ count, T* __restrict__ din, long long n_in, int channels,
-                   int kv) {
-  using A = typename PoolAcc<T>::type;
-  const int tpr = channels / VEC;
-  const long long e = blockIdx.x * 256ll + threadIdx.x;
-  const long long row = e / tpr;
-  if (row >= n_in) return;
-  const int c0 = static_cast<int>(e % tpr) * VEC;
-  A acc[VEC];
+  PoolRow<T, VEC, U, OP> pr;
+  if (live) pr.begin(own, row, channels, c0, cstep);
+
+  for (int k0 = 0; k0 < kv; k0 += kChunk) {
+    const int kc = min(kChunk, kv - k0);
+    if (k0 != 0) __syncthreads();
+    for (int i = t; i < kc * g.rpb; i += nthr) {
+      const int k = i / g.rpb, r = i - k * g.rpb;
+      const long long rr = row0 + r;
+      tab[k][r] = rr < n_rows ? __ldg(&table[static_cast<long long>(k0 + k) * n_rows + rr]) : -1;
+    }
+    __syncthreads();
+    for (int r = warp; r < g.rpb; r += nwarps) {
+      const int v = lane < kc ? tab[lane][r] : -1;
+      const unsigned m = __ballot_sync(0xffffffffu, v >= 0);
+      if (v >= 0) lst[r][__popc(m & ((1u << lane) - 1u))] = v;
+      if (lane == 0) cnt[r] = __popc(m);
+    }
+    __syncthreads();
+    if (!live) continue;
+    const int n = cnt[rl];
+    for (int i = 0; i < n; i += B) {
+      int j[B];
 #pragma unroll
-  for (int u = 0; u < VEC; ++u) acc[u] = A(0);
-  for (int k = 0; k < kv; ++k) {
-    const int o = __ldg(&pair_bwd[static_cast<long long>(k) * n_in + row]);
-    if (o < 0) continue;
-    const A cnt = static_cast<A>(__ldg(&count[o]));
-    const Pack<T, VEC> gv = load_pack<T, VEC>(gout + static_cast<long long>(o) * channels + c0);
-#pragma unroll
-    for (int u = 0; u < VEC; ++u) acc[u] += up<T>(gv.v[u]) * cnt;
+      for (int b = 0; b < B; ++b) j[b] = i + b < n ? lst[rl][i + b] : -1;
+      pr.template gather<B>(j, src, ref, aux_in, channels, c0, cstep);
+    }
   }
-  Pack<T, VEC> r;
-#pragma unroll
-  for (int u = 0; u < VEC; ++u) r.v[u] = down<T>(acc[u]);
-  store_pack<T, VEC>(din + row * channels + c0, r);
+  if (live) pr.finish(dst, aux_out, row, channels, c0, cstep);
 }
 
 template <typename T>
@@ -146,50 +270,51 @@ int vec_for(int channels, const void* a, const void* b, const void* c = nullptr,
   return 1;
 }
 
-inline unsigned grid_for(long long rows, int tpr) {
-  return static_cast<unsigned>(ceil_div(std::max<long long>(rows * tpr, 1), 256));
+template <typename T, int VEC, int U, int OP>
+void pool_launch_u(const T* src, const T* own, const T* ref, const int32_t* table, const int32_t* aux_in, T* dst,
+                   int32_t* aux_out, int64_t n_rows, int channels, int kv, cudaStream_t st) {
+  PoolGeom g;
+  g.nt = channels / (VEC * U);
+  g.tpb = std::min(g.nt, 256);
+  g.rpb = std::min(kMaxRows, std::max(1, 256 / g.tpb));
+  const int threads = static_cast<int>(ceil_div(static_cast<long long>(g.tpb) * g.rpb, 32) * 32);
+  const dim3 grid(static_cast<unsigned>(ceil_div(static_cast<long long>(n_rows), g.rpb)),
+                  static_cast<unsigned>(ceil_div(g.nt, g.tpb)));
+  if (g.nt >= 4 && g.nt <= 32 && (g.nt & (g.nt - 1)) == 0) {
+    int lg = 0;
+    while ((1 << lg) < g.nt) ++lg;
+    const long long warps = ceil_div(static_cast<long long>(n_rows), (32 >> lg) * kGroupIters);
+    pool_group_kernel<T, VEC, U, OP><<<static_cast<unsigned>(ceil_div(warps, 8)), 256, 0, st>>>(
+        src, own, ref, table, aux_in, dst, aux_out, n_rows, channels, kv, lg);
+  } else {
+    pool_compact_kernel<T, VEC, U, OP><<<grid, threads, 0, st>>>(src, own, ref, table, aux_in, dst, aux_out,
+                                                                n_rows, channels, kv, g);
+  }
 }
 
 template <typename T, int OP>
-int pool_fwd(const void* feats, const int32_t* pairs, void* out, int32_t* count, int64_t n_out, int channels,
-             int kv, cudaStream_t st) {
+int pool_launch(const void* src_, const void* own_, const void* ref_, const int32_t* table,
+                const int32_t* aux_in, void* dst_, int32_t* aux_out, int64_t n_rows, int channels, int kv,
+                cudaStream_t st) {
   constexpr int full = 16 / sizeof(T);
-  if (vec_for<T>(channels, feats, out) == full)
-    pool_fwd_kernel<T, full, OP><<<grid_for(n_out, channels / full), 256, 0, st>>>(
-        static_cast<const T*>(feats), pairs, static_cast<T*>(out), count, n_out, channels, kv);
-  else
-    pool_fwd_kernel<T, 1, OP><<<grid_for(n_out, channels), 256, 0, st>>>(
-        static_cast<const T*>(feats), pairs, static_cast<T*>(out), count, n_out, channels, kv);
-  SPC_LAUNCH_OK();
-  return SPC_OK;
-}
-
-template <typename T>
-int maxpool_bwd(const void* feats, const void* outf, const void* gout, const int32_t* pb, void* din,
-                int64_t n_in, int channels, int kv, cudaStream_t st) {
-  constexpr int full = 16 / sizeof(T);
-  if (vec_for<T>(channels, feats, outf, gout, din) == full)
-    maxpool_bwd_kernel<T, full><<<grid_for(n_in, channels / full), 256, 0, st>>>(
-        static_cast<const T*>(feats), static_cast<const T*>(outf), static_cast<const T*>(gout), pb,
-        static_cast<T*>(din), n_in, channels, kv);
-  else
-    maxpool_bwd_kernel<T, 1><<<grid_for(n_in, channels), 256, 0, st>>>(
-        static_cast<const T*>(feats), static_cast<const T*>(outf), static_cast<const T*>(gout), pb,
-        static_cast<T*>(din), n_in, channels, kv);
-  SPC_LAUNCH_OK();
-  return SPC_OK;
-}
-
-template <typename T>
-int avgpool_bwd(const void* gout, const int32_t* pb, const int32_t* count, void* din, int64_t n_in,
-                int channels, int kv, cudaStream_t st) {
-  constexpr int full = 16 / sizeof(T);
-  if (vec_for<T>(channels, gout, din) == full)
-    avgpool_bwd_kernel<T, full><<<grid_for(n_in, channels / full), 256, 0, st>>>(
-        static_cast<const T*>(gout), pb, count, static_cast<T*>(din), n_in, channels, kv);
-  else
-    avgpool_bwd_kernel<T, 1><<<grid_for(n_in, channels), 256, 0, st>>>(
-        static_cast<const T*>(gout), pb, count, static_cast<T*>(din), n_in, channels, kv);
+  const T* src = static_cast<const T*>(src_);
+  const T* own = static_cast<const T*>(own_);
+  const T* ref = static_cast<const T*>(ref_);
+  T* dst = static_cast<T*>(dst_);
+  if (vec_for<T>(channels, src_, own_, ref_, dst_) != full) {
+    pool_launch_u<T, 1, 1, OP>(src, own, ref, table, aux_in, dst, aux_out, n_rows, channels, kv, st);
+  } else {
+    // most vectors per thread that still leave a row at least 4 threads (the warp-group kernel)
+    const int tpr = channels / full;
+    int u = PoolTune<OP>::max_u;
+    while (u > 1 && (tpr % u != 0 || tpr / u < 4)) u /= 2;
+    if (u == 4)
+      pool_launch_u<T, full, 4, OP>(src, own, ref, table, aux_in, dst, aux_out, n_rows, channels, kv, st);
+    else if (u == 2)
+      pool_launch_u<T, full, 2, OP>(src, own, ref, table, aux_in, dst, aux_out, n_rows, channels, kv, st);
+    else
+      pool_launch_u<T, full, 1, OP>(src, own, ref, table, aux_in, dst, aux_out, n_rows, channels, kv, st);
+  }
   SPC_LAUNCH_OK();
   return SPC_OK;
 }
@@ -218,7 +343,7 @@ extern "C" int spc_maxpool_forward(const void* features, const int32_t* pair_fwd
     return fail(SPC_ERR_INVALID_ARGUMENT, "maxpool_forward: bad arguments");
   if (n_out == 0) return SPC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  SPC_POOL_DISPATCH(dtype, (pool_fwd<T, kMaxFwd>(features, pair_fwd, out, nullptr, n_out, channels, kv, st)));
+  SPC_POOL_DISPATCH(dtype, (pool_launch<T, kMaxFwd>(features, nullptr, nullptr, pair_fwd, nullptr, out, nullptr, n_out, channels, kv, st)));
 }
 
 extern "C" int spc_avgpool_forward(const void* features, const int32_t* pair_fwd, void* out, int32_t* count,
@@ -227,7 +352,7 @@ extern "C" int spc_avgpool_forward(const void* features, const int32_t* pair_fwd
     return fail(SPC_ERR_INVALID_ARGUMENT, "avgpool_forward: bad arguments");
   if (n_out == 0) return SPC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  SPC_POOL_DISPATCH(dtype, (pool_fwd<T, kAvgFwd>(features, pair_fwd, out, count, n_out, channels, kv, st)));
+  SPC_POOL_DISPATCH(dtype, (pool_launch<T, kAvgFwd>(features, nullptr, nullptr, pair_fwd, nullptr, out, count, n_out, channels, kv, st)));
 }
 
 extern "C" int spc_maxpool_backward(const void* features, const void* out_features, const void* grad_out,
@@ -237,7 +362,7 @@ extern "C" int spc_maxpool_backward(const void* features, const void* out_featur
     return fail(SPC_ERR_INVALID_ARGUMENT, "maxpool_backward: bad arguments");
   if (n_in == 0) return SPC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  SPC_POOL_DISPATCH(dtype, (maxpool_bwd<T>(features, out_features, grad_out, pair_bwd, din, n_in, channels, kv, st)));
+  SPC_POOL_DISPATCH(dtype, (pool_launch<T, kMaxBwd>(grad_out, features, out_features, pair_bwd, nullptr, din, nullptr, n_in, channels, kv, st)));
 }
 
 extern "C" int spc_avgpool_backward(const void* grad_out, const int32_t* pair_bwd, const int32_t* count,
@@ -246,5 +371,5 @@ extern "C" int spc_avgpool_backward(const void* grad_out, const int32_t* pair_bw
     return fail(SPC_ERR_INVALID_ARGUMENT, "avgpool_backward: bad arguments");
   if (n_in == 0) return SPC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  SPC_POOL_DISPATCH(dtype, (avgpool_bwd<T>(grad_out, pair_bwd, count, din, n_in, channels, kv, st)));
+  SPC_POOL_DISPATCH(dtype, (pool_launch<T, kAvgBwd>(grad_out, nullptr, nullptr, pair_bwd, count, din, nullptr, n_in, channels, kv, st)));
 }

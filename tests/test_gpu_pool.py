@@ -41,12 +41,19 @@ def test_matches_reference_vectors(ref_ops, name):
     assert rel_err(to_np(din.double()), g("din").double().numpy()) <= TOL[dt]
 
 
-@pytest.mark.parametrize("dtype,channels", [(torch.float16, 64), (torch.float32, 32), (torch.float16, 20),
-                                            (torch.bfloat16, 16), (torch.float64, 6), (torch.float32, 7)])
-def test_matches_oracle(dtype, channels):
-    shape, batch, n = [32, 48, 40], 3, 40000
+# Channel counts chosen to reach every launch shape: rows of 4, 8, 16 and 32
+# threads with 1, 2 or 4 vectors each (the warp-group kernel), and rows that are
+# too narrow, not a power of two, or unaligned (the shared-memory kernel).
+# ksize 4 stride 1 has 64 offsets: more than one 32-entry round of the table.
+@pytest.mark.parametrize("dtype,channels,ksize,stride", [
+    (torch.float16, 64, 2, 2), (torch.float32, 32, 2, 2), (torch.float16, 20, 2, 2), (torch.bfloat16, 16, 2, 2),
+    (torch.float64, 6, 2, 2), (torch.float32, 7, 2, 2), (torch.float16, 256, 3, 1), (torch.float16, 512, 2, 2),
+    (torch.bfloat16, 1024, 2, 2), (torch.float16, 32, 3, 1), (torch.float32, 48, 3, 2), (torch.float16, 96, 4, 1),
+    (torch.float32, 20, 4, 1), (torch.float64, 8, 3, 1), (torch.float16, 4096, 2, 2)])
+def test_matches_oracle(dtype, channels, ksize, stride):
+    shape, batch, n = [32, 48, 40], 3, (40000 if channels <= 256 else 6000)
     idx_np = unique_coords(31, n, batch, shape)
-    res = orb.igemm_pairs(idx_np, batch, shape, [2] * 3, [2] * 3, [0] * 3, [1] * 3, [0] * 3, False, False, True, False)
+    res = orb.igemm_pairs(idx_np, batch, shape, [ksize] * 3, [stride] * 3, [0] * 3, [1] * 3, [0] * 3, False, False, True, False)
     pf, pb = res[2], res[3]
     n_out = pf.shape[1]
     gen = torch.Generator().manual_seed(5)
