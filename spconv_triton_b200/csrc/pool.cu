@@ -39,6 +39,58 @@ __device__ __forceinline__ void store_pack(T* p, const Pack<T, VEC>& v) {
   *reinterpret_cast<Pack<T, VEC>*>(p) = v;
 }
 
+// Whole-vector conversions.  The 16-bit types convert two lanes per instruction
+// on the FMA pipe; one-lane conversions issue on the quarter-rate XU pipe, which
+// made the gather-reduce instruction-bound.
+template <typename T, int VEC>
+__device__ __forceinline__ void unpack(const Pack<T, VEC>& p, typename PoolAcc<T>::type (&out)[VEC]) {
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) out[v] = up<T>(p.v[v]);
+}
+template <>
+__device__ __forceinline__ void unpack<__half, 8>(const Pack<__half, 8>& p, float (&out)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(p.v);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float2 f = __half22float2(h[q]);
+    out[2 * q] = f.x;
+    out[2 * q + 1] = f.y;
+  }
+}
+template <>
+__device__ __forceinline__ void unpack<__nv_bfloat16, 8>(const Pack<__nv_bfloat16, 8>& p, float (&out)[8]) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(p.v);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {  // bf16 is the upper half of an fp32
+    out[2 * q] = __uint_as_float(w[q] << 16);
+    out[2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u);
+  }
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ Pack<T, VEC> pack(const typename PoolAcc<T>::type (&in)[VEC]) {
+  Pack<T, VEC> o;
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) o.v[v] = down<T>(in[v]);
+  return o;
+}
+template <>
+__device__ __forceinline__ Pack<__half, 8> pack<__half, 8>(const float (&in)[8]) {
+  Pack<__half, 8> o;
+  __half2* h = reinterpret_cast<__half2*>(o.v);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(in[2 * q], in[2 * q + 1]);
+  return o;
+}
+template <>
+__device__ __forceinline__ Pack<__nv_bfloat16, 8> pack<__nv_bfloat16, 8>(const float (&in)[8]) {
+  Pack<__nv_bfloat16, 8> o;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(o.v);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(in[2 * q], in[2 * q + 1]);
+  return o;
+}
+
 enum PoolOp { kMaxFwd = 0, kAvgFwd = 1, kAvgBwd = 2, kMaxBwd = 3 };
 // Independent 16-byte gathers one thread keeps in flight, and 16-byte vectors of
 // a row one thread owns.  Max backward reads two rows per table entry and keeps
@@ -97,15 +149,21 @@ struct PoolRow {
       if (j[b] < 0) continue;
       ++total;
 #pragma unroll
-      for (int u = 0; u < U; ++u)
+      for (int u = 0; u < U; ++u) {
+        A x[VEC], r[VEC], o[VEC];
+        unpack<T, VEC>(pk[b][u], x);
+        if (OP == kMaxBwd) {
+          unpack<T, VEC>(rk[b][u], r);
+          unpack<T, VEC>(f[u], o);
+        }
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
-          const A x = up<T>(pk[b][u].v[v]);
-          if (OP == kMaxFwd) acc[u][v] = x > acc[u][v] ? x : acc[u][v];
-          else if (OP == kAvgFwd) acc[u][v] += x;
-          else if (OP == kMaxBwd) { if (up<T>(rk[b][u].v[v]) == up<T>(f[u].v[v])) acc[u][v] += x; }
-          else acc[u][v] += x * w[b];
+          if (OP == kMaxFwd) acc[u][v] = x[v] > acc[u][v] ? x[v] : acc[u][v];
+          else if (OP == kAvgFwd) acc[u][v] += x[v];
+          else if (OP == kMaxBwd) { if (r[v] == o[v]) acc[u][v] += x[v]; }
+          else acc[u][v] += x[v] * w[b];
         }
+      }
     }
   }
 
@@ -114,10 +172,11 @@ struct PoolRow {
     const A d = static_cast<A>(total > 1 ? total : 1);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      Pack<T, VEC> o;
+      if (OP == kAvgFwd) {
 #pragma unroll
-      for (int v = 0; v < VEC; ++v) o.v[v] = down<T>(OP == kAvgFwd ? acc[u][v] / d : acc[u][v]);
-      store_pack<T, VEC>(dst + row * channels + c0 + u * cstep, o);
+        for (int v = 0; v < VEC; ++v) acc[u][v] /= d;
+      }
+      store_pack<T, VEC>(dst + row * channels + c0 + u * cstep, pack<T, VEC>(acc[u]));
     }
     if (OP == kAvgFwd && aux_out != nullptr && c0 == 0) aux_out[row] = total;
   }
