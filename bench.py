@@ -490,7 +490,32 @@ def main():
     voxels = sum(voxels_per_scene[s % N_SCENES] for s in range(args.steps))
     total_voxels = sum_over_ranks(voxels)
     value = total_voxels / (dev_ms * 1e-3) / 1e6
+    gemm_overlapped = prof.summarize()
+
+    # ---- the dominant kernel alone: the same steps once more with the rulebook run-ahead off,
+    # so that no rulebook kernel shares the SMs with the GEMM launches the events bracket ------
+    from spconv_triton_b200 import constants as spc_constants
+
+    runahead = spc_constants.SPCONV_RULEBOOK_RUNAHEAD
+    spc_constants.SPCONV_RULEBOOK_RUNAHEAD = False
+    prof.records.clear()
+    for w in range(N_SCENES):
+        out = None
+        out = forward(*scenes_dev[w % N_SCENES], scene=w % N_SCENES)
+    prof.records.clear()
+    prof.enabled = True
+    torch.cuda.synchronize()
+    ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ea.record()
+    for s in range(args.steps):
+        out = None
+        out = forward(*scenes_dev[s % N_SCENES], scene=s % N_SCENES)
+    eb.record()
+    torch.cuda.synchronize()
+    prof.enabled = False
     gemm = prof.summarize()
+    serial_ms = ea.elapsed_time(eb)
+    spc_constants.SPCONV_RULEBOOK_RUNAHEAD = runahead
 
     # ---- end-to-end arm: pinned host buffers in, checksum out ----------------------------
     h2d = int(np.mean([i.numel() * 4 + f.numel() * 2 for i, f in scenes_host]))
@@ -554,11 +579,17 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
         "roofline": {
-            "kernel": "gather-GEMM forward (all launches of the timed region, aggregated)",
+            "kernel": "gather-GEMM forward (every launch of the timed steps, aggregated)",
+            "timing": "CUDA events around each launch on its stream, in a repeat of the timed steps with the "
+                      "rulebook run-ahead off so the kernel runs alone; overlapped_* are the same events inside "
+                      "the timed region, where rulebook kernels of the next layer share the SMs",
             "bound": "hbm", "achieved": achieved_gbs, "peak": hbm_peak, "unit": "GB/s",
             "frac": achieved_gbs / hbm_peak if hbm_peak else None, "traffic": None, "peak_kind": peak_kind,
             "launches": gemm["launches"], "avg_launch_ms": gemm["avg_ms"],
-            "share_of_step": gemm["ms"] / dev_ms if dev_ms else None,
+            "share_of_step": gemm["ms"] / serial_ms if serial_ms else None,
+            "serial_ms_per_step": serial_ms / args.steps,
+            "overlapped_avg_launch_ms": gemm_overlapped["avg_ms"],
+            "rulebook_runahead": bool(runahead),
             "tflops": achieved_tflops, "tensor_frac": achieved_tflops / tensor_peak if tensor_peak else None,
         },
         "cpu_baseline": cpu_baseline,

@@ -8,6 +8,7 @@ Read by this package:
   SPCONV_DO_SORT (env)              default of ``do_sort`` in pair generation
   SPCONV_ALLOW_TF32                 live switch: fp32 GEMMs use TF32 tensor cores
   SPCONV_FOLD_BN_RELU (env)         fold inference BatchNorm + ReLU into the conv kernel
+  SPCONV_RULEBOOK_RUNAHEAD (env)    build the next layer's rulebook beside the current GEMM
   SPCONV_ALLOW_FP16_ACCUM (env)     accepted; 16-bit GEMMs always accumulate in
                                     fp32 on B200 (full rate, more accurate)
 Everything else is kept only so that ``from ...constants import X`` works.
@@ -32,6 +33,10 @@ SPCONV_ALLOW_FP16_ACCUM = os.getenv("SPCONV_ALLOW_FP16_ACCUM", "0") == "1"
 # [sparse conv, BatchNorm1d, ReLU] as one kernel (normalisation folded into the
 # GEMM's store).  Read at call time; set to False for the unfused modules.
 SPCONV_FOLD_BN_RELU = os.getenv("SPCONV_FOLD_BN_RELU", "1") == "1"
+# Not in the reference.  SparseSequential builds the rulebook of the next layer on
+# a second CUDA stream while the GEMM of the current layer runs (same results).
+# Read at call time.
+SPCONV_RULEBOOK_RUNAHEAD = os.getenv("SPCONV_RULEBOOK_RUNAHEAD", "1") == "1"
 NDIM_DONT_CARE = 3
 
 ALL_WEIGHT_IS_KRSC = True

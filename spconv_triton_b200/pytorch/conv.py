@@ -180,13 +180,16 @@ class SparseConvolutionBase:
             return _Rulebook(datas.out_indices, out_spatial_shape, igemm=(
                 datas.pair_fwd, datas.pair_bwd, datas.pair_mask_fwd_splits, datas.pair_mask_bwd_splits,
                 datas.mask_argsort_fwd_splits, datas.mask_argsort_bwd_splits, datas.masks))
-        res = self._generate(
-            x, out_tensor.benchmark_record, name,
-            lambda: ops.get_indice_pairs_implicit_gemm(
-                x.indices, x.batch_size, x.spatial_shape, self.algo, ksize=self.kernel_size,
-                stride=self.stride, padding=self.padding, dilation=self.dilation,
-                out_padding=self.output_padding, subm=self.subm, transpose=self.transposed,
-                is_train=(not self.subm) or training, alloc=x.thrust_allocator, timer=x._timer))
+        planner = x._planner
+        res = planner.take(self, x) if planner is not None else None
+        if res is None:
+            res = self._generate(
+                x, out_tensor.benchmark_record, name,
+                lambda: ops.get_indice_pairs_implicit_gemm(
+                    x.indices, x.batch_size, x.spatial_shape, self.algo, ksize=self.kernel_size,
+                    stride=self.stride, padding=self.padding, dilation=self.dilation,
+                    out_padding=self.output_padding, subm=self.subm, transpose=self.transposed,
+                    is_train=(not self.subm) or training, alloc=x.thrust_allocator, timer=x._timer))
         if self.indice_key is not None:
             register_implicit_gemm_indice_data(
                 indice_dict, self.indice_key, res, x.indices, is_subm=self.subm,

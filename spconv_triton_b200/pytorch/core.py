@@ -120,6 +120,7 @@ class SparseConvTensor(metaclass=SpConvTensorMeta):
         self._timer = CUDAKernelTimer(enable_timer)
         self.force_algo = force_algo
         self.int8_scale: np.ndarray | None = None
+        self._planner = None  # rulebook run-ahead state of the enclosing SparseSequential
 
     def __repr__(self):
         return f"SparseConvTensor[shape={self._features.shape}]"
@@ -140,6 +141,7 @@ class SparseConvTensor(metaclass=SpConvTensorMeta):
         other._timer = self._timer
         other.force_algo = self.force_algo
         other.int8_scale = self.int8_scale
+        other._planner = self._planner
         return other
 
     def replace_feature(self, feature: torch.Tensor):

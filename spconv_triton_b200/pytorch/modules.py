@@ -64,6 +64,19 @@ class SparseSequential(SparseModule):
         self.add_module(name, module)
 
     def forward(self, x):
+        from . import runahead
+
+        entered, owned = x, runahead.begin(self, x)
+        try:
+            x = self._run(x)
+        finally:
+            if owned is not None:
+                entered._planner = None
+        if owned is not None and isinstance(x, SparseConvTensor):
+            x._planner = None
+        return x
+
+    def _run(self, x):
         mods = list(self._modules.values())
         i = 0
         while i < len(mods):
@@ -71,15 +84,18 @@ class SparseSequential(SparseModule):
             fused = _try_fold_bn_relu(mods, i, x)
             if fused is not None:
                 x, i = fused
-                continue
-            if is_spconv_module(module):
-                x = module(x)
-            elif isinstance(x, SparseConvTensor):
-                if x.indices.shape[0] != 0:
-                    x = x.replace_feature(module(x.features))
             else:
-                x = module(x)
-            i += 1
+                if is_spconv_module(module):
+                    x = module(x)
+                elif isinstance(x, SparseConvTensor):
+                    if x.indices.shape[0] != 0:
+                        x = x.replace_feature(module(x.features))
+                else:
+                    x = module(x)
+                i += 1
+            # the GEMM of this layer is queued: build the next rulebook beside it
+            if is_sparse_conv(module) and isinstance(x, SparseConvTensor) and x._planner is not None:
+                x._planner.advance()
         return x
 
 
