@@ -107,3 +107,24 @@ def test_edge_behaviour_of_constructors_and_tensor():
         x.features = torch.zeros(2, 3)
     y = x.replace_feature(x.features * 2)
     assert y.indice_dict is x.indice_dict and y.indices is x.indices
+
+
+def test_runahead_plan_walk():
+    """The rulebook run-ahead plans the sparse convolutions of nested
+    SparseSequential containers in execution order and stops at the first
+    sparse module whose output indices it cannot predict."""
+    from torch import nn
+
+    import spconv_triton_b200.pytorch as sp
+    from spconv_triton_b200.pytorch import runahead
+
+    a, b, c, d = sp.SubMConv3d(4, 8, 3), sp.SparseConv3d(8, 8, 3, 2), sp.SubMConv3d(8, 8, 3), sp.SubMConv3d(8, 8, 3)
+    net = sp.SparseSequential(a, nn.ReLU(), sp.SparseSequential(b, nn.BatchNorm1d(8), sp.SparseSequential(c)),
+                              sp.SparseMaxPool3d(2, 2), d)
+    assert runahead.flatten_convs(net) == [a, b, c]
+    assert runahead.flatten_convs(sp.SparseSequential(nn.ReLU())) == []
+    # CPU tensors never get a planner
+    import torch
+
+    x = sp.SparseConvTensor(torch.zeros(1, 4), torch.zeros(1, 4, dtype=torch.int32), [4, 4, 4], 1)
+    assert runahead.begin(net, x) is None and x._planner is None
