@@ -152,6 +152,18 @@ int spc_rulebook_igemm(const spc_geometry* g, const int32_t* indices, int64_t n_
                        int do_sort, int32_t* pair_fwd_rowmajor, int32_t* pair_bwd_rowmajor,
                        void* stream);
 
+/* The input-side half of spc_rulebook_igemm for strided / transposed layers
+ * (pair_bwd, mask_bwd, argsort_bwd, pair_bwd_rowmajor; same meaning), for
+ * callers that pass pair_bwd = NULL there and build these tables later or on
+ * another stream, off the path of the forward GEMM.  Same part of
+ * _impl/pairs.py:281-426 (its pair_bwd / mask_bwd outputs).  Must run after
+ * that call has finished with the same workspace (they share scratch). */
+int spc_rulebook_igemm_backward(const spc_geometry* g, const int32_t* indices, int64_t n_in,
+                                int64_t n_out, void* workspace, size_t workspace_bytes,
+                                int32_t* pair_bwd, int32_t* mask_bwd, int32_t* argsort_bwd,
+                                const uint32_t* split_masks, int n_split, int do_sort,
+                                int32_t* pair_bwd_rowmajor, void* stream);
+
 /* Row-major copy [n, kvp] of a pair table [kv, n] that was not produced by
  * spc_rulebook_igemm (tables converted from the Native format, user tables). */
 int spc_pairs_to_rowmajor(const int32_t* pairs, int kv, int64_t n, int32_t* out, void* stream);

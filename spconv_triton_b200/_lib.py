@@ -72,6 +72,8 @@ _PROTOTYPES = {
     "spc_rulebook_prepare": (c_int, [POINTER(Geometry), _P, c_int64, _P, c_size_t, POINTER(c_int64), _P]),
     "spc_rulebook_igemm": (c_int, [POINTER(Geometry), _P, c_int64, c_int64, _P, c_size_t, _P, _P, _P, _P, _P,
                                    _P, _P, POINTER(c_uint32), c_int, c_int, _P, _P, _P]),
+    "spc_rulebook_igemm_backward": (c_int, [POINTER(Geometry), _P, c_int64, c_int64, _P, c_size_t, _P, _P, _P,
+                                            POINTER(c_uint32), c_int, c_int, _P, _P]),
     "spc_pairs_to_rowmajor": (c_int, [_P, c_int, c_int64, _P, _P]),
     "spc_rulebook_native": (c_int, [POINTER(Geometry), _P, c_int64, c_int64, _P, c_size_t, _P, _P, _P, _P]),
     "spc_native_to_tables": (c_int, [_P, c_int, c_int64, c_int, _P, c_int64, _P, c_int64, _P]),

@@ -38,7 +38,9 @@ constexpr int kWgIssueThreads = kWgIssueWarps * 32;  // 256
 constexpr int kWgMmaWarp = kWgIssueWarps;
 constexpr int kWgThreads = kWgIssueThreads + 32;     // 288
 constexpr int kPairsPerStage = 64;
-constexpr int kRing = 512;                           // capacity of the pair list (power of two)
+constexpr int kScanBatch = 4;                        // table entries per thread per scan round
+constexpr int kScanEntries = kScanBatch * kWgIssueThreads;  // 1024
+constexpr int kRing = 2048;                          // capacity of the pair list (power of two, > 64 + 1024)
 
 struct WgParams {
   const void* feats;
@@ -63,12 +65,22 @@ template <int ELEM>
 __device__ __forceinline__ void copy_rows(uint32_t dst_base, const uint8_t* src, uint32_t src_pitch,
                                           const int* rows, int n_rows, int n_rows_padded, int pieces_per_row,
                                           int row_bytes, int tid) {
-  const int per_block = row_bytes / 16;
+  const int per_block = row_bytes / 16;  // 2, 4 or 8
   const uint32_t swz_mask = static_cast<uint32_t>(per_block - 1);
+  const int lg_pb = per_block == 8 ? 3 : (per_block == 4 ? 2 : 1);
   const int total = n_rows_padded * pieces_per_row;
+  const bool pow2 = (pieces_per_row & (pieces_per_row - 1)) == 0;
+  const int lg_ppr = 31 - __clz(pieces_per_row);
   for (int q = tid; q < total; q += kWgIssueThreads) {
-    const int p = q / pieces_per_row, piece = q - p * pieces_per_row;
-    const int block = piece / per_block, chunk = piece - block * per_block;
+    int p, piece;
+    if (pow2) {  // the usual case: no integer division per copy
+      p = q >> lg_ppr;
+      piece = q & (pieces_per_row - 1);
+    } else {
+      p = q / pieces_per_row;
+      piece = q - p * pieces_per_row;
+    }
+    const int block = piece >> lg_pb, chunk = piece & (per_block - 1);
     const uint32_t lin = static_cast<uint32_t>(p * row_bytes + chunk * 16);
     const uint32_t off = static_cast<uint32_t>(block * kPairsPerStage * row_bytes) + (lin ^ (((lin >> 7) & swz_mask) << 4));
     const bool live = p < n_rows;
@@ -93,8 +105,8 @@ wgrad_tc_kernel(const __grid_constant__ WgParams p) {
   int* rows_i = rows_m + kMaxStages * kPairsPerStage;
   uint64_t* bars = reinterpret_cast<uint64_t*>(rows_i + kMaxStages * kPairsPerStage);
   StageInfo* info = reinterpret_cast<StageInfo*>(bars + 2 * kMaxStages + 1);
-  int* warp_cnt = reinterpret_cast<int*>(info + kMaxStages);  // [8]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(warp_cnt + kWgIssueWarps);
+  int* warp_cnt = reinterpret_cast<int*>(info + kMaxStages);  // [kScanBatch][8]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(warp_cnt + kScanBatch * kWgIssueWarps);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -138,29 +150,54 @@ wgrad_tc_kernel(const __grid_constant__ WgParams p) {
     const uint8_t* f_src = static_cast<const uint8_t*>(p.feats);
     const uint32_t g_pitch = static_cast<uint32_t>(p.c_out) * ELEM, f_pitch = static_cast<uint32_t>(p.c_in) * ELEM;
 
+    // Table entries are fetched one scan round (1024 entries, four per thread) ahead:
+    // the loads of the next round are in flight while the stages of this one are built,
+    // so the walk over a sparse table does not pay a memory latency per round.
+    const int32_t* table = p.pair_fwd + static_cast<long long>(k) * p.n_out;
+    int ahead[kScanBatch];
+    auto fetch = [&](long long at) {
+#pragma unroll
+      for (int j = 0; j < kScanBatch; ++j) {
+        const long long m = at + j * kWgIssueThreads + tid;
+        ahead[j] = m < hi ? __ldg(&table[m]) : -1;
+      }
+    };
+    fetch(pos);
     while (pos < hi || tail > head) {
       if (tail - head < kPairsPerStage && pos < hi) {
-        // ---- scan 256 table entries, append the existing pairs to the ring ----
-        const long long m = pos + tid;
-        const int in_row = m < hi ? __ldg(&p.pair_fwd[static_cast<long long>(k) * p.n_out + m]) : -1;
-        const unsigned ballot = __ballot_sync(0xffffffffu, in_row >= 0);
-        if (lane == 0) warp_cnt[warp] = __popc(ballot);
-        named_bar_sync(1, kWgIssueThreads);
-        int before = 0, total = 0;
+        // ---- append the existing pairs of one scan round to the ring, in table order ----
+        int cur[kScanBatch];
+        unsigned ballot[kScanBatch];
 #pragma unroll
-        for (int w = 0; w < kWgIssueWarps; ++w) {
-          const int c = warp_cnt[w];
-          if (w < warp) before += c;
-          total += c;
+        for (int j = 0; j < kScanBatch; ++j) {
+          cur[j] = ahead[j];
+          ballot[j] = __ballot_sync(0xffffffffu, cur[j] >= 0);
+          if (lane == 0) warp_cnt[j * kWgIssueWarps + warp] = __popc(ballot[j]);
         }
-        if (in_row >= 0) {
-          const int slot = (tail + before + __popc(ballot & ((1u << lane) - 1u))) & (kRing - 1);
-          ring_m[slot] = static_cast<int>(m);
-          ring_i[slot] = in_row;
+        const long long at = pos;
+        pos += kScanEntries;
+        if (pos < hi) fetch(pos);
+        named_bar_sync(1, kWgIssueThreads);
+        int before[kScanBatch];
+        int run = 0;
+#pragma unroll
+        for (int j = 0; j < kScanBatch; ++j) {
+#pragma unroll
+          for (int w = 0; w < kWgIssueWarps; ++w) {
+            if (w == warp) before[j] = run;
+            run += warp_cnt[j * kWgIssueWarps + w];
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < kScanBatch; ++j) {
+          if (cur[j] >= 0) {
+            const int slot = (tail + before[j] + __popc(ballot[j] & ((1u << lane) - 1u))) & (kRing - 1);
+            ring_m[slot] = static_cast<int>(at + j * kWgIssueThreads + tid);
+            ring_i[slot] = cur[j];
+          }
         }
         named_bar_sync(1, kWgIssueThreads);
-        tail += total;
-        pos += kWgIssueThreads;
+        tail += run;
         continue;
       }
       // ---- one stage: up to 64 pairs from the head of the ring ----
@@ -353,7 +390,7 @@ int wgrad_tc(const void* feats, const void* gout, const int32_t* pair_fwd, float
   p.f_stage_bytes = static_cast<int>(align_up(static_cast<size_t>(c_in) * 2 * kPairsPerStage, 1024));
   const int stage_bytes = p.g_stage_bytes + p.f_stage_bytes;
   const size_t fixed = 1024 + 2 * kRing * 4 + 2 * tc::kMaxStages * kPairsPerStage * 4 + (2 * tc::kMaxStages + 1) * 8 +
-                       tc::kMaxStages * sizeof(tc::StageInfo) + 128;
+                       tc::kMaxStages * sizeof(tc::StageInfo) + kScanBatch * kWgIssueWarps * 4 + 64;
   const size_t budget = 110 * 1024;
   p.stages = std::max(2, std::min<int>(tc::kMaxStages, static_cast<int>((budget - fixed) / stage_bytes)));
   const size_t smem_bytes = fixed + static_cast<size_t>(p.stages) * stage_bytes;

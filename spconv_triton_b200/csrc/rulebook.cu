@@ -813,6 +813,23 @@ int emit_masks(const Layout& L, char* ws, int64_t n, int kv, const uint32_t* spl
   return SPC_OK;
 }
 
+// Input-side tables of a strided / transposed layer: pair_bwd and its masks.
+// Reads the output hash the forward phase ranked; shares the mask scratch with
+// it, so it must follow the forward phase of the same workspace.
+template <int ND, bool K64>
+int igemm_backward_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, int64_t n_out, char* ws,
+                        int32_t* pair_bwd, int32_t* mask_bwd, int32_t* argsort_bwd, const uint32_t* split_masks,
+                        int n_split, int do_sort, int32_t* bwd_rm, cudaStream_t st) {
+  const int kvp = (g.kv + 3) & ~3;
+  Table<K64> tout = table_at<K64>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
+  uint32_t* words = reinterpret_cast<uint32_t*>(ws + L.off_words);
+  fill_bwd_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(
+      g, idx, n_in, n_out, tout, pair_bwd, mask_bwd ? words : nullptr, L.mic, bwd_rm, kvp);
+  SPC_LAUNCH_OK();
+  if (mask_bwd != nullptr) return emit_masks(L, ws, n_in, g.kv, split_masks, n_split, do_sort, mask_bwd, argsort_bwd, st);
+  return SPC_OK;
+}
+
 template <int ND, bool K64>
 int igemm_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, int64_t n_out, char* ws,
                int32_t* out_indices, int32_t* pair_fwd, int32_t* pair_bwd, int32_t* mask_fwd,
@@ -834,15 +851,9 @@ int igemm_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, 
   SPC_LAUNCH_OK();
   int rc = emit_masks(L, ws, n_out, g.kv, split_masks, n_split, do_sort, mask_fwd, argsort_fwd, st);
   if (rc != SPC_OK) return rc;
-  if (!g.subm && pair_bwd != nullptr) {
-    fill_bwd_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(
-        g, idx, n_in, n_out, tout, pair_bwd, mask_bwd ? words : nullptr, L.mic, bwd_rm, kvp);
-    SPC_LAUNCH_OK();
-    if (mask_bwd != nullptr) {
-      rc = emit_masks(L, ws, n_in, g.kv, split_masks, n_split, do_sort, mask_bwd, argsort_bwd, st);
-      if (rc != SPC_OK) return rc;
-    }
-  }
+  if (!g.subm && pair_bwd != nullptr)
+    return igemm_backward_impl<ND, K64>(g, L, idx, n_in, n_out, ws, pair_bwd, mask_bwd, argsort_bwd, split_masks,
+                                        n_split, do_sort, bwd_rm, st);
   return SPC_OK;
 }
 
@@ -953,6 +964,31 @@ extern "C" int spc_rulebook_igemm(const spc_geometry* sg, const int32_t* indices
     return igemm_impl<decltype(nd)::value, decltype(k64)::value>(
         g, L, indices, n_in, n_out, ws, out_indices, pair_fwd, pair_bwd, mask_fwd, argsort_fwd, mask_bwd,
         argsort_bwd, split_masks, n_split, do_sort, pair_fwd_rowmajor, pair_bwd_rowmajor, st);
+  });
+}
+
+extern "C" int spc_rulebook_igemm_backward(const spc_geometry* sg, const int32_t* indices, int64_t n_in,
+                                           int64_t n_out, void* workspace, size_t workspace_bytes,
+                                           int32_t* pair_bwd, int32_t* mask_bwd, int32_t* argsort_bwd,
+                                           const uint32_t* split_masks, int n_split, int do_sort,
+                                           int32_t* pair_bwd_rowmajor, void* stream) {
+  Geo g;
+  if (!make_geo(sg, &g)) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: bad geometry");
+  if (g.subm) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm backward: submanifold tables come from the forward call");
+  if (n_in <= 0 || n_out <= 0 || !indices || !workspace || !pair_bwd || !split_masks || n_split < 1 || n_split > 2)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm backward: bad arguments");
+  if ((mask_bwd == nullptr) != (argsort_bwd == nullptr))
+    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm backward: mask_bwd and argsort_bwd go together");
+  const Layout L = make_layout(g, n_in);
+  if (workspace_bytes < L.total)
+    return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "rulebook: workspace %zu < %zu bytes", workspace_bytes, L.total);
+  if (n_out > L.bound) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm backward: n_out exceeds prepared bound");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* ws = static_cast<char*>(workspace);
+  return dispatch(g.ndim, L.k64, [&](auto nd, auto k64) {
+    return igemm_backward_impl<decltype(nd)::value, decltype(k64)::value>(
+        g, L, indices, n_in, n_out, ws, pair_bwd, mask_bwd, argsort_bwd, split_masks, n_split, do_sort,
+        pair_bwd_rowmajor, st);
   });
 }
 

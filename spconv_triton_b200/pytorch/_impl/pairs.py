@@ -8,7 +8,9 @@ done by ``spc_rulebook_*`` in libspconv_b200.so.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import threading
 import functools
 
 import numpy as np
@@ -136,6 +138,31 @@ def _split_masks(kv, is_mask_split):
     return [np.array([0xFFFFFFFF], dtype=np.uint32)]
 
 
+class DeferredBackward:
+    """While one of these is installed (``deferred_backward``), igemm_pairs builds
+    the input-side tables of strided layers on ``stream`` instead of the current
+    one, after the forward tables, and appends ``(event, tensors)`` to
+    ``pending``: whoever reads those tensors on another stream waits for the
+    event first.  Used by the rulebook run-ahead of SparseSequential."""
+
+    def __init__(self, stream):
+        self.stream = stream
+        self.pending: list = []
+
+
+_tls = threading.local()
+
+
+@contextlib.contextmanager
+def deferred_backward(defer: DeferredBackward):
+    old = getattr(_tls, "defer", None)
+    _tls.defer = defer
+    try:
+        yield defer
+    finally:
+        _tls.defer = old
+
+
 def igemm_pairs(indices, batch_size, spatial_shape, ksize, stride, padding, dilation, out_padding, subm,
                 transpose, is_train, is_mask_split, do_sort=True, num_out_act_bound=-1):
     """Reference: igemm_pairs, _impl/pairs.py:281-426.  Same 9-tuple:
@@ -171,12 +198,31 @@ def igemm_pairs(indices, batch_size, spatial_shape, ksize, stride, padding, dila
         fwd_rm = torch.empty((n_out, kvp), dtype=torch.int32, device=dev)
         bwd_rm = torch.empty((p.n_in, kvp), dtype=torch.int32, device=dev) if want_bwd else None
         split_words = (ctypes.c_uint32 * n_split)(*[int(m[0]) for m in masks])
-        _lib.check(_lib.load().spc_rulebook_igemm(
+        defer = getattr(_tls, "defer", None) if want_bwd_masks else None
+        lib = _lib.load()
+        _lib.check(lib.spc_rulebook_igemm(
             ctypes.byref(p.geom), _lib.ptr(p.indices), p.n_in, n_out, _lib.ptr(p.workspace),
             p.workspace.numel(), None if subm else _lib.ptr(out_inds), _lib.ptr(pair_fwd),
-            _lib.ptr(pair_bwd), _lib.ptr(pm_fwd), _lib.ptr(ma_fwd), _lib.ptr(pm_bwd), _lib.ptr(ma_bwd),
-            split_words, n_split, int(bool(do_sort)), _lib.ptr(fwd_rm), _lib.ptr(bwd_rm),
+            None if defer else _lib.ptr(pair_bwd), _lib.ptr(pm_fwd), _lib.ptr(ma_fwd),
+            None if defer else _lib.ptr(pm_bwd), None if defer else _lib.ptr(ma_bwd),
+            split_words, n_split, int(bool(do_sort)), _lib.ptr(fwd_rm), None if defer else _lib.ptr(bwd_rm),
             _lib.current_stream(dev)))
+        if defer is not None:
+            # the input-side tables follow on the other stream, once the forward half is done
+            fwd_done = torch.cuda.Event()
+            fwd_done.record()
+            late = [pair_bwd, pm_bwd, ma_bwd, bwd_rm]
+            for t in late + [p.workspace, p.indices]:
+                t.record_stream(defer.stream)
+            with torch.cuda.stream(defer.stream):
+                defer.stream.wait_event(fwd_done)
+                _lib.check(lib.spc_rulebook_igemm_backward(
+                    ctypes.byref(p.geom), _lib.ptr(p.indices), p.n_in, n_out, _lib.ptr(p.workspace),
+                    p.workspace.numel(), _lib.ptr(pair_bwd), _lib.ptr(pm_bwd), _lib.ptr(ma_bwd), split_words,
+                    n_split, int(bool(do_sort)), _lib.ptr(bwd_rm), _lib.current_stream(dev)))
+                done = torch.cuda.Event()
+                done.record()
+            defer.pending.append((done, late))
         npl = torch.zeros(kv, dtype=torch.int32, device=dev)
         pair_fwd._spc_rowmajor = fwd_rm
         if want_bwd:

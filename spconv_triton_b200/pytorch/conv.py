@@ -169,6 +169,8 @@ class SparseConvolutionBase:
             if datas.is_subm is not False:
                 raise AssertionError("inverse conv can only be used with standard conv and pool ops.")
             self._check_inverse_reuse_valid(x, x.spatial_shape, datas)
+            if x._planner is not None:
+                x._planner.join_late()  # pair_bwd of the down-sampling layer may still be in the making
             # the inverse layer runs the down-sampling layer's rulebook backwards
             return _Rulebook(datas.indices, datas.spatial_shape, igemm=(
                 datas.pair_bwd, datas.pair_fwd, datas.pair_mask_bwd_splits, datas.pair_mask_fwd_splits,

@@ -71,6 +71,7 @@ class SparseSequential(SparseModule):
             x = self._run(x)
         finally:
             if owned is not None:
+                owned.join_late()
                 entered._planner = None
         if owned is not None and isinstance(x, SparseConvTensor):
             x._planner = None

@@ -28,13 +28,14 @@ from spconv_triton_b200.core import ConvAlgo
 
 from .. import constants
 from . import ops
+from ._impl import pairs as _pairs
 from .core import ImplicitGemmIndiceData, SparseConvTensor, register_implicit_gemm_indice_data
 
 _side_streams: dict = {}
 
 
-def _side_stream(device: torch.device) -> torch.cuda.Stream:
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+def _side_stream(device: torch.device, which: int) -> torch.cuda.Stream:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), which)
     if key not in _side_streams:
         _side_streams[key] = torch.cuda.Stream(device=device, priority=-1)
     return _side_streams[key]
@@ -92,7 +93,10 @@ class RulebookPlanner:
         self.allocator = x.thrust_allocator
         self.timer = x._timer
         self.main = torch.cuda.current_stream(device)
-        self.side = _side_stream(device)
+        self.side = _side_stream(device, 0)
+        # input-side tables of strided layers: needed by inverse layers and the backward
+        # pass only, so they are built on a third stream, off the chain of rulebooks
+        self.late = _pairs.DeferredBackward(_side_stream(device, 1))
         self.side.wait_stream(self.main)
         x.indices.record_stream(self.side)
 
@@ -130,7 +134,7 @@ class RulebookPlanner:
             self.indices, self.spatial_shape = datas.out_indices, out_shape
             return True
         src = self.indices
-        with torch.cuda.stream(self.side):
+        with torch.cuda.stream(self.side), _pairs.deferred_backward(self.late):
             res = ops.get_indice_pairs_implicit_gemm(
                 src, self.batch_size, self.spatial_shape, conv.algo, ksize=conv.kernel_size,
                 stride=conv.stride, padding=conv.padding, dilation=conv.dilation,
@@ -164,6 +168,18 @@ class RulebookPlanner:
             if t.is_cuda:
                 t.record_stream(main)
         return res
+
+
+    def join_late(self) -> None:
+        """Makes the caller's stream wait for every input-side table built so far."""
+        if not self.late.pending:
+            return
+        main = torch.cuda.current_stream(self.indices.device)
+        for event, tensors in self.late.pending:
+            main.wait_event(event)
+            for t in tensors:
+                t.record_stream(main)
+        self.late.pending.clear()
 
 
 def begin(container, x):
