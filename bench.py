@@ -305,7 +305,10 @@ def run_op_bench(args):
     headline line): ``--op pool`` = configs[4] SparseMaxPool3d k2 s2 and
     SparseAvgPool3d k3 s1 at C = 256 fp16, 4 x 400k voxels in 256^3;
     ``--op conv_s2`` = configs[1] SparseConv3d k3 s2 64 -> 128 fp16, 4 x 120k
-    voxels.  One JSON line per kernel with algorithmic GB/s (and TFLOP/s)."""
+    voxels; ``--op conv_subm`` = SubMConv3d k3 (forward, input and weight gradient)
+    at 32, 64 and 128 channels on the voxel set two stride-2 layers leave of a
+    4-sample LiDAR-like batch.  One JSON line per kernel with algorithmic GB/s
+    (and TFLOP/s)."""
     from spconv_triton_b200.pytorch._impl import gemm as G
     from spconv_triton_b200.pytorch._impl import pairs as P
     from spconv_triton_b200.pytorch._impl import pool as PL
@@ -363,6 +366,28 @@ def run_op_bench(args):
                      voxels=int(idx.shape[0]), n_out=n_out, pairs=pairs, voxel_order=args.voxel_order)
                 bwd_bytes = idx.shape[0] * c * 2 + pairs * (c * 2 + 4) + kv * idx.shape[0] * 4
                 emit(name + "_bwd", timed(lambda: PL.avgpool_backward(g, pb, cnt), iters), bwd_bytes)
+    elif args.op == "conv_subm":
+        # the backbone's dominant layer type: SubMConv3d k3 at the geometry two stride-2 layers leave
+        batch, shape = 4, list(GRID)
+        idx = torch.from_numpy(lidar_like_batch(3, batch, (16000, 24000), tuple(GRID))).to(dev)
+        for _ in range(2):
+            r = P.igemm_pairs(idx, batch, shape, [3] * 3, [2] * 3, [1] * 3, [1] * 3, [0] * 3, False, False, False, False)
+            idx, shape = r[0], P.get_conv_output_size(shape, [3] * 3, [2] * 3, [1] * 3, [1] * 3)
+        r = P.igemm_pairs(idx, batch, shape, [3] * 3, [1] * 3, [1] * 3, [1] * 3, [0] * 3, True, False, True, False)
+        pf, pb, maf, mab = r[2], r[3], r[6][0], r[6][0]
+        n, kv = idx.shape[0], pf.shape[0]
+        pairs = int((pf >= 0).sum())
+        for c in (32, 64, 128):
+            x = torch.randn(n, c, device=dev).half()
+            w = (torch.randn(c, kv, c, device=dev) * 0.02).half()
+            g = torch.randn(n, c, device=dev).half()
+            flops = 2.0 * pairs * c * c
+            nbytes = pairs * c * 2 + n * c * 2 + kv * n * 4 + kv * c * c * 2
+            emit(f"subm_fwd_{c}_{c}", timed(lambda: G.conv_forward(x, w, pf, n, mask_argsort=maf), iters), nbytes, flops,
+                 voxels=n, pairs=pairs)
+            emit(f"subm_dgrad_{c}_{c}", timed(lambda: G.conv_backward_input(g, w, pb, n, mask_argsort=mab), iters), nbytes, flops)
+            emit(f"subm_wgrad_{c}_{c}", timed(lambda: G.conv_backward_weight(x, g, pf, (c, kv, c)), iters),
+                 pairs * 2 * c * 2 + kv * n * 4, flops)
     else:
         batch = 4
         idx = torch.from_numpy(lidar_like_batch(100, batch, (120000, 120000), tuple(GRID))).to(dev)
@@ -393,7 +418,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-baseline-seconds", type=float, default=20.0)
-    ap.add_argument("--op", default=None, choices=["pool", "conv_s2"],
+    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm"],
                     help="single-operator timings at the other configurations instead of the headline benchmark")
     ap.add_argument("--voxel-order", default="random", choices=["random", "sorted"],
                     help="--op pool: input voxel order (random = as a voxeliser emits them, sorted = as a previous layer's rulebook emits them)")
