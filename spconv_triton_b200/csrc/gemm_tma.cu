@@ -28,6 +28,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <type_traits>
 
 #include "common.cuh"
 #include "gemm_internal.cuh"
@@ -305,52 +306,78 @@ if (has_epilogue) finish_epilogue16(v, epi_scale + c0, epi_shift + c0, p.epi.act
     }
   } else {
     // ---------------- MMA issuer ----------------
+    // One thread paces the whole CTA: every instruction between "stage full" and the commit is
+    // on the critical path, so the loop carries running descriptor words (a stage advance is one
+    // add to the address field) and the reduction steps are unrolled.
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (TcType<T>::fmt << 7) | (TcType<T>::fmt << 10) |
                              ((B_MN ? 1u : 0u) << 16) | (static_cast<uint32_t>(p.n_dim >> 3) << 17) |
                              (static_cast<uint32_t>(kTileM >> 4) << 24);
       const uint32_t a_type = layout_type_for(p.a_row_bytes);
       const uint32_t b_type = B_MN ? layout_type_for(p.b_row_bytes) : a_type;
-      int stage = 0;
-      uint32_t full_parity = 0;
-      uint32_t accumulate = 0;
+      const uint32_t a_addr0 = smem_u32(stage_base);
+      const uint64_t a_desc0 = make_desc(a_addr0, 16, 8 * p.a_row_bytes, a_type);
+      const uint64_t b_desc0 = B_MN ? make_desc(a_addr0 + p.a_stage_bytes, epr * p.b_row_bytes, 8 * p.b_row_bytes, b_type)
+                                    : make_desc(a_addr0 + p.a_stage_bytes, 16, 8 * p.a_row_bytes, a_type);
+      const uint32_t a_hi = static_cast<uint32_t>(a_desc0 >> 32), b_hi = static_cast<uint32_t>(b_desc0 >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(a_desc0), b_lo0 = static_cast<uint32_t>(b_desc0);
+      const uint32_t stage_step = static_cast<uint32_t>(stage_bytes >> 4);  // address field counts 16-byte units
+      const uint32_t b_step = static_cast<uint32_t>(B_MN ? UMMA_K * p.b_row_bytes / 16 : 2);
+      const uint32_t info0 = smem_u32(info);
       bool ok = true;
-      int mma_n = 0;
-      (void)mma_n;
-      while (true) {
-        // a wait that expires here is either a real failure or the producers having aborted
-        if (!mbar_wait(bar_full + 8 * stage, full_parity)) {
-          ok = false;
-          break;
+
+      auto run = [&](auto ks_tag) {
+        constexpr int KS = decltype(ks_tag)::value;
+        uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full, empty = bar_empty, inf = info0;
+        uint32_t full_parity = 0, accumulate = 0;
+        int stage = 0;
+        int mma_n = 0;
+        (void)mma_n;
+        while (true) {
+          // a wait that expires here is either a real failure or the producers having aborted
+          if (!mbar_wait(full, full_parity)) {
+            ok = false;
+            break;
+          }
+          // the feature rows were written through the generic proxy (cp.async): order
+          // those writes before the tensor core's async-proxy reads
+          fence_proxy_async();
+          tc_fence_after();
+          SPC_STAMP(512 + mma_n);
+          ++mma_n;
+          uint32_t ksteps;
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(ksteps) : "r"(inf) : "memory");
+          if (ksteps == 0) {  // terminator
+            tc_commit(bar_accum);
+            break;
+          }
+#pragma unroll
+          for (int ks = 0; ks < KS; ++ks) {
+            const uint64_t a_desc = (static_cast<uint64_t>(a_hi) << 32) | (a_lo + 2u * ks);
+            const uint64_t b_desc = (static_cast<uint64_t>(b_hi) << 32) | (b_lo + b_step * ks);
+            tc_mma<TF32>(tmem_base, a_desc, b_desc, idesc, accumulate);
+            accumulate = 1;
+          }
+          tc_commit(empty);
+          a_lo += stage_step;
+          b_lo += stage_step;
+          full += 8;
+          empty += 8;
+          inf += static_cast<uint32_t>(sizeof(StageInfo));
+          if (++stage == p.stages) {
+            stage = 0;
+            full_parity ^= 1;
+            a_lo = a_lo0;
+            b_lo = b_lo0;
+            full = bar_full;
+            empty = bar_empty;
+            inf = info0;
+          }
         }
-        // the feature rows were written through the generic proxy (cp.async): order
-        // those writes before the tensor core's async-proxy reads
-        fence_proxy_async();
-        tc_fence_after();
-        SPC_STAMP(512 + mma_n);
-        ++mma_n;
-        const StageInfo si = info[stage];
-        const uint32_t a_addr = smem_u32(stage_base + static_cast<size_t>(stage) * stage_bytes);
-        const uint32_t b_addr = a_addr + p.a_stage_bytes;
-        const uint64_t a_desc = make_desc(a_addr, 16, 8 * p.a_row_bytes, a_type);
-        const uint64_t b_desc = B_MN ? make_desc(b_addr, epr * p.b_row_bytes, 8 * p.b_row_bytes, b_type)
-                                     : make_desc(b_addr, 16, 8 * p.a_row_bytes, a_type);
-        for (int ks = 0; ks < si.ksteps; ++ks) {
-          const uint64_t a_step = static_cast<uint64_t>(ks * 2);
-          const uint64_t b_step = static_cast<uint64_t>(B_MN ? ks * (UMMA_K * p.b_row_bytes / 16) : ks * 2);
-          tc_mma<TF32>(tmem_base, a_desc + a_step, b_desc + b_step, idesc, accumulate);
-          accumulate = 1;
-        }
-        if (si.last) {
-          tc_commit(bar_accum);
-          break;
-        }
-        tc_commit(bar_empty + 8 * stage);
-        if (++stage == p.stages) {
-          stage = 0;
-          full_parity ^= 1;
-        }
-      }
+      };
+      if (ksteps == 4) run(std::integral_constant<int, 4>{});
+      else if (ksteps == 2) run(std::integral_constant<int, 2>{});
+      else run(std::integral_constant<int, 1>{});
       if (!ok) {
         atomicExch(p.status, SPC_ERR_DEVICE_WAIT_EXPIRED);
         // release the epilogue warps: nothing more will be accumulated
