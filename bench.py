@@ -185,6 +185,11 @@ class ClockSampler:
         return out
 
 
+# DRAM bytes (read + write) of one forward gather-GEMM launch of this workload, averaged over the
+# launches of one ncu capture of this file (see profiles/).
+GEMM_DRAM_BYTES_PER_LAUNCH = 298.3e6
+
+
 class GemmProfiler:
     """Wraps the forward gather-GEMM wrapper so that every launch inside the
     timed region is bracketed by CUDA events on the launching stream and its
@@ -609,7 +614,11 @@ def main():
                       "rulebook run-ahead off so the kernel runs alone; overlapped_* are the same events inside "
                       "the timed region, where rulebook kernels of the next layer share the SMs",
             "bound": "hbm", "achieved": achieved_gbs, "peak": hbm_peak, "unit": "GB/s",
-            "frac": achieved_gbs / hbm_peak if hbm_peak else None, "traffic": None, "peak_kind": peak_kind,
+            "frac": achieved_gbs / hbm_peak if hbm_peak else None, "traffic": GEMM_DRAM_BYTES_PER_LAUNCH,
+            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, average of the 34 gather-GEMM "
+                              "launches captured on this workload (profiles/voxelnet_backbone_launch_list.md)",
+            "algorithmic_bytes_per_launch": gemm["bytes"] / gemm["launches"] if gemm["launches"] else None,
+            "peak_kind": peak_kind,
             "launches": gemm["launches"], "avg_launch_ms": gemm["avg_ms"],
             "share_of_step": gemm["ms"] / serial_ms if serial_ms else None,
             "serial_ms_per_step": serial_ms / args.steps,
