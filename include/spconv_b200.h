@@ -182,6 +182,27 @@ int spc_native_to_tables(const int32_t* pair, int kv, int64_t n_pair, int invers
                          int32_t* pair_fwd, int64_t n_out, int32_t* pair_bwd, int64_t n_in,
                          void* stream);
 
+/* ---- voxelisation (the step before the rulebook in a LiDAR pipeline) ---- */
+
+/* Replaces PointToVoxel.generate_voxel_with_id, spconv_triton/pytorch/utils.py:72-163.
+ *   points [n_points, point_stride] fp32 (first ndim columns are x, y, z..; the
+ *   first num_features columns are stored); cmin / vsize / grid_xyz: HOST arrays
+ *   of ndim entries in x, y, z order (grid = round((cmax - cmin) / vsize));
+ *   voxels [max_voxels, max_points, num_features] fp32 (cleared first when
+ *   clear_voxels), indices [max_voxels, ndim] int32 in z, y, x order,
+ *   num_per_voxel [max_voxels] int32, pc_voxel_id [n_points] int64 (-1 = out of
+ *   range or beyond the voxel cap).  Voxels are numbered by their first point,
+ *   points keep arrival order inside a voxel: the result equals the
+ *   reference's bit for bit.  *num_voxels_host receives the number of voxels
+ *   written (the call synchronises the stream once to read it, where the
+ *   reference reads uniq.numel()).  Grids of 2^32 cells or more are rejected. */
+size_t spc_voxelize_workspace_bytes(int64_t n_points, int64_t max_voxels);
+int spc_voxelize(const float* points, int64_t n_points, int point_stride, int ndim, int num_features,
+                 const float* cmin, const float* vsize, const int32_t* grid_xyz, int64_t max_voxels,
+                 int max_points, int clear_voxels, int empty_mean, void* workspace,
+                 size_t workspace_bytes, float* voxels, int32_t* indices, int32_t* num_per_voxel,
+                 int64_t* pc_voxel_id, int64_t* num_voxels_host, void* stream);
+
 /* ---- implicit gather-GEMM ---------------------------------------------- */
 
 /* Forward: replaces conv_forward, _impl/gemm.py:501-568.
