@@ -312,8 +312,8 @@ def run_op_bench(args):
     ``--op conv_s2`` = configs[1] SparseConv3d k3 s2 64 -> 128 fp16, 4 x 120k
     voxels; ``--op conv_subm`` = SubMConv3d k3 (forward, input and weight gradient)
     at 32, 64 and 128 channels on the voxel set two stride-2 layers leave of a
-    4-sample LiDAR-like batch.  One JSON line per kernel with algorithmic GB/s
-    (and TFLOP/s)."""
+    4-sample LiDAR-like batch; ``--op voxelize`` = PointToVoxel on 1.2M points.
+    One JSON line per kernel with algorithmic GB/s (and TFLOP/s)."""
     from spconv_triton_b200.pytorch._impl import gemm as G
     from spconv_triton_b200.pytorch._impl import pairs as P
     from spconv_triton_b200.pytorch._impl import pool as PL
@@ -337,6 +337,8 @@ def run_op_bench(args):
     def emit(name, ms, nbytes, flops=None, **extra):
         line = {"op": name, "ms": ms, "algorithmic_GBps": nbytes / ms / 1e6, "hbm_frac": nbytes / ms / 1e6 / hbm_peak,
                 "peak_kind": peak_kind, **extra}
+        if "mpoints_per_s" in line:
+            line["mpoints_per_s"] = line["points"] / ms / 1e3
         if flops:
             line["TFLOPs"] = flops / ms / 1e9
             line["tensor_frac"] = flops / ms / 1e9 / tensor_peak
@@ -371,6 +373,21 @@ def run_op_bench(args):
                      voxels=int(idx.shape[0]), n_out=n_out, pairs=pairs, voxel_order=args.voxel_order)
                 bwd_bytes = idx.shape[0] * c * 2 + pairs * (c * 2 + 4) + kv * idx.shape[0] * 4
                 emit(name + "_bwd", timed(lambda: PL.avgpool_backward(g, pb, cnt), iters), bwd_bytes)
+    elif args.op == "voxelize":
+        # the step before the backbone: 8 LiDAR sweeps of 150k points -> voxels of 0.16 x 0.16 x 0.2 m
+        from spconv_triton_b200.pytorch.utils import PointToVoxel
+
+        g = torch.Generator().manual_seed(1)
+        n, f, maxpts, cap = 1_200_000, 4, 5, 800_000
+        pts = torch.cat([torch.randn(n, 3, generator=g) * torch.tensor([18.0, 18.0, 0.9]), torch.rand(n, 1, generator=g)], 1)
+        pts = pts.to(dev)
+        p2v = PointToVoxel([0.16, 0.16, 0.2], [-35.2, -40.0, -3.0, 35.2, 40.0, 1.0], f, cap, maxpts, dev)
+        vox, idx, npv, pcvid = p2v.generate_voxel_with_id(pts)
+        m = int(idx.shape[0])
+        stored = int(npv.sum())
+        nbytes = n * f * 4 + cap * maxpts * f * 4 + stored * f * 4 + n * 8 + m * 16
+        emit("voxelize_1.2M_points", timed(lambda: p2v.generate_voxel_with_id(pts), iters), nbytes, points=n,
+             voxels=m, stored_points=stored, mpoints_per_s=None)
     elif args.op == "conv_subm":
         # the backbone's dominant layer type: SubMConv3d k3 at the geometry two stride-2 layers leave
         batch, shape = 4, list(GRID)
@@ -423,7 +440,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-baseline-seconds", type=float, default=20.0)
-    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm"],
+    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm", "voxelize"],
                     help="single-operator timings at the other configurations instead of the headline benchmark")
     ap.add_argument("--voxel-order", default="random", choices=["random", "sorted"],
                     help="--op pool: input voxel order (random = as a voxeliser emits them, sorted = as a previous layer's rulebook emits them)")

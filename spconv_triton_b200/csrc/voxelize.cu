@@ -121,6 +121,11 @@ mark_first_kernel(const uint32_t* __restrict__ keys, long long n, const unsigned
   flag[i] = (f == static_cast<int>(i)) ? 1 : 0;
 }
 
+// status[1] = number of voxels found (rank of the last point + its flag): one word for the host to read.
+__global__ void total_kernel(const int* __restrict__ rank, const int* __restrict__ flag, long long n, int* __restrict__ status) {
+  status[1] = rank[n - 1] + flag[n - 1];
+}
+
 __global__ void __launch_bounds__(kVoxThreads)
 assign_kernel(const __grid_constant__ VoxGeo g, const uint32_t* __restrict__ keys, const int* __restrict__ first,
               const int* __restrict__ rank, long long n, long long num_voxels, int* __restrict__ counts,
@@ -135,7 +140,7 @@ assign_kernel(const __grid_constant__ VoxGeo g, const uint32_t* __restrict__ key
     if (vid >= num_voxels) vid = -1;  // beyond the voxel cap
   }
   pc_voxel_id[i] = vid;
-  sort_keys[i] = vid >= 0 ? static_cast<uint32_t>(vid) : kNoKey;
+  sort_keys[i] = vid >= 0 ? static_cast<uint32_t>(vid) : static_cast<uint32_t>(num_voxels);  // dropped: behind every voxel
   sort_vals[i] = static_cast<int>(i);
   if (vid < 0) return;
   atomicAdd(&counts[vid], 1);
@@ -161,14 +166,14 @@ clamp_counts_kernel(const int* __restrict__ counts, long long num_voxels, int ma
 __global__ void __launch_bounds__(kVoxThreads)
 scatter_points_kernel(const float* __restrict__ points, int point_stride, int num_features,
                       const uint32_t* __restrict__ sorted_vid, const int* __restrict__ sorted_idx,
-                      const int* __restrict__ seg_start, long long n_kept, int max_points,
+                      const int* __restrict__ seg_start, long long n_kept, long long num_voxels, int max_points,
                       float* __restrict__ voxels) {
   const long long e = blockIdx.x * static_cast<long long>(kVoxThreads) + threadIdx.x;
   const long long pos = e / num_features;
   if (pos >= n_kept) return;
   const int c = static_cast<int>(e - pos * num_features);
   const uint32_t vid = sorted_vid[pos];
-  if (vid == kNoKey) return;  // out of range or beyond the voxel cap: sorted behind every kept point
+  if (vid >= num_voxels) return;  // out of range or beyond the voxel cap: sorted behind every kept point
   const long long slot = pos - seg_start[vid];
   if (slot >= max_points) return;
   voxels[(static_cast<long long>(vid) * max_points + slot) * num_features + c] =
@@ -302,13 +307,13 @@ extern "C" int spc_voxelize(const float* points, int64_t n_points, int point_str
   SPC_LAUNCH_OK();
   size_t cub_bytes = L.cub_bytes;
   SPC_CUDA_OK(cub::DeviceScan::ExclusiveSum(ws + L.off_cub, cub_bytes, flag, rank, n, st));
-  int host[3] = {0, 0, 0};  // status, rank[n-1], flag[n-1]
-  SPC_CUDA_OK(cudaMemcpyAsync(&host[0], status, sizeof(int), cudaMemcpyDeviceToHost, st));
-  SPC_CUDA_OK(cudaMemcpyAsync(&host[1], rank + (n - 1), sizeof(int), cudaMemcpyDeviceToHost, st));
-  SPC_CUDA_OK(cudaMemcpyAsync(&host[2], flag + (n - 1), sizeof(int), cudaMemcpyDeviceToHost, st));
+  total_kernel<<<1, 1, 0, st>>>(rank, flag, n, status);
+  SPC_LAUNCH_OK();
+  int host[2] = {0, 0};  // status, voxels found
+  SPC_CUDA_OK(cudaMemcpyAsync(host, status, sizeof(host), cudaMemcpyDeviceToHost, st));
   SPC_CUDA_OK(cudaStreamSynchronize(st));
   if (host[0] != 0) return fail(host[0], "voxelize: hash table full (status %d)", host[0]);
-  const int64_t total_voxels = static_cast<int64_t>(host[1]) + host[2];
+  const int64_t total_voxels = host[1];
   const int64_t num_voxels = std::min<int64_t>(total_voxels, max_voxels);
   *num_voxels_host = num_voxels;
   if (num_voxels == 0) {
@@ -323,12 +328,15 @@ extern "C" int spc_voxelize(const float* points, int64_t n_points, int point_str
   SPC_LAUNCH_OK();
   cub_bytes = L.cub_bytes;
   SPC_CUDA_OK(cub::DeviceScan::ExclusiveSum(ws + L.off_cub, cub_bytes, counts, seg, static_cast<int>(num_voxels), st));
-  // stable: arrival order survives inside a voxel; dropped points (kNoKey) sort behind all others
+  // stable: arrival order survives inside a voxel; dropped points carry the key num_voxels and
+  // sort behind all others; only the bits that key needs are sorted
+  int bits = 1;
+  while (bits < 32 && (1ll << bits) <= num_voxels) ++bits;
   cub_bytes = L.cub_bytes;
-  SPC_CUDA_OK(cub::DeviceRadixSort::SortPairs(ws + L.off_cub, cub_bytes, sk_a, sk_b, sv_a, sv_b, n, 0, 32, st));
+  SPC_CUDA_OK(cub::DeviceRadixSort::SortPairs(ws + L.off_cub, cub_bytes, sk_a, sk_b, sv_a, sv_b, n, 0, bits, st));
   const long long work = static_cast<long long>(n) * num_features;
   scatter_points_kernel<<<vox_blocks(work), kVoxThreads, 0, st>>>(points, point_stride, num_features, sk_b, sv_b, seg,
-                                                                 n, max_points, voxels);
+                                                                 n, num_voxels, max_points, voxels);
   SPC_LAUNCH_OK();
   if (empty_mean) {
     fill_mean_kernel<<<vox_blocks(num_voxels * num_features), kVoxThreads, 0, st>>>(voxels, num_per_voxel, num_voxels,
