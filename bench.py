@@ -373,6 +373,28 @@ def run_op_bench(args):
                      voxels=int(idx.shape[0]), n_out=n_out, pairs=pairs, voxel_order=args.voxel_order)
                 bwd_bytes = idx.shape[0] * c * 2 + pairs * (c * 2 + 4) + kv * idx.shape[0] * 4
                 emit(name + "_bwd", timed(lambda: PL.avgpool_backward(g, pb, cnt), iters), bwd_bytes)
+    elif args.op == "dense":
+        # the step after the backbone: 8 samples, 128 channels, BEV volume [2, 200, 176], 60k rows per sample
+        import spconv_triton_b200.pytorch as sp
+        from spconv_triton_b200.scenes import uniform_batch
+
+        batch, shape, c = 8, [2, 200, 176], 128
+        idx = torch.from_numpy(uniform_batch(5, batch, 40000, tuple(shape))).to(dev)
+        key = ((idx[:, 0].long() * shape[0] + idx[:, 1]) * shape[1] + idx[:, 2]) * shape[2] + idx[:, 3]
+        idx = idx[torch.argsort(key)]  # the order a rulebook emits
+        feats = torch.randn(idx.shape[0], c, device=dev).half()
+        x = sp.SparseConvTensor(feats, idx, shape, batch)
+        vol = batch * shape[0] * shape[1] * shape[2]
+        nbytes = vol * c * 2 + 2 * idx.shape[0] * c * 2 + idx.shape[0] * 16
+
+        def torch_dense():
+            res = torch.zeros([batch, *shape, c], dtype=feats.dtype, device=dev)
+            il = idx.long()
+            res[il[:, 0], il[:, 1], il[:, 2], il[:, 3]] = feats
+            return res.permute(0, 4, 1, 2, 3).contiguous()
+
+        emit("dense_channels_first", timed(lambda: x.dense(), iters), nbytes, rows=int(idx.shape[0]), dense_elems=vol * c,
+             torch_definition_ms=timed(torch_dense, iters))
     elif args.op == "voxelize":
         # the step before the backbone: 8 LiDAR sweeps of 150k points -> voxels of 0.16 x 0.16 x 0.2 m
         from spconv_triton_b200.pytorch.utils import PointToVoxel
@@ -440,7 +462,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-baseline-seconds", type=float, default=20.0)
-    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm", "voxelize"],
+    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm", "voxelize", "dense"],
                     help="single-operator timings at the other configurations instead of the headline benchmark")
     ap.add_argument("--voxel-order", default="random", choices=["random", "sorted"],
                     help="--op pool: input voxel order (random = as a voxeliser emits them, sorted = as a previous layer's rulebook emits them)")

@@ -203,6 +203,22 @@ int spc_voxelize(const float* points, int64_t n_points, int point_stride, int nd
                  size_t workspace_bytes, float* voxels, int32_t* indices, int32_t* num_per_voxel,
                  int64_t* pc_voxel_id, int64_t* num_voxels_host, void* stream);
 
+/* ---- sparse -> dense (the step after the backbone) ----------------------- */
+
+/* Replaces SparseConvTensor.dense(), spconv_triton/pytorch/core.py:320-334
+ * (scatter_nd into zeros, then permute + contiguous for channels_first).
+ *   dense: [B, C, *spatial] when channels_first else [B, *spatial, C], elements of
+ *   elem_size bytes (2, 4 or 8; the bits are copied); zero-filled, then every
+ *   row's channels are written at its coordinate; spatial_shape is a HOST array.
+ *   Rows outside the volume are skipped.  spc_dense_gather is the gradient
+ *   (features[i, :] = dense[coordinate of row i], 0 for rows outside). */
+int spc_dense_scatter(const void* features, const int32_t* indices, int64_t n, int channels, int ndim,
+                      int batch_size, const int32_t* spatial_shape, int channels_first, int elem_size,
+                      void* dense, void* stream);
+int spc_dense_gather(const void* dense, const int32_t* indices, int64_t n, int channels, int ndim,
+                     int batch_size, const int32_t* spatial_shape, int channels_first, int elem_size,
+                     void* features, void* stream);
+
 /* ---- implicit gather-GEMM ---------------------------------------------- */
 
 /* Forward: replaces conv_forward, _impl/gemm.py:501-568.

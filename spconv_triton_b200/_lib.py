@@ -75,6 +75,8 @@ _PROTOTYPES = {
     "spc_rulebook_igemm_backward": (c_int, [POINTER(Geometry), _P, c_int64, c_int64, _P, c_size_t, _P, _P, _P,
                                             POINTER(c_uint32), c_int, c_int, _P, _P]),
     "spc_pairs_to_rowmajor": (c_int, [_P, c_int, c_int64, _P, _P]),
+    "spc_dense_scatter": (c_int, [_P, _P, c_int64, c_int, c_int, c_int, POINTER(ctypes.c_int32), c_int, c_int, _P, _P]),
+    "spc_dense_gather": (c_int, [_P, _P, c_int64, c_int, c_int, c_int, POINTER(ctypes.c_int32), c_int, c_int, _P, _P]),
     "spc_voxelize_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "spc_voxelize": (c_int, [_P, c_int64, c_int, c_int, c_int, POINTER(ctypes.c_float), POINTER(ctypes.c_float),
                              POINTER(ctypes.c_int32), c_int64, c_int, c_int, c_int, _P, c_size_t, _P, _P, _P, _P,

@@ -194,6 +194,14 @@ class SparseConvTensor(metaclass=SpConvTensorMeta):
                    sp.shape[0])
 
     def dense(self, channels_first: bool = True):
+        """Dense ``[B, C, *spatial]`` (or ``[B, *spatial, C]``) tensor (reference:
+        core.py:320-334).  CUDA features go through one zero fill and one scatter
+        kernel of the library instead of scatter_nd + permute + contiguous."""
+        feats = self.features
+        if (feats.is_cuda and self.indices.is_cuda and feats.element_size() in (2, 4, 8) and not feats.is_complex()
+                and len(self.spatial_shape) <= 4 and self.indices.shape[0] > 0):
+            return _DenseScatter.apply(feats, self.indices, self.batch_size, tuple(self.spatial_shape),
+                                       bool(channels_first))
         shape = [self.batch_size, *self.spatial_shape, self.features.shape[1]]
         res = scatter_nd(self.indices.to(self.features.device).long(), self.features, shape)
         if not channels_first:
@@ -215,6 +223,44 @@ class SparseConvTensor(metaclass=SpConvTensorMeta):
     def __iadd__(self, other: Union["SparseConvTensor", torch.Tensor]):
         self.features += self._features_of(other)
         return self
+
+
+def _dense_call(fn_name, src, indices, batch_size, spatial_shape, channels_first, dst):
+    import ctypes
+
+    from spconv_triton_b200 import _lib
+
+    shape = (ctypes.c_int32 * len(spatial_shape))(*[int(v) for v in spatial_shape])
+    with torch.cuda.device(src.device):
+        _lib.check(getattr(_lib.load(), fn_name)(
+            _lib.ptr(src), _lib.ptr(indices), int(indices.shape[0]), int(src.shape[1] if fn_name == "spc_dense_scatter"
+                                                                        else dst.shape[1]),
+            len(spatial_shape), int(batch_size), shape, int(channels_first), src.element_size(), _lib.ptr(dst),
+            _lib.current_stream(src.device)))
+    return dst
+
+
+class _DenseScatter(torch.autograd.Function):
+    """features [N, C] -> dense; the gradient gathers the dense gradient back per row."""
+
+    @staticmethod
+    def forward(ctx, features, indices, batch_size, spatial_shape, channels_first):
+        indices = indices.contiguous()
+        c = features.shape[1]
+        shape = [batch_size, c, *spatial_shape] if channels_first else [batch_size, *spatial_shape, c]
+        out = torch.empty(shape, dtype=features.dtype, device=features.device)
+        _dense_call("spc_dense_scatter", features.contiguous(), indices, batch_size, spatial_shape, channels_first, out)
+        ctx.save_for_backward(indices)
+        ctx.meta = (batch_size, spatial_shape, channels_first, c)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        (indices,) = ctx.saved_tensors
+        batch_size, spatial_shape, channels_first, c = ctx.meta
+        gfeat = torch.empty((indices.shape[0], c), dtype=grad.dtype, device=grad.device)
+        _dense_call("spc_dense_gather", grad.contiguous(), indices, batch_size, spatial_shape, channels_first, gfeat)
+        return gfeat, None, None, None, None
 
 
 def expand_nd(ndim: int, val) -> list[int]:
