@@ -150,11 +150,48 @@ class DeferredBackward:
         self.pending: list = []
 
 
+class LateTables:
+    """The input-side tables of a strided layer (pair_bwd, its masks and argsort),
+    not built yet.  An inference forward never reads them; an inverse layer that
+    reuses the rulebook, or anyone reading them from the indice_dict entry, calls
+    ``get()`` and they are built then, from the hash table the forward half left
+    in the workspace."""
+
+    def __init__(self, prepared, n_out, split_words, n_split, do_sort, mic):
+        self.p, self.n_out, self.split_words, self.n_split = prepared, n_out, split_words, n_split
+        self.do_sort, self.mic = do_sort, mic
+        self.value = None
+
+    def get(self):
+        if self.value is None:
+            p, dev = self.p, self.p.indices.device
+            kv, kvp = p.kv, (p.kv + 3) // 4 * 4
+            with torch.cuda.device(dev):
+                stream = torch.cuda.current_stream(dev)
+                for t in (p.workspace, p.indices):
+                    t.record_stream(stream)
+                pair_bwd = torch.empty((kv, p.n_in), dtype=torch.int32, device=dev)
+                pm_bwd = torch.empty((self.n_split, p.n_in, self.mic), dtype=torch.int32, device=dev)
+                ma_bwd = torch.empty((self.n_split, p.n_in), dtype=torch.int32, device=dev)
+                bwd_rm = torch.empty((p.n_in, kvp), dtype=torch.int32, device=dev)
+                _lib.check(_lib.load().spc_rulebook_igemm_backward(
+                    ctypes.byref(p.geom), _lib.ptr(p.indices), p.n_in, self.n_out, _lib.ptr(p.workspace),
+                    p.workspace.numel(), _lib.ptr(pair_bwd), _lib.ptr(pm_bwd), _lib.ptr(ma_bwd), self.split_words,
+                    self.n_split, int(bool(self.do_sort)), _lib.ptr(bwd_rm), _lib.current_stream(dev)))
+                pair_bwd._spc_rowmajor = bwd_rm
+            self.value = (pair_bwd, [pm_bwd[s] for s in range(self.n_split)],
+                          [ma_bwd[s] for s in range(self.n_split)])
+            self.p = None  # the workspace is no longer needed
+        return self.value
+
+
 _tls = threading.local()
 
 
 @contextlib.contextmanager
-def deferred_backward(defer: DeferredBackward):
+def deferred_backward(defer):
+    """``defer``: a DeferredBackward (build the input-side tables on its stream), the
+    string "late" (do not build them; attach a LateTables to the result) or None."""
     old = getattr(_tls, "defer", None)
     _tls.defer = defer
     try:
@@ -199,6 +236,13 @@ def igemm_pairs(indices, batch_size, spatial_shape, ksize, stride, padding, dila
         bwd_rm = torch.empty((p.n_in, kvp), dtype=torch.int32, device=dev) if want_bwd else None
         split_words = (ctypes.c_uint32 * n_split)(*[int(m[0]) for m in masks])
         defer = getattr(_tls, "defer", None) if want_bwd_masks else None
+        late = None
+        if defer == "late":
+            # the forward half only; the other half waits until somebody reads it
+            late = LateTables(p, n_out, None, n_split, do_sort, mic)
+            want_bwd = want_bwd_masks = False
+            pair_bwd = pm_bwd = ma_bwd = bwd_rm = None
+            defer = None
         lib = _lib.load()
         _lib.check(lib.spc_rulebook_igemm(
             ctypes.byref(p.geom), _lib.ptr(p.indices), p.n_in, n_out, _lib.ptr(p.workspace),
@@ -225,6 +269,9 @@ def igemm_pairs(indices, batch_size, spatial_shape, ksize, stride, padding, dila
             defer.pending.append((done, late))
         npl = torch.zeros(kv, dtype=torch.int32, device=dev)
         pair_fwd._spc_rowmajor = fwd_rm
+        if late is not None:
+            late.split_words = split_words
+            pair_fwd._spc_late = late
         if want_bwd:
             pair_bwd._spc_rowmajor = bwd_rm
     pb = pair_bwd if want_bwd else torch.Tensor()

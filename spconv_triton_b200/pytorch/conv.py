@@ -26,6 +26,7 @@ from spconv_triton_b200.tools import nullcontext  # noqa: F401
 
 from . import functional as Fsp
 from . import ops
+from ._impl import pairs as _pairs
 from .core import ImplicitGemmIndiceData, IndiceData, SparseConvTensor, expand_nd, register_implicit_gemm_indice_data
 from .modules import SparseModule
 
@@ -185,13 +186,15 @@ class SparseConvolutionBase:
         planner = x._planner
         res = planner.take(self, x) if planner is not None else None
         if res is None:
-            res = self._generate(
-                x, out_tensor.benchmark_record, name,
-                lambda: ops.get_indice_pairs_implicit_gemm(
-                    x.indices, x.batch_size, x.spatial_shape, self.algo, ksize=self.kernel_size,
-                    stride=self.stride, padding=self.padding, dilation=self.dilation,
-                    out_padding=self.output_padding, subm=self.subm, transpose=self.transposed,
-                    is_train=(not self.subm) or training, alloc=x.thrust_allocator, timer=x._timer))
+            # an inference forward of a strided layer leaves the input-side tables pending
+            with _pairs.deferred_backward(None if (training or self.subm) else "late"):
+                res = self._generate(
+                    x, out_tensor.benchmark_record, name,
+                    lambda: ops.get_indice_pairs_implicit_gemm(
+                        x.indices, x.batch_size, x.spatial_shape, self.algo, ksize=self.kernel_size,
+                        stride=self.stride, padding=self.padding, dilation=self.dilation,
+                        out_padding=self.output_padding, subm=self.subm, transpose=self.transposed,
+                        is_train=(not self.subm) or training, alloc=x.thrust_allocator, timer=x._timer))
         if self.indice_key is not None:
             register_implicit_gemm_indice_data(
                 indice_dict, self.indice_key, res, x.indices, is_subm=self.subm,

@@ -64,7 +64,25 @@ class ImplicitGemmIndiceData(_Record):
                  mask_argsort_fwd_splits, mask_argsort_bwd_splits, masks, spatial_shape, out_spatial_shape,
                  is_subm: bool, algo: ConvAlgo, ksize, stride, dilation, padding, in_voxel_num: Any = None,
                  out_voxel_num: Any = None):
+        self._late = None
         self._assign(locals())
+
+    # The input-side tables of a strided layer may be pending (an inference forward does
+    # not build them); reading any of the three attributes builds them.
+    def _resolved(self, name):
+        late = self.__dict__.get("_late")
+        if late is not None:
+            self.__dict__["_late"] = None
+            pair_bwd, pm_bwd, ma_bwd = late.get()
+            self.__dict__.update(_pair_bwd=pair_bwd, _pair_mask_bwd_splits=pm_bwd, _mask_argsort_bwd_splits=ma_bwd)
+        return self.__dict__[name]
+
+    pair_bwd = property(lambda self: self._resolved("_pair_bwd"),
+                        lambda self, v: self.__dict__.__setitem__("_pair_bwd", v))
+    pair_mask_bwd_splits = property(lambda self: self._resolved("_pair_mask_bwd_splits"),
+                                    lambda self, v: self.__dict__.__setitem__("_pair_mask_bwd_splits", v))
+    mask_argsort_bwd_splits = property(lambda self: self._resolved("_mask_argsort_bwd_splits"),
+                                       lambda self, v: self.__dict__.__setitem__("_mask_argsort_bwd_splits", v))
 
 
 def register_implicit_gemm_indice_data(indice_dict, indice_key, res, indices, *, is_subm, spatial_shape,
@@ -73,9 +91,11 @@ def register_implicit_gemm_indice_data(indice_dict, indice_key, res, indices, *,
     ``indice_key``; a key that already exists is an error (reference: core.py:123-164)."""
     if indice_key in indice_dict:
         raise AssertionError(f"your indice key {indice_key} already exists in this sparse tensor.")
-    indice_dict[indice_key] = ImplicitGemmIndiceData(
+    data = ImplicitGemmIndiceData(
         res[0], indices, res[2], res[3], res[4], res[5], res[6], res[7], res[8], spatial_shape,
         out_spatial_shape, is_subm, algo, ksize, stride, dilation, padding)
+    data._late = getattr(res[2], "_spc_late", None)
+    indice_dict[indice_key] = data
 
 
 def scatter_nd(indices, updates, shape):

@@ -134,7 +134,8 @@ class RulebookPlanner:
             self.indices, self.spatial_shape = datas.out_indices, out_shape
             return True
         src = self.indices
-        with torch.cuda.stream(self.side), _pairs.deferred_backward(self.late):
+        # training: the input-side tables go to the third stream; inference: they stay pending
+        with torch.cuda.stream(self.side), _pairs.deferred_backward(self.late if conv.training else "late"):
             res = ops.get_indice_pairs_implicit_gemm(
                 src, self.batch_size, self.spatial_shape, conv.algo, ksize=conv.kernel_size,
                 stride=conv.stride, padding=conv.padding, dilation=conv.dilation,

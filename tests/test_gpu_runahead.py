@@ -146,3 +146,30 @@ def test_unknown_modules_end_the_plan(sp):
         finally:
             constants.SPCONV_RULEBOOK_RUNAHEAD = old
     assert torch.equal(outs[0].features, outs[1].features) and torch.equal(outs[0].indices, outs[1].indices)
+
+
+@pytest.mark.parametrize("runahead", [False, True])
+def test_pending_input_side_tables(sp, runahead):
+    """An inference forward of a strided layer leaves pair_bwd and its masks unbuilt;
+    reading them from the indice_dict entry builds exactly what a training forward builds."""
+    from spconv_triton_b200 import constants
+    from spconv_triton_b200.pytorch._impl import pairs
+
+    shape, batch = [20, 36, 32], 2
+    idx, feats = _scene(21, 9000, batch, shape, 8, torch.float16)
+    net = sp.SparseSequential(sp.SubMConv3d(8, 16, 3, indice_key="s"),
+                              sp.SparseConv3d(16, 16, 3, stride=2, padding=1, indice_key="d")).to(DEV).half().eval()
+    old, constants.SPCONV_RULEBOOK_RUNAHEAD = constants.SPCONV_RULEBOOK_RUNAHEAD, runahead
+    try:
+        with torch.no_grad():
+            out = net(sp.SparseConvTensor(feats, idx, shape, batch))
+    finally:
+        constants.SPCONV_RULEBOOK_RUNAHEAD = old
+    entry = out.indice_dict["d"]
+    assert entry._late is not None  # nothing built yet
+    full = pairs.igemm_pairs(idx, batch, shape, [3] * 3, [2] * 3, [1] * 3, [1] * 3, [0] * 3, False, False, True, False)
+    assert torch.equal(entry.pair_bwd, full[3])
+    assert entry._late is None
+    assert torch.equal(entry.pair_mask_bwd_splits[0], full[5][0])
+    assert torch.equal(entry.mask_argsort_bwd_splits[0], full[7][0])
+    assert torch.equal(entry.pair_fwd, full[2]) and torch.equal(entry.out_indices, full[0])
