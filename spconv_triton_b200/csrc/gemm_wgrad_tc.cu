@@ -277,39 +277,62 @@ wgrad_tc_kernel(const __grid_constant__ WgParams p) {
     }
   } else {
     // ---------------- MMA issuer ----------------
+    // This one thread paces the CTA: the loop keeps running descriptor words (a stage advance
+    // is one add to the address field) and unrolls the four 16-pair steps of a stage.
     if (lane == 0) {
       // fp32 accumulate, both operands MN-major, M = 128, N = c_in
       const uint32_t idesc = (1u << 4) | (TcType<T>::fmt << 7) | (TcType<T>::fmt << 10) | (1u << 15) | (1u << 16) |
                              (static_cast<uint32_t>(p.c_in >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
       const uint32_t g_type = wg_layout_type(p.g_row_bytes), f_type = wg_layout_type(p.f_row_bytes);
+      const uint32_t g_addr0 = smem_u32(stage_base);
+      const uint64_t a_desc0 = make_desc(g_addr0, kPairsPerStage * p.g_row_bytes, 8 * p.g_row_bytes, g_type);
+      const uint64_t b_desc0 = make_desc(g_addr0 + p.g_stage_bytes, kPairsPerStage * p.f_row_bytes, 8 * p.f_row_bytes, f_type);
+      const uint32_t a_hi = static_cast<uint32_t>(a_desc0 >> 32), b_hi = static_cast<uint32_t>(b_desc0 >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(a_desc0), b_lo0 = static_cast<uint32_t>(b_desc0);
+      const uint32_t stage_step = static_cast<uint32_t>(stage_bytes >> 4);
+      const uint32_t a_step = static_cast<uint32_t>(UMMA_K * p.g_row_bytes / 16);
+      const uint32_t b_step = static_cast<uint32_t>(UMMA_K * p.f_row_bytes / 16);
+      const uint32_t info0 = smem_u32(info);
+      uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full, empty = bar_empty, inf = info0;
       int stage = 0;
       uint32_t full_parity = 0, accumulate = 0;
       bool ok = true;
       while (true) {
-        if (!mbar_wait(bar_full + 8 * stage, full_parity)) {
+        if (!mbar_wait(full, full_parity)) {
           ok = false;
           break;
         }
         fence_proxy_async();  // stage was written by cp.async (generic proxy)
         tc_fence_after();
-        const StageInfo si = info[stage];
-        const uint32_t g_addr = smem_u32(stage_base + static_cast<size_t>(stage) * stage_bytes);
-        const uint32_t f_addr = g_addr + p.g_stage_bytes;
-        const uint64_t a_desc = make_desc(g_addr, kPairsPerStage * p.g_row_bytes, 8 * p.g_row_bytes, g_type);
-        const uint64_t b_desc = make_desc(f_addr, kPairsPerStage * p.f_row_bytes, 8 * p.f_row_bytes, f_type);
-        for (int ks = 0; ks < si.ksteps; ++ks) {
-          tc_mma<false>(tmem_base, a_desc + static_cast<uint64_t>(ks * (UMMA_K * p.g_row_bytes / 16)),
-                        b_desc + static_cast<uint64_t>(ks * (UMMA_K * p.f_row_bytes / 16)), idesc, accumulate);
-          accumulate = 1;
-        }
-        if (si.last) {
+        uint32_t ksteps;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(ksteps) : "r"(inf) : "memory");
+        if (ksteps == 0) {  // terminator
           tc_commit(bar_accum);
           break;
         }
-        tc_commit(bar_empty + 8 * stage);
+#pragma unroll
+        for (int ks = 0; ks < kPairsPerStage / UMMA_K; ++ks) {
+          if (static_cast<uint32_t>(ks) < ksteps) {
+            const uint64_t a_desc = (static_cast<uint64_t>(a_hi) << 32) | (a_lo + a_step * ks);
+            const uint64_t b_desc = (static_cast<uint64_t>(b_hi) << 32) | (b_lo + b_step * ks);
+            tc_mma<false>(tmem_base, a_desc, b_desc, idesc, accumulate);
+            accumulate = 1;
+          }
+        }
+        tc_commit(empty);
+        a_lo += stage_step;
+        b_lo += stage_step;
+        full += 8;
+        empty += 8;
+        inf += static_cast<uint32_t>(sizeof(StageInfo));
         if (++stage == p.stages) {
           stage = 0;
           full_parity ^= 1;
+          a_lo = a_lo0;
+          b_lo = b_lo0;
+          full = bar_full;
+          empty = bar_empty;
+          inf = info0;
         }
       }
       if (!ok) {
@@ -364,7 +387,9 @@ bool wgrad_tc_supported(int c_in, int c_out, int kv, int dtype) {
 WgradSplit wgrad_tc_split(int64_t n_out, int c_in, int c_out, int kv) {
   WgradSplit s;
   const int64_t tiles = static_cast<int64_t>(kv) * ceil_div(c_out, tc::kTileM);
-  int64_t want = ceil_div(2 * 148, std::max<int64_t>(tiles, 1));
+  // several CTAs per resident slot: offsets differ a lot in how many pairs they have (the centre
+  // offset of a submanifold layer has all of them), and surplus CTAs even that out
+  int64_t want = ceil_div(16 * 148, std::max<int64_t>(tiles, 1));
   const int64_t by_len = std::max<int64_t>(1, n_out / 4096);
   want = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(want, by_len), 64));
   s.splits = static_cast<int>(want);
