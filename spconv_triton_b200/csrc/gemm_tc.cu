@@ -85,7 +85,9 @@ gather_gemm_tc_kernel(const __grid_constant__ TcParams p) {
   const int warp = tid >> 5, lane = tid & 31;
   // once any CTA has given up on a wait, the remaining CTAs return at once
   if (*reinterpret_cast<volatile int*>(p.status) != 0) return;
-  const long long m0 = static_cast<long long>(blockIdx.x) * kTileM;
+  // tiles are taken from the END of the mask-sorted order first: those rows have the most
+  // kernel offsets, and starting the long tiles first leaves the short ones to fill the tail
+  const long long m0 = static_cast<long long>(gridDim.x - 1 - blockIdx.x) * kTileM;
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = smem_u32(bars + kMaxStages);
   const uint32_t bar_accum = smem_u32(bars + 2 * kMaxStages);
