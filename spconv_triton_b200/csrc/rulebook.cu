@@ -281,14 +281,16 @@ enum Counter { kUniqueCount = 0, kStatus = 1 };
 template <int ND, bool K64>
 __global__ void __launch_bounds__(kThreads)
 insert_inputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n,
-                     Table<K64> tin, int* counters) {
+                     Table<K64> tin, int* counters, uint32_t* __restrict__ bitmap) {
   const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
   if (j >= n) return;
   int c[ND + 1];
   load_coord<ND>(idx, j, c);
   using key_t = typename Table<K64>::key_t;
-  if (!tin.insert_min(static_cast<key_t>(in_key_of<ND>(g, c)), static_cast<uint32_t>(j)))
+  const long long key = in_key_of<ND>(g, c);
+  if (!tin.insert_min(static_cast<key_t>(key), static_cast<uint32_t>(j)))
     atomicExch(&counters[kStatus], SPC_ERR_HASH_TABLE_FULL);
+  if (bitmap != nullptr) atomicOr(&bitmap[key >> 5], 1u << (key & 31));
 }
 
 // One thread per input row walks the kv offsets and inserts each candidate
@@ -368,7 +370,8 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
                 const typename Table<K64>::key_t* __restrict__ sorted_out, long long n_out,
                 Table<K64> tin, int32_t* __restrict__ out_indices, int32_t* __restrict__ pair_fwd,
                 int32_t* __restrict__ pair_bwd, uint32_t* __restrict__ words, int mic,
-                int32_t* __restrict__ fwd_rm, int32_t* __restrict__ bwd_rm, int kvp) {
+                int32_t* __restrict__ fwd_rm, int32_t* __restrict__ bwd_rm, int kvp,
+                const uint32_t* __restrict__ bitmap) {
   using key_t = typename Table<K64>::key_t;
   const long long r = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
   if (r >= n_out) return;
@@ -384,9 +387,52 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
   Odometer<ND> od;
   od.reset();
   uint32_t word = 0;
+  // Non-transposed layers: the input cell of offset (p_0, .., p_last) is base + sum p_d * step_d, and
+  // whether it lies inside the grid is one bit per dimension; both are set up once per row so that
+  // the loop over the kv offsets does no coordinate arithmetic.
+  bool fast = !g.transpose;
+  long long base = o[0];
+  long long step[ND];
+  uint32_t inside[ND];
+  if (fast) {
+    long long mult = 1;
+#pragma unroll
+    for (int d = ND - 1; d >= 0; --d) {
+      step[d] = mult * g.dil[d];
+      mult *= g.in_shape[d];
+      if (g.ksize[d] > 32) fast = false;
+    }
+  }
+  if (fast) {
+#pragma unroll
+    for (int d = 0; d < ND; ++d) {
+      const int x0 = o[d + 1] * g.stride[d] - g.pad[d];
+      base = base * g.in_shape[d] + x0;
+      uint32_t m = 0;
+      for (int q = 0; q < g.ksize[d]; ++q) {
+        const int x = x0 + q * g.dil[d];
+        m |= static_cast<uint32_t>(x >= 0 && x < g.in_shape[d]) << q;
+      }
+      inside[d] = m;
+    }
+  }
   for (int k = 0; k < g.kv; ++k) {
-    const long long key = in_key_from_output<ND>(g, o, od.pos);
-    const int j = key >= 0 ? tin.find(static_cast<key_t>(key)) : -1;
+    long long key;
+    if (fast) {
+      uint32_t ok = 1u;
+      key = base;
+#pragma unroll
+      for (int d = 0; d < ND; ++d) {
+        ok &= inside[d] >> od.pos[d];
+        key += od.pos[d] * step[d];
+      }
+      if (!(ok & 1u)) key = -1;
+    } else {
+      key = in_key_from_output<ND>(g, o, od.pos);
+    }
+    bool there = key >= 0;
+    if (there && bitmap != nullptr) there = (__ldg(&bitmap[key >> 5]) >> (key & 31)) & 1u;
+    const int j = there ? tin.find(static_cast<key_t>(key)) : -1;
     pair_fwd[static_cast<long long>(k) * n_out + r] = j;
     if (SUBM_BWD) {
       pair_bwd[static_cast<long long>(g.kv - 1 - k) * n_out + r] = j;
@@ -609,6 +655,7 @@ struct Layout {
   size_t off_counters, off_tin, off_tin_vals, off_tout, off_tout_vals, off_uniq, off_sorted;
   size_t off_words, off_keys_a, off_keys_b, off_vals_a, off_vals_b, off_cub, off_native;
   size_t cub_bytes, total;
+  size_t off_bitmap, bitmap_bytes;  // occupancy bitmap of the input grid (0 bytes: not used)
 };
 
 uint32_t pow2_at_least(int64_t v) {
@@ -710,6 +757,11 @@ Layout make_layout(const Geo& g, int64_t n_in) {
   L.off_vals_b = take(static_cast<size_t>(n_max) * 4);
   L.off_cub = take(L.cub_bytes);
   L.off_native = take(static_cast<size_t>(L.n_blocks_native) * g.kv * 4);
+  // One bit per input cell, when that is small enough to live in L2 beside the hash table: most of
+  // the kv neighbour cells of a voxel are empty, and a bit test (neighbours share bytes) then
+  // answers "absent" without a hash probe.
+  L.bitmap_bytes = (!L.k64 && vol_in / 8.0 <= 24.0 * 1024 * 1024) ? align_up(static_cast<size_t>(vol_in / 8.0) + 4, 256) : 0;
+  L.off_bitmap = take(L.bitmap_bytes);
   L.total = off;
   return L;
 }
@@ -746,7 +798,9 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
   SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin, 0xFF, static_cast<size_t>(L.cap_in) * 8, st));
   if (K64) SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin_vals, 0x7F, static_cast<size_t>(L.cap_in) * 4, st));
   Table<K64> tin = table_at<K64>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
-  insert_inputs_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, tin, counters);
+  uint32_t* bitmap = L.bitmap_bytes ? reinterpret_cast<uint32_t*>(ws + L.off_bitmap) : nullptr;
+  if (bitmap != nullptr) SPC_CUDA_OK(cudaMemsetAsync(bitmap, 0, L.bitmap_bytes, st));
+  insert_inputs_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, tin, counters, bitmap);
   SPC_LAUNCH_OK();
   if (g.subm) {
     *n_out_host = n_in;
@@ -842,12 +896,13 @@ int igemm_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, 
   Table<K64> tout = table_at<K64>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
   const key_t* sorted = reinterpret_cast<const key_t*>(ws + L.off_sorted);
   uint32_t* words = reinterpret_cast<uint32_t*>(ws + L.off_words);
+  const uint32_t* bitmap = L.bitmap_bytes ? reinterpret_cast<const uint32_t*>(ws + L.off_bitmap) : nullptr;
   if (g.subm && pair_bwd != nullptr)
     fill_fwd_kernel<ND, K64, true><<<blocks_for(n_out), kThreads, 0, st>>>(
-        g, idx, sorted, n_out, tin, out_indices, pair_fwd, pair_bwd, words, L.mic, fwd_rm, bwd_rm, kvp);
+        g, idx, sorted, n_out, tin, out_indices, pair_fwd, pair_bwd, words, L.mic, fwd_rm, bwd_rm, kvp, bitmap);
   else
     fill_fwd_kernel<ND, K64, false><<<blocks_for(n_out), kThreads, 0, st>>>(
-        g, idx, sorted, n_out, tin, out_indices, pair_fwd, nullptr, words, L.mic, fwd_rm, nullptr, kvp);
+        g, idx, sorted, n_out, tin, out_indices, pair_fwd, nullptr, words, L.mic, fwd_rm, nullptr, kvp, bitmap);
   SPC_LAUNCH_OK();
   int rc = emit_masks(L, ws, n_out, g.kv, split_masks, n_split, do_sort, mask_fwd, argsort_fwd, st);
   if (rc != SPC_OK) return rc;
