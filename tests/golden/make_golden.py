@@ -1,7 +1,7 @@
 """Generate the golden vectors under tests/golden/ from the reference itself.
 
 Run once in a container that has the reference checkout (read-only) at
-$SPCONV_REFERENCE_ROOT (default /root/reference):
+$SPCONV_REFERENCE_ROOT:
 
     python tests/golden/make_golden.py
 
@@ -29,7 +29,7 @@ import os
 import sys
 from pathlib import Path
 
-REF = os.environ.get("SPCONV_REFERENCE_ROOT", "/root/reference")
+REF = os.environ["SPCONV_REFERENCE_ROOT"]  # the read-only reference checkout
 OUT = Path(__file__).parent
 
 os.environ["TRITON_INTERPRET"] = "1"

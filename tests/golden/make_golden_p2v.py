@@ -1,7 +1,6 @@
 """Generate tests/golden/ref_p2v.pt: golden vectors of the point-to-voxel step.
 
-Run once where the reference checkout is readable at $SPCONV_REFERENCE_ROOT
-(default /root/reference):
+Run once where the reference checkout is readable at $SPCONV_REFERENCE_ROOT:
 
     python tests/golden/make_golden_p2v.py
 
@@ -23,7 +22,7 @@ from pathlib import Path
 
 import torch
 
-REF = Path(os.environ.get("SPCONV_REFERENCE_ROOT", "/root/reference"))
+REF = Path(os.environ["SPCONV_REFERENCE_ROOT"])  # the read-only reference checkout
 OUT = Path(__file__).parent / "ref_p2v.pt"
 
 spec = importlib.util.spec_from_file_location("ref_p2v_utils", REF / "spconv_triton" / "pytorch" / "utils.py")
