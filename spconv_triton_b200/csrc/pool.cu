@@ -195,43 +195,46 @@ struct PoolGeom { int nt, tpb, rpb; };
 // Each warp takes kGroupIters consecutive row groups and loads the table entries
 // of the next group before it gathers for the current one, so a table latency is
 // exposed once per warp and gathers are in flight the rest of the time.
-constexpr int kGroupMaxE = 8;   // table entries per lane per round (32 / nt)
 constexpr int kGroupIters = 8;  // row groups per warp
 
-template <typename T, int VEC, int U, int OP>
+template <typename T, int VEC, int U, int OP, int LGNT>
 __global__ void __launch_bounds__(256)
 pool_group_kernel(const T* __restrict__ src, const T* __restrict__ own, const T* __restrict__ ref,
                   const int32_t* __restrict__ table, const int32_t* __restrict__ aux_in, T* __restrict__ dst,
-                  int32_t* __restrict__ aux_out, long long n_rows, int channels, int kv, int lg_nt) {
+                  int32_t* __restrict__ aux_out, long long n_rows, int channels, int kv) {
+  // the threads per row are a compile-time power of two: the entry loops below unroll to
+  // exactly 32 / nt loads, ballots and selects
+  constexpr int lg_nt = LGNT;
+  constexpr int kE = 32 >> LGNT;  // table entries per lane per round == rows per warp
   constexpr int B = PoolTune<OP>::in_flight / U > 0 ? PoolTune<OP>::in_flight / U : 1;
   constexpr unsigned kFull = 0xffffffffu;
-  const int nt = 1 << lg_nt;
+  constexpr int nt = 1 << lg_nt;
   const int lane = threadIdx.x & 31;
   const int kl = lane & (nt - 1), gbase = lane - kl;
   const unsigned gmask = nt == 32 ? kFull : ((1u << nt) - 1u);
   const int c0 = kl * VEC, cstep = nt * VEC;
-  const int per_lane = 32 >> lg_nt;  // table entries per lane per round == rows per warp
+  constexpr int per_lane = kE;
   const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long row_first = warp_id * kGroupIters * per_lane + (lane >> lg_nt);
 
-  auto load_entries = [&](long long row, int k0, int (&v)[kGroupMaxE]) {
+  auto load_entries = [&](long long row, int k0, int (&v)[kE]) {
 #pragma unroll
-    for (int e = 0; e < kGroupMaxE; ++e) {
+    for (int e = 0; e < kE; ++e) {
       const int k = k0 + e * nt + kl;
       v[e] = (row < n_rows && e < per_lane && k < kv) ? __ldg(&table[static_cast<long long>(k) * n_rows + row]) : -1;
     }
   };
 
-  int vn[kGroupMaxE];
+  int vn[kE];
   load_entries(row_first, 0, vn);
 #pragma unroll 1
   for (int it = 0; it < kGroupIters; ++it) {
     const long long row = row_first + static_cast<long long>(it) * per_lane;
     if (row - (lane >> lg_nt) >= n_rows) break;  // warp-uniform: the whole group is past the end
     const bool live = row < n_rows;
-    int v[kGroupMaxE];
+    int v[kE];
 #pragma unroll
-    for (int e = 0; e < kGroupMaxE; ++e) v[e] = vn[e];
+    for (int e = 0; e < kE; ++e) v[e] = vn[e];
     if (it + 1 < kGroupIters) load_entries(row + per_lane, 0, vn);
 
     PoolRow<T, VEC, U, OP> pr;
@@ -240,7 +243,7 @@ pool_group_kernel(const T* __restrict__ src, const T* __restrict__ own, const T*
       if (k0 != 0) load_entries(row, k0, v);
       unsigned gm = 0;
 #pragma unroll
-      for (int e = 0; e < kGroupMaxE; ++e) {
+      for (int e = 0; e < kE; ++e) {
         if (e < per_lane) {  // warp-uniform
           const unsigned m = __ballot_sync(kFull, v[e] >= 0);
           gm |= ((m >> gbase) & gmask) << (e * nt);
@@ -254,7 +257,7 @@ pool_group_kernel(const T* __restrict__ src, const T* __restrict__ own, const T*
           const int e = p >> lg_nt;
           int mine = v[0];
 #pragma unroll
-          for (int q = 1; q < kGroupMaxE; ++q) mine = e == q ? v[q] : mine;
+          for (int q = 1; q < kE; ++q) mine = e == q ? v[q] : mine;
           const int got = __shfl_sync(kFull, mine, gbase + (p & (nt - 1)));
           j[b] = gm ? got : -1;
           gm &= gm - 1;
@@ -343,8 +346,13 @@ void pool_launch_u(const T* src, const T* own, const T* ref, const int32_t* tabl
     int lg = 0;
     while ((1 << lg) < g.nt) ++lg;
     const long long warps = ceil_div(static_cast<long long>(n_rows), (32 >> lg) * kGroupIters);
-    pool_group_kernel<T, VEC, U, OP><<<static_cast<unsigned>(ceil_div(warps, 8)), 256, 0, st>>>(
-        src, own, ref, table, aux_in, dst, aux_out, n_rows, channels, kv, lg);
+    const unsigned blocks = static_cast<unsigned>(ceil_div(warps, 8));
+    switch (lg) {
+      case 2: pool_group_kernel<T, VEC, U, OP, 2><<<blocks, 256, 0, st>>>(src, own, ref, table, aux_in, dst, aux_out, n_rows, channels, kv); break;
+      case 3: pool_group_kernel<T, VEC, U, OP, 3><<<blocks, 256, 0, st>>>(src, own, ref, table, aux_in, dst, aux_out, n_rows, channels, kv); break;
+      case 4: pool_group_kernel<T, VEC, U, OP, 4><<<blocks, 256, 0, st>>>(src, own, ref, table, aux_in, dst, aux_out, n_rows, channels, kv); break;
+      default: pool_group_kernel<T, VEC, U, OP, 5><<<blocks, 256, 0, st>>>(src, own, ref, table, aux_in, dst, aux_out, n_rows, channels, kv); break;
+    }
   } else {
     pool_compact_kernel<T, VEC, U, OP><<<grid, threads, 0, st>>>(src, own, ref, table, aux_in, dst, aux_out,
                                                                 n_rows, channels, kv, g);
