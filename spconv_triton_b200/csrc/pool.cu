@@ -92,12 +92,17 @@ __device__ __forceinline__ Pack<__nv_bfloat16, 8> pack<__nv_bfloat16, 8>(const f
 }
 
 enum PoolOp { kMaxFwd = 0, kAvgFwd = 1, kAvgBwd = 2, kMaxBwd = 3 };
-// Independent 16-byte gathers one thread keeps in flight, and 16-byte vectors of
-// a row one thread owns.  Max backward reads two rows per table entry and keeps
-// its own row in registers, so it runs with half of each (measured best on B200:
-// 116 registers and 2 CTAs per SM for the others, 80 and 3 for max backward).
-template <int OP> struct PoolTune { static constexpr int in_flight = 8, max_u = 4; };
-template <> struct PoolTune<3> { static constexpr int in_flight = 2, max_u = 2; };
+// Independent 16-byte gathers one thread keeps in flight (rows in flight = in_flight / U), and
+// 16-byte vectors of a row one thread owns, per operator; each pair is the measured best on B200
+// for 512-byte rows (C = 256 fp16): max forward has few present entries per row and gains from
+// four rows in flight with two vectors each (0.26 ms = 0.81 of the copy peak, against 0.31 with
+// 4 x 2); average forward over a 3^3 window prefers four vectors and one row; max backward
+// reads two rows per entry and keeps its own row in registers, so it runs with less of each.
+template <int OP> struct PoolTune;
+template <> struct PoolTune<0> { static constexpr int in_flight = 8, max_u = 2; };  // kMaxFwd
+template <> struct PoolTune<1> { static constexpr int in_flight = 4, max_u = 4; };  // kAvgFwd
+template <> struct PoolTune<2> { static constexpr int in_flight = 8, max_u = 2; };  // kAvgBwd
+template <> struct PoolTune<3> { static constexpr int in_flight = 2, max_u = 2; };  // kMaxBwd
 constexpr int kChunk = 32;    // table entries of one row compacted per pass (one per lane)
 constexpr int kMaxRows = 64;  // rows per CTA
 
