@@ -97,12 +97,13 @@ enum PoolOp { kMaxFwd = 0, kAvgFwd = 1, kAvgBwd = 2, kMaxBwd = 3 };
 // for 512-byte rows (C = 256 fp16): max forward has few present entries per row and gains from
 // four rows in flight with two vectors each (0.26 ms = 0.81 of the copy peak, against 0.31 with
 // 4 x 2); average forward over a 3^3 window prefers four vectors and one row; max backward
-// reads two rows per entry and keeps its own row in registers, so it runs with less of each.
+// reads two rows per entry and keeps its own row in registers: one vector and one row per thread
+// (more resident threads) is best for it.
 template <int OP> struct PoolTune;
 template <> struct PoolTune<0> { static constexpr int in_flight = 8, max_u = 2; };  // kMaxFwd
 template <> struct PoolTune<1> { static constexpr int in_flight = 4, max_u = 4; };  // kAvgFwd
 template <> struct PoolTune<2> { static constexpr int in_flight = 8, max_u = 2; };  // kAvgBwd
-template <> struct PoolTune<3> { static constexpr int in_flight = 2, max_u = 2; };  // kMaxBwd
+template <> struct PoolTune<3> { static constexpr int in_flight = 1, max_u = 1; };  // kMaxBwd
 constexpr int kChunk = 32;    // table entries of one row compacted per pass (one per lane)
 constexpr int kMaxRows = 64;  // rows per CTA
 
