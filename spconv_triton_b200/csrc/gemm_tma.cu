@@ -74,6 +74,8 @@ struct TmaParams {
   int src_rows;  // rows of the gathered matrix; also the "absent row" index
   int n_dim, r_dim, kv;
   int stages, a_stage_bytes, b_stage_bytes, tmem_cols;
+  int group_rows;  // kernel offsets voted on together: min(kv, 32); sizes the table tile in shared memory
+  int epi_pad;     // output channels rounded up to 16; sizes the epilogue scale / shift arrays
   int a_row_bytes, b_row_bytes;  // swizzle span of the A rows / of the MN-major B rows
   int* status;
 };
@@ -82,13 +84,20 @@ __host__ __device__ inline uint32_t layout_type_for(int row_bytes) {
   return row_bytes == 128 ? 2u : (row_bytes == 64 ? 4u : 6u);
 }
 
-constexpr int kIssueWarps = 8;                       // warps that issue the feature-row copies
-constexpr int kIssueThreads = kIssueWarps * 32;       // 256
-constexpr int kMmaWarp = kIssueWarps;                 // warp 8
-constexpr int kThreadsHybrid = kIssueThreads + 32;    // 288
+// Four copy warps + the MMA warp: 160 threads.  A small CTA lets three or four of them share an SM
+// (shared memory permitting), i.e. three or four MMA issuers and that many tiles whose table
+// load, pipeline drain and epilogue overlap the others' stages: 64 -> 64 went from 166 us with
+// 2 x 288 threads to 141 us with 3 x 160, 32 -> 32 from 149 us to 103 us with 4 x 160.
+constexpr int kIssueWarps = 4;                        // warps that issue the feature-row copies
+constexpr int kIssueThreads = kIssueWarps * 32;       // 128
+constexpr int kMmaWarp = kIssueWarps;                 // warp 4
+constexpr int kThreadsHybrid = kIssueThreads + 32;    // 160
+constexpr int kRowsPerThread = kTileM * 8 / kIssueThreads;  // 8: a thread copies one 16-byte piece of 8 rows
+constexpr int kRowStep = kTileM / kRowsPerThread;            // 16
+constexpr int kMaxCtasPerSm = 4;                      // 4 x 160 threads x 96 registers fit the register file
 
 template <typename T, typename TO, bool B_MN>
-__global__ void __maxnreg__(80)
+__global__ void __maxnreg__(96)
 gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constant__ CUtensorMap map_b) {
   constexpr int ELEM = sizeof(T);
   constexpr int UMMA_K = 32 / ELEM;
@@ -98,14 +107,14 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int stage_bytes = p.a_stage_bytes + p.b_stage_bytes;
   uint8_t* stage_base = smem;
-  int* idx_s = reinterpret_cast<int*>(smem + static_cast<size_t>(p.stages) * stage_bytes);  // [kGroup][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(idx_s + kGroup * kTileM);
+  int* idx_s = reinterpret_cast<int*>(smem + static_cast<size_t>(p.stages) * stage_bytes);  // [group_rows][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(idx_s + p.group_rows * kTileM);
   StageInfo* info = reinterpret_cast<StageInfo*>(bars + 2 * kMaxStages + 1);
   uint32_t* vote = reinterpret_cast<uint32_t*>(info + kMaxStages);
   uint32_t* tmem_slot = vote + 4;
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
-  float* epi_scale = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(abort_flag + 1) + 15) & ~uintptr_t(15));  // [256]
-  float* epi_shift = epi_scale + 256;                             // [256] per-channel shift (bias folded in)
+  float* epi_scale = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(abort_flag + 1) + 15) & ~uintptr_t(15));  // [epi_pad]
+  float* epi_shift = epi_scale + p.epi_pad;                       // [epi_pad] per-channel shift (bias folded in)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -157,14 +166,14 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
     const int ncb = B_MN ? (p.n_dim + b_cols - 1) / b_cols : 1;
     const uint32_t b_bytes = B_MN ? static_cast<uint32_t>(ncb * epr * p.b_row_bytes)
                                   : static_cast<uint32_t>(p.n_dim * p.a_row_bytes);
-    // this thread copies 16-byte piece `chunk` of rows row_lo, row_lo+32, row_lo+64, row_lo+96
+    // this thread copies 16-byte piece `chunk` of rows row_lo, row_lo + 16, .., row_lo + 112
     const int chunk = tid & 7, row_lo = tid >> 3;
     const bool copies = chunk < p.a_row_bytes / 16;
     const uint32_t swz_mask = static_cast<uint32_t>(p.a_row_bytes / 16 - 1);  // 7, 3 or 1
-    uint32_t dst_off[4];
+    uint32_t dst_off[kRowsPerThread];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t lin = static_cast<uint32_t>((row_lo + 32 * i) * p.a_row_bytes + chunk * 16);
+    for (int i = 0; i < kRowsPerThread; ++i) {
+      const uint32_t lin = static_cast<uint32_t>((row_lo + kRowStep * i) * p.a_row_bytes + chunk * 16);
       dst_off[i] = lin ^ (((lin >> 7) & swz_mask) << 4);
     }
     const uint8_t* src_chunk = static_cast<const uint8_t*>(p.src) + chunk * 16;
@@ -212,9 +221,9 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
       for (uint32_t rest = active; rest != 0; rest &= rest - 1) {
         const int kk = __ffs(rest) - 1;
         const int k = k0 + kk;
-        int j[4];
+        int j[kRowsPerThread];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) j[i] = idx_s[kk * kTileM + row_lo + 32 * i];
+        for (int i = 0; i < kRowsPerThread; ++i) j[i] = idx_s[kk * kTileM + row_lo + kRowStep * i];
         for (int rc = 0; rc < n_rchunks; ++rc) {
           if (tid == 0) SPC_STAMP(16 + 2 * trace_n);
           if (ok && !mbar_wait(bar_empty + 8 * stage, empty_parity)) ok = false;
@@ -227,7 +236,7 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
             if (copies) {
               const uint8_t* base = src_chunk + static_cast<long long>(r0) * ELEM;
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
+              for (int i = 0; i < kRowsPerThread; ++i) {
                 const bool present = j[i] >= 0;
                 cp_async16(a_dst + dst_off[i],
                            base + static_cast<unsigned long long>(present ? static_cast<uint32_t>(j[i]) : 0u) * src_pitch,
@@ -488,13 +497,34 @@ int gather_gemm_tma(const void* src, const void* w, const Epilogue& epi, const i
   }
   p.b_stage_bytes = static_cast<int>(align_up(p.b_stage_bytes, 1024));
   const int stage_bytes = p.a_stage_bytes + p.b_stage_bytes;
-  const size_t fixed = 1024 + kGroup * kTileM * 4 + (2 * kMaxStages + 1) * 8 + kMaxStages * sizeof(StageInfo) + 64 + 2 * 256 * sizeof(float) + 16;
-  const size_t budget = 110 * 1024;  // two CTAs per SM
-  p.stages = std::max(2, std::min<int>(kMaxStages, static_cast<int>((budget - fixed) / stage_bytes)));
-  const size_t smem_bytes = fixed + static_cast<size_t>(p.stages) * stage_bytes;
+  // Everything besides the stages is sized to the layer.  As many CTAs per SM as shared memory
+  // (228 KB per SM, 1 KB reserved per CTA), tensor memory (512 columns) and registers allow, as
+  // long as each keeps at least two stages.
+  p.group_rows = std::min(kv, kGroup);
+  p.epi_pad = (n_dim + 15) / 16 * 16;
   int cols = 32;
   while (cols < n_dim) cols <<= 1;
   p.tmem_cols = cols;
+  const size_t fixed = 1024 + static_cast<size_t>(p.group_rows) * kTileM * 4 + (2 * kMaxStages + 1) * 8 +
+                       kMaxStages * sizeof(StageInfo) + 64 + 2 * p.epi_pad * sizeof(float) + 16;
+  p.stages = 0;
+  int ctas = std::min(kMaxCtasPerSm, 512 / cols) + 1;
+  while (p.stages < 2 && ctas > 1) {
+    --ctas;
+    const size_t per_cta = (228 * 1024 - static_cast<size_t>(ctas) * 1024) / ctas - 256;
+    p.stages = per_cta > fixed ? std::min<int>(kMaxStages, static_cast<int>((per_cta - fixed) / stage_bytes)) : 0;
+  }
+  // the kernel's dynamic shared memory limit is set to 200 KB
+  while (p.stages > 2 && fixed + static_cast<size_t>(p.stages) * stage_bytes > 200 * 1024) --p.stages;
+  // shared memory is carved out of the L1: beyond two stages, keep about 36 KB of the SM as cache
+  // for the table and epilogue traffic (a third stage that took it cost 8 % on 64 -> 128)
+  // (layers whose reduction spans several stages per offset keep the deeper pipeline: 128 -> 128
+  // lost 10 % without its third stage)
+  const bool long_reduction = r_dim * elem > p.a_row_bytes;
+  while (!long_reduction && p.stages > 2 && ctas * (fixed + static_cast<size_t>(p.stages) * stage_bytes) > 192 * 1024)
+    --p.stages;
+  if (p.stages < 2) return fail(SPC_ERR_UNSUPPORTED, "TMA gather-GEMM: a stage of %d bytes does not fit twice", stage_bytes);
+  const size_t smem_bytes = fixed + static_cast<size_t>(p.stages) * stage_bytes;
   p.status = device_status_ptr();
   if (p.status == nullptr) return fail(SPC_ERR_CUDA, "TMA gather-GEMM: no device status word");
 
