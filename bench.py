@@ -187,7 +187,7 @@ class ClockSampler:
 
 # DRAM bytes (read + write) of one forward gather-GEMM launch of this workload, averaged over the
 # launches of one ncu capture of this file (see profiles/).
-GEMM_DRAM_BYTES_PER_LAUNCH = 285.3e6
+GEMM_DRAM_BYTES_PER_LAUNCH = 283.4e6
 
 
 class GemmProfiler:
@@ -654,7 +654,7 @@ def main():
                       "the timed region, where rulebook kernels of the next layer share the SMs",
             "bound": "hbm", "achieved": achieved_gbs, "peak": hbm_peak, "unit": "GB/s",
             "frac": achieved_gbs / hbm_peak if hbm_peak else None, "traffic": GEMM_DRAM_BYTES_PER_LAUNCH,
-            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, average of the 36 gather-GEMM "
+            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, average of the 68 gather-GEMM "
                               "launches captured on this workload (profiles/voxelnet_backbone_launch_list.md)",
             "algorithmic_bytes_per_launch": gemm["bytes"] / gemm["launches"] if gemm["launches"] else None,
             "peak_kind": peak_kind,
