@@ -33,13 +33,11 @@ namespace {
 
 using namespace tc;
 
-constexpr int kWgIssueWarps = 8;
-constexpr int kWgIssueThreads = kWgIssueWarps * 32;  // 256
-constexpr int kWgMmaWarp = kWgIssueWarps;
-constexpr int kWgThreads = kWgIssueThreads + 32;     // 288
+// The number of copy warps is a template parameter: four (160-thread CTAs, three per SM) where a pair
+// is at most 384 bytes of rows, eight (two CTAs per SM) for wider rows, which need the copy throughput.
+constexpr int kWgMaxIssueWarps = 8;
 constexpr int kPairsPerStage = 64;
 constexpr int kScanBatch = 4;                        // table entries per thread per scan round
-constexpr int kScanEntries = kScanBatch * kWgIssueThreads;  // 1024
 constexpr int kRing = 2048;                          // capacity of the pair list (power of two, > 64 + 1024)
 
 struct WgParams {
@@ -64,14 +62,14 @@ __host__ __device__ inline uint32_t wg_layout_type(int row_bytes) {
 template <int ELEM>
 __device__ __forceinline__ void copy_rows(uint32_t dst_base, const uint8_t* src, uint32_t src_pitch,
                                           const int* rows, int n_rows, int n_rows_padded, int pieces_per_row,
-                                          int row_bytes, int tid) {
+                                          int row_bytes, int tid, int nthreads) {
   const int per_block = row_bytes / 16;  // 2, 4 or 8
   const uint32_t swz_mask = static_cast<uint32_t>(per_block - 1);
   const int lg_pb = per_block == 8 ? 3 : (per_block == 4 ? 2 : 1);
   const int total = n_rows_padded * pieces_per_row;
   const bool pow2 = (pieces_per_row & (pieces_per_row - 1)) == 0;
   const int lg_ppr = 31 - __clz(pieces_per_row);
-  for (int q = tid; q < total; q += kWgIssueThreads) {
+  for (int q = tid; q < total; q += nthreads) {
     int p, piece;
     if (pow2) {  // the usual case: no integer division per copy
       p = q >> lg_ppr;
@@ -89,9 +87,13 @@ __device__ __forceinline__ void copy_rows(uint32_t dst_base, const uint8_t* src,
   }
 }
 
-template <typename T>
-__global__ void __maxnreg__(80)
+template <typename T, int W>
+__global__ void __maxnreg__(W == 4 ? 96 : 80)
 wgrad_tc_kernel(const __grid_constant__ WgParams p) {
+  constexpr int kWgIssueWarps = W;
+  constexpr int kWgIssueThreads = W * 32;
+  constexpr int kWgMmaWarp = W;
+  constexpr int kScanEntries = kScanBatch * kWgIssueThreads;
   constexpr int ELEM = sizeof(T);
   constexpr int UMMA_K = 32 / ELEM;  // 16 pairs per MMA
 
@@ -217,8 +219,8 @@ wgrad_tc_kernel(const __grid_constant__ WgParams p) {
         const uint32_t g_dst = smem_u32(stage_base + static_cast<size_t>(stage) * stage_bytes);
         const uint32_t f_dst = g_dst + p.g_stage_bytes;
         const uint32_t full = bar_full + 8 * stage;
-        copy_rows<ELEM>(g_dst, g_src, g_pitch, sm, n, n_pad, g_pieces, p.g_row_bytes, tid);
-        copy_rows<ELEM>(f_dst, f_src, f_pitch, si, n, n_pad, f_pieces, p.f_row_bytes, tid);
+        copy_rows<ELEM>(g_dst, g_src, g_pitch, sm, n, n_pad, g_pieces, p.g_row_bytes, tid, kWgIssueThreads);
+        copy_rows<ELEM>(f_dst, f_src, f_pitch, si, n, n_pad, f_pieces, p.f_row_bytes, tid, kWgIssueThreads);
         cp_async_arrive_noinc(full);
         if (tid == 0) {
           info[stage].ksteps = n_pad / UMMA_K;
@@ -357,15 +359,15 @@ int span_of(int elems, int elem_size) {
   return 0;
 }
 
-template <typename T>
+template <typename T, int W>
 int launch_wgrad_tc(const WgParams& p, size_t smem_bytes, cudaStream_t st) {
   static bool configured = false;
   if (!configured) {
-    SPC_CUDA_OK(cudaFuncSetAttribute(wgrad_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    SPC_CUDA_OK(cudaFuncSetAttribute(wgrad_tc_kernel<T, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     configured = true;
   }
   dim3 grid(static_cast<unsigned>(p.kv * p.splits), static_cast<unsigned>(ceil_div(p.c_out, kTileM)));
-  wgrad_tc_kernel<T><<<grid, kWgThreads, smem_bytes, st>>>(p);
+  wgrad_tc_kernel<T, W><<<grid, W * 32 + 32, smem_bytes, st>>>(p);
   SPC_LAUNCH_OK();
   return SPC_OK;
 }
@@ -415,8 +417,9 @@ int wgrad_tc(const void* feats, const void* gout, const int32_t* pair_fwd, float
   p.f_stage_bytes = static_cast<int>(align_up(static_cast<size_t>(c_in) * 2 * kPairsPerStage, 1024));
   const int stage_bytes = p.g_stage_bytes + p.f_stage_bytes;
   const size_t fixed = 1024 + 2 * kRing * 4 + 2 * tc::kMaxStages * kPairsPerStage * 4 + (2 * tc::kMaxStages + 1) * 8 +
-                       tc::kMaxStages * sizeof(tc::StageInfo) + kScanBatch * kWgIssueWarps * 4 + 64;
-  const size_t budget = 110 * 1024;
+                       tc::kMaxStages * sizeof(tc::StageInfo) + kScanBatch * kWgMaxIssueWarps * 4 + 64;
+  const bool narrow = (c_in + g_cols) * 2 <= 384;  // bytes of rows per pair
+  const size_t budget = narrow ? 74 * 1024 : 110 * 1024;  // three / two CTAs per SM
   p.stages = std::max(2, std::min<int>(tc::kMaxStages, static_cast<int>((budget - fixed) / stage_bytes)));
   const size_t smem_bytes = fixed + static_cast<size_t>(p.stages) * stage_bytes;
   int cols = 32;
@@ -424,8 +427,12 @@ int wgrad_tc(const void* feats, const void* gout, const int32_t* pair_fwd, float
   p.tmem_cols = cols;
   p.status = device_status_ptr();
   if (p.status == nullptr) return fail(SPC_ERR_CUDA, "tcgen05 wgrad: no device status word");
-  if (dtype == SPC_F16) return launch_wgrad_tc<__half>(p, smem_bytes, st);
-  return launch_wgrad_tc<__nv_bfloat16>(p, smem_bytes, st);
+  if (narrow) {
+    if (dtype == SPC_F16) return launch_wgrad_tc<__half, 4>(p, smem_bytes, st);
+    return launch_wgrad_tc<__nv_bfloat16, 4>(p, smem_bytes, st);
+  }
+  if (dtype == SPC_F16) return launch_wgrad_tc<__half, 8>(p, smem_bytes, st);
+  return launch_wgrad_tc<__nv_bfloat16, 8>(p, smem_bytes, st);
 }
 
 }  // namespace spc
