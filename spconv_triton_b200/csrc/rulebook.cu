@@ -103,6 +103,21 @@ struct Table<false> {
     }
     return -1;
   }
+  // A look-up split in two so that several keys' first probes can be in flight at once:
+  // first_probe() returns the home slot's word, finish() resolves it (almost always at once).
+  __device__ __forceinline__ unsigned long long first_probe(key_t key) const { return __ldg(&slots[home(key)]); }
+  __device__ __forceinline__ int finish(key_t key, unsigned long long v) const {
+    if (v == kEmpty) return -1;
+    if (static_cast<key_t>(v >> 32) == key) return static_cast<int>(v & 0xffffffffu);
+    uint32_t s = (home(key) + kStep) & cap_mask;
+    for (uint32_t probe = 1; probe <= (cap_mask >> 2); ++probe) {
+      const unsigned long long w = __ldg(&slots[s]);
+      if (w == kEmpty) return -1;
+      if (static_cast<key_t>(w >> 32) == key) return static_cast<int>(w & 0xffffffffu);
+      s = (s + kStep) & cap_mask;
+    }
+    return -1;
+  }
   __device__ void set_value(key_t key, uint32_t val) const {
     uint32_t s = home(key);
     for (uint32_t probe = 0; probe <= (cap_mask >> 2); ++probe) {
@@ -163,6 +178,8 @@ struct Table<true> {
     }
     return -1;
   }
+  __device__ __forceinline__ unsigned long long first_probe(key_t) const { return 0; }
+  __device__ __forceinline__ int finish(key_t key, unsigned long long) const { return find(key); }
   __device__ void set_value(key_t key, uint32_t val) const {
     uint32_t s = home(key);
     for (uint32_t probe = 0; probe <= (cap_mask >> 2); ++probe) {
@@ -416,41 +433,64 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
       inside[d] = m;
     }
   }
-  for (int k = 0; k < g.kv; ++k) {
-    long long key;
-    if (fast) {
-      uint32_t ok = 1u;
-      key = base;
+  // Offsets are handled three at a time (the three neighbours along the last axis of a 3^3
+  // kernel): their bitmap words, then their first hash probes, are requested together, so a row
+  // has up to three L2 accesses in flight instead of one after the other.
+  constexpr int kBatch = 3;
+  for (int k0 = 0; k0 < g.kv; k0 += kBatch) {
+    long long key[kBatch];
+    uint32_t bits[kBatch];
+    unsigned long long probe[kBatch];
 #pragma unroll
-      for (int d = 0; d < ND; ++d) {
-        ok &= inside[d] >> od.pos[d];
-        key += od.pos[d] * step[d];
-      }
-      if (!(ok & 1u)) key = -1;
-    } else {
-      key = in_key_from_output<ND>(g, o, od.pos);
-    }
-    bool there = key >= 0;
-    if (there && bitmap != nullptr) there = (__ldg(&bitmap[key >> 5]) >> (key & 31)) & 1u;
-    const int j = there ? tin.find(static_cast<key_t>(key)) : -1;
-    pair_fwd[static_cast<long long>(k) * n_out + r] = j;
-    if (SUBM_BWD) {
-      pair_bwd[static_cast<long long>(g.kv - 1 - k) * n_out + r] = j;
-      if (bwd_rm != nullptr) bwd_rm[r * kvp + (g.kv - 1 - k)] = j;
-    }
-    if (fwd_rm != nullptr) {
-      quad[k & 3] = j;
-      if ((k & 3) == 3 || k == g.kv - 1) {
-        *reinterpret_cast<int4*>(&fwd_rm[r * kvp + (k & ~3)]) = make_int4(quad[0], quad[1], quad[2], quad[3]);
-        quad[0] = quad[1] = quad[2] = quad[3] = -1;
+    for (int b = 0; b < kBatch; ++b) {
+      key[b] = -1;
+      if (k0 + b < g.kv) {
+        if (fast) {
+          uint32_t ok = 1u;
+          long long kk = base;
+#pragma unroll
+          for (int d = 0; d < ND; ++d) {
+            ok &= inside[d] >> od.pos[d];
+            kk += od.pos[d] * step[d];
+          }
+          if (ok & 1u) key[b] = kk;
+        } else {
+          key[b] = in_key_from_output<ND>(g, o, od.pos);
+        }
+        od.next(g);
       }
     }
-    word |= static_cast<uint32_t>(j >= 0) << (k & 31);
-    if ((k & 31) == 31 || k == g.kv - 1) {
-      words[r * mic + (k >> 5)] = word;
-      word = 0;
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b)
+      bits[b] = (key[b] >= 0 && bitmap != nullptr) ? __ldg(&bitmap[key[b] >> 5]) : 0xffffffffu;
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      if (key[b] >= 0 && !((bits[b] >> (key[b] & 31)) & 1u)) key[b] = -1;
+      probe[b] = key[b] >= 0 ? tin.first_probe(static_cast<key_t>(key[b])) : 0ull;
     }
-    od.next(g);
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const int k = k0 + b;
+      if (k >= g.kv) break;
+      const int j = key[b] >= 0 ? tin.finish(static_cast<key_t>(key[b]), probe[b]) : -1;
+      pair_fwd[static_cast<long long>(k) * n_out + r] = j;
+      if (SUBM_BWD) {
+        pair_bwd[static_cast<long long>(g.kv - 1 - k) * n_out + r] = j;
+        if (bwd_rm != nullptr) bwd_rm[r * kvp + (g.kv - 1 - k)] = j;
+      }
+      if (fwd_rm != nullptr) {
+        quad[k & 3] = j;
+        if ((k & 3) == 3 || k == g.kv - 1) {
+          *reinterpret_cast<int4*>(&fwd_rm[r * kvp + (k & ~3)]) = make_int4(quad[0], quad[1], quad[2], quad[3]);
+          quad[0] = quad[1] = quad[2] = quad[3] = -1;
+        }
+      }
+      word |= static_cast<uint32_t>(j >= 0) << (k & 31);
+      if ((k & 31) == 31 || k == g.kv - 1) {
+        words[r * mic + (k >> 5)] = word;
+        word = 0;
+      }
+    }
   }
   if (SUBM_BWD && bwd_rm != nullptr)
     for (int k = g.kv; k < kvp; ++k) bwd_rm[r * kvp + k] = -1;
