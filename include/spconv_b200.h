@@ -219,6 +219,51 @@ int spc_dense_gather(const void* dense, const int32_t* indices, int64_t n, int c
                      int batch_size, const int32_t* spatial_shape, int channels_first, int elem_size,
                      void* features, void* stream);
 
+/* ---- key -> value hash table and misaligned sparse add ------------------- */
+
+/* A fixed-capacity GPU hash table; replaces HashTable, spconv_triton/pytorch/hash.py:15-110
+ * (sorted arrays + searchsorted there).  The table lives in ONE caller-owned device buffer of
+ * spc_hash_bytes(capacity) bytes; capacity = number of slots, a power of two (the host wrapper
+ * takes the power of two >= 2 * max_size).  Keys are int32 or int64 (key_bytes 4 / 8; INT64_MIN
+ * is reserved), values are the bits of any 1/2/4/8-byte type.
+ *   spc_hash_clear     empties the table.
+ *   spc_hash_insert    hash.py:38-60: stores keys[i] -> values[i] (0 when values is NULL); of equal
+ *                      keys in one call the LAST wins.  `epoch` must grow with every insert call on a
+ *                      table (it orders the writers; 24 bits).
+ *   spc_hash_counters  host read (synchronises the stream): number of stored keys and of keys an
+ *                      insert dropped because the table was full ("hash table full", hash.py:59-60).
+ *   spc_hash_query     hash.py:62-79: out_values[i] = value or 0, is_empty[i] = 1 when absent.
+ *   spc_hash_update    insert_exist_keys, hash.py:81-92: overwrites values of stored keys only.
+ *   spc_hash_items     hash.py:94-110: the `count` stored pairs in ascending key order into
+ *                      out_keys / out_values (either may be NULL; at most out_limit entries written).
+ *                      assign_kind -1 keeps the values; 0 / 1 / 2 first replaces them by the rank
+ *                      in that order as integer / float / double (assign_arange_, hash.py:94-99).
+ *                      `count` = the stored-key count read with spc_hash_counters. */
+size_t spc_hash_bytes(int64_t capacity);
+int spc_hash_clear(void* table, int64_t capacity, void* stream);
+int spc_hash_insert(void* table, int64_t capacity, const void* keys, int key_bytes, const void* values,
+                    int val_bytes, int64_t n, uint64_t epoch, void* stream);
+int spc_hash_counters(const void* table, int64_t capacity, int64_t* stored, int64_t* dropped, void* stream);
+int spc_hash_query(const void* table, int64_t capacity, const void* keys, int key_bytes, int64_t n,
+                   void* out_values, int val_bytes, uint8_t* is_empty, void* stream);
+int spc_hash_update(void* table, int64_t capacity, const void* keys, int key_bytes, const void* values,
+                    int val_bytes, int64_t n, uint8_t* found, void* stream);
+size_t spc_hash_items_workspace_bytes(int64_t count);
+int spc_hash_items(void* table, int64_t capacity, int64_t count, int assign_kind, void* ws, size_t ws_bytes,
+                   void* out_keys, int key_bytes, void* out_values, int val_bytes, int64_t out_limit,
+                   void* stream);
+
+/* The accumulation of sparse_add_hash_based, spconv_triton/pytorch/functional.py:476-480:
+ *   dst[rows[i], :] += src[i, :]  and  idx_dst[rows[i], :] = idx_src[i, :]  (idx_src may be NULL)
+ * for rows that are distinct within the call (no atomics); rows outside [0, dst_rows) are skipped.
+ * src [n, channels] and dst [dst_rows, channels] of `dtype` (spc_dtype).  spc_rows_gather is its
+ * gradient: dst[i, :] = src[rows[i], :]. */
+int spc_rows_scatter_add(const void* src, const int32_t* rows, int64_t n, int channels, int dtype,
+                         int64_t dst_rows, void* dst, const int32_t* idx_src, int idx_width,
+                         int32_t* idx_dst, void* stream);
+int spc_rows_gather(const void* src, const int32_t* rows, int64_t n, int channels, int dtype,
+                    int64_t src_rows, void* dst, void* stream);
+
 /* ---- implicit gather-GEMM ---------------------------------------------- */
 
 /* Forward: replaces conv_forward, _impl/gemm.py:501-568.

@@ -77,6 +77,16 @@ _PROTOTYPES = {
     "spc_pairs_to_rowmajor": (c_int, [_P, c_int, c_int64, _P, _P]),
     "spc_dense_scatter": (c_int, [_P, _P, c_int64, c_int, c_int, c_int, POINTER(ctypes.c_int32), c_int, c_int, _P, _P]),
     "spc_dense_gather": (c_int, [_P, _P, c_int64, c_int, c_int, c_int, POINTER(ctypes.c_int32), c_int, c_int, _P, _P]),
+    "spc_hash_bytes": (c_size_t, [c_int64]),
+    "spc_hash_clear": (c_int, [_P, c_int64, _P]),
+    "spc_hash_insert": (c_int, [_P, c_int64, _P, c_int, _P, c_int, c_int64, ctypes.c_uint64, _P]),
+    "spc_hash_counters": (c_int, [_P, c_int64, POINTER(c_int64), POINTER(c_int64), _P]),
+    "spc_hash_query": (c_int, [_P, c_int64, _P, c_int, c_int64, _P, c_int, _P, _P]),
+    "spc_hash_update": (c_int, [_P, c_int64, _P, c_int, _P, c_int, c_int64, _P, _P]),
+    "spc_hash_items_workspace_bytes": (c_size_t, [c_int64]),
+    "spc_hash_items": (c_int, [_P, c_int64, c_int64, c_int, _P, c_size_t, _P, c_int, _P, c_int, c_int64, _P]),
+    "spc_rows_scatter_add": (c_int, [_P, _P, c_int64, c_int, c_int, c_int64, _P, _P, c_int, _P, _P]),
+    "spc_rows_gather": (c_int, [_P, _P, c_int64, c_int, c_int, c_int64, _P, _P]),
     "spc_voxelize_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "spc_voxelize": (c_int, [_P, c_int64, c_int, c_int, c_int, POINTER(ctypes.c_float), POINTER(ctypes.c_float),
                              POINTER(ctypes.c_int32), c_int64, c_int, c_int, c_int, _P, c_size_t, _P, _P, _P, _P,

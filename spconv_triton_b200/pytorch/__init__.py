@@ -1,6 +1,6 @@
 """Public PyTorch API: ``import spconv_triton_b200.pytorch as spconv``."""
 
-from . import functional, ops
+from . import functional, hash, ops
 from .conv import (
     SparseConv1d, SparseConv2d, SparseConv3d, SparseConv4d,
     SparseConvTranspose1d, SparseConvTranspose2d, SparseConvTranspose3d, SparseConvTranspose4d,
@@ -18,7 +18,7 @@ from .pool import (
     SparseAvgPool1d, SparseAvgPool2d, SparseAvgPool3d, SparseGlobalAvgPool, SparseGlobalMaxPool,
     SparseMaxPool1d, SparseMaxPool2d, SparseMaxPool3d, SparseMaxPool4d,
 )
-from .tables import AddTable, ConcatTable, JoinTable
+from .tables import AddTable, AddTableMisaligned, ConcatTable, JoinTable
 
 
 class ToDense(SparseModule):

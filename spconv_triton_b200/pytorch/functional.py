@@ -157,3 +157,129 @@ indice_subm_conv = SubMConvFunction.apply
 indice_maxpool = SparseMaxPoolFunction.apply
 indice_maxpool_implicit_gemm = SparseMaxPoolImplicitGemmFunction.apply
 indice_avgpool_implicit_gemm = SparseAvgPoolImplicitGemmFunction.apply
+
+
+# ---- misaligned sparse add --------------------------------------------------------------------
+_MAX_INT32 = 2147483647
+
+
+def _indice_to_scalar(indices: torch.Tensor, shape: list[int]):
+    """Row-major linear index of [N, len(shape)] coordinates (functional.py:415-426 of the reference)."""
+    if indices.shape[1] != len(shape):
+        raise AssertionError
+    stride = [1] * len(shape)
+    for i in range(len(shape) - 2, -1, -1):
+        stride[i] = stride[i + 1] * shape[i + 1]
+    scalar_inds = indices[:, -1].clone()
+    for i in range(len(shape) - 1):
+        scalar_inds += stride[i] * indices[:, i]
+    return scalar_inds.contiguous()
+
+
+class _RowsScatterAdd(Function):
+    """out[rows_k[i], :] += features_k[i, :] over all operands k, and the coordinates with them.
+
+    args = (rows_0.., indices_0.., features_0..), ``n_tens`` of each.  The gradient of operand k
+    is the gather grad_out[rows_k]."""
+
+    @staticmethod
+    def forward(ctx, count, n_tens, *args):
+        from spconv_triton_b200 import _lib
+
+        rows, idxs, feats = args[:n_tens], args[n_tens:2 * n_tens], args[2 * n_tens:]
+        first = feats[0]
+        channels, width = int(first.shape[1]), int(idxs[0].shape[1])
+        out = torch.zeros([count, channels], dtype=first.dtype, device=first.device)
+        out_idx = torch.zeros([count, width], dtype=idxs[0].dtype, device=first.device)
+        lib = _lib.load()
+        code = _lib.dtype_code(first.dtype)
+        with torch.cuda.device(first.device):
+            stream = _lib.current_stream(first.device)
+            for r, ix, f in zip(rows, idxs, feats, strict=True):
+                f, ix = f.contiguous(), ix.contiguous()
+                _lib.check(lib.spc_rows_scatter_add(_lib.ptr(f), _lib.ptr(r), int(f.shape[0]), channels, code, count,
+                                                    _lib.ptr(out), _lib.ptr(ix), width, _lib.ptr(out_idx), stream))
+        ctx.save_for_backward(*rows)
+        ctx.meta = (n_tens, channels, code)
+        ctx.mark_non_differentiable(out_idx)
+        return out, out_idx
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_out, _grad_idx):
+        from spconv_triton_b200 import _lib
+
+        n_tens, channels, code = ctx.meta
+        grad_out = grad_out.contiguous()
+        lib = _lib.load()
+        grads = []
+        with torch.cuda.device(grad_out.device):
+            stream = _lib.current_stream(grad_out.device)
+            for k, r in enumerate(ctx.saved_tensors):
+                if not ctx.needs_input_grad[2 + 2 * n_tens + k]:
+                    grads.append(None)
+                    continue
+                g = torch.empty([r.shape[0], channels], dtype=grad_out.dtype, device=grad_out.device)
+                _lib.check(lib.spc_rows_gather(_lib.ptr(grad_out), _lib.ptr(r), int(r.shape[0]), channels, code,
+                                               int(grad_out.shape[0]), _lib.ptr(g), stream))
+                grads.append(g)
+        return (None, None, *([None] * (2 * n_tens)), *grads)
+
+
+def _sparse_add_cuda(tens):
+    from .core import SparseConvTensor
+    from .hash import HashTable
+
+    table_size = 0
+    max_num_indices = 0
+    max_num_indices_idx = 0
+    for i, ten in enumerate(tens):
+        if ten.spatial_shape != tens[0].spatial_shape:
+            raise AssertionError
+        if ten.batch_size != tens[0].batch_size:
+            raise AssertionError
+        if ten.features.shape[1] != tens[0].features.shape[1]:
+            raise AssertionError
+        table_size += ten.features.shape[0]
+        if max_num_indices < ten.features.shape[0]:
+            max_num_indices_idx = i
+            max_num_indices = ten.features.shape[0]
+    first = tens[0]
+    if not first.features.is_cuda:
+        raise NotImplementedError("spconv_triton_b200 sparse add is CUDA only")
+    shape = [first.batch_size, *first.spatial_shape]
+    whole_shape = int(np.prod(shape))
+    k_type = torch.int64 if whole_shape >= _MAX_INT32 else torch.int32
+    table = HashTable(first.features.device, k_type, torch.int32, max(2 * table_size, 2))
+    scalars = []
+    for ten in tens:
+        indices = ten.indices.long() if whole_shape >= _MAX_INT32 else ten.indices
+        scalar = _indice_to_scalar(indices, shape)
+        scalars.append(scalar)
+        table.insert(scalar)
+    count_val = int(table.assign_arange_().item())
+    rows = [table.query(scalar)[0] for scalar in scalars]
+    out_features, out_indices = _RowsScatterAdd.apply(
+        count_val, len(tens), *rows, *[t.indices for t in tens], *[t.features for t in tens])
+    res = SparseConvTensor(out_features, out_indices, first.spatial_shape, first.batch_size, benchmark=first.benchmark)
+    if count_val == max_num_indices:
+        res.indice_dict = tens[max_num_indices_idx].indice_dict
+    res.benchmark_record = first.benchmark_record
+    res._timer = first._timer
+    res.thrust_allocator = first.thrust_allocator
+    return res
+
+
+def sparse_add_hash_based(*tens):
+    """Sum of sparse tensors whose voxel sets differ (functional.py:429-490 of the reference).
+
+    The union of the coordinates is numbered through a GPU hash table in ascending order of the
+    linear coordinate (what the reference's sorted table gives), then every operand's rows are
+    accumulated into their numbered rows by one kernel per operand."""
+    return _sparse_add_cuda(tens)
+
+
+def sparse_add(*tens):
+    """Same sum; the reference goes through torch.sparse coalescing (functional.py:493-535), whose
+    result rows are in the same ascending coordinate order, so both names share one CUDA path."""
+    return _sparse_add_cuda(tens)

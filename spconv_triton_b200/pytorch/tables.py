@@ -52,6 +52,18 @@ class AddTable(SparseModule):
         return out_size
 
 
+class AddTableMisaligned(SparseModule):
+    """Add sparse tensors of one shape but different voxel sets (tables.py:78-85 of the reference)."""
+
+    def forward(self, inputs: list[SparseConvTensor]):
+        from . import functional as F
+
+        return F.sparse_add_hash_based(*inputs)
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+
 class ConcatTable(SparseModule):
     """Apply every child to the same input and return the list of results."""
 
