@@ -395,6 +395,38 @@ def run_op_bench(args):
 
         emit("dense_channels_first", timed(lambda: x.dense(), iters), nbytes, rows=int(idx.shape[0]), dense_elems=vol * c,
              torch_definition_ms=timed(torch_dense, iters))
+    elif args.op == "sparse_add":
+        # the residual join of two branches with different voxel sets: 2 x 400k rows of 64 fp16 channels, 4 samples
+        import spconv_triton_b200.pytorch as sp
+        from spconv_triton_b200.scenes import uniform_batch
+
+        batch, shape, c = 4, [41, 400, 352], 64
+        tens = []
+        for seed in (11, 12):
+            idx = torch.from_numpy(uniform_batch(seed, batch, 100000, tuple(shape))).to(dev)
+            tens.append(sp.SparseConvTensor(torch.randn(idx.shape[0], c, device=dev).half(), idx, shape, batch))
+        out = sp.functional.sparse_add_hash_based(*tens)
+        n_in, n_out = sum(int(t.indices.shape[0]) for t in tens), int(out.indices.shape[0])
+        # read features + coordinates, write the union (read-modify-write of the second operand's rows)
+        nbytes = n_in * (c * 2 + 16) + n_out * (c * 2 + 16) + int(tens[1].indices.shape[0]) * c * 2
+
+        def torch_definition():
+            # the reference's formulation (sort-based table): unique of the linear coordinates + index_add
+            lin = [((t.indices[:, 0].long() * shape[0] + t.indices[:, 1]) * shape[1] + t.indices[:, 2]) * shape[2]
+                   + t.indices[:, 3] for t in tens]
+            uniq, inv = torch.unique(torch.cat(lin), return_inverse=True)
+            res = torch.zeros([uniq.shape[0], c], dtype=tens[0].features.dtype, device=dev)
+            ind = torch.zeros([uniq.shape[0], 4], dtype=torch.int32, device=dev)
+            start = 0
+            for t in tens:
+                rows = inv[start:start + t.indices.shape[0]]
+                start += t.indices.shape[0]
+                res[rows] += t.features
+                ind[rows] = t.indices
+            return res, ind
+
+        emit("sparse_add_hash_based_2x400k_c64", timed(lambda: sp.functional.sparse_add_hash_based(*tens), iters), nbytes,
+             rows_in=n_in, rows_out=n_out, torch_definition_ms=timed(torch_definition, iters))
     elif args.op == "voxelize":
         # the step before the backbone: 8 LiDAR sweeps of 150k points -> voxels of 0.16 x 0.16 x 0.2 m
         from spconv_triton_b200.pytorch.utils import PointToVoxel
@@ -462,7 +494,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-baseline-seconds", type=float, default=20.0)
-    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm", "voxelize", "dense"],
+    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm", "voxelize", "dense", "sparse_add"],
                     help="single-operator timings at the other configurations instead of the headline benchmark")
     ap.add_argument("--voxel-order", default="random", choices=["random", "sorted"],
                     help="--op pool: input voxel order (random = as a voxeliser emits them, sorted = as a previous layer's rulebook emits them)")

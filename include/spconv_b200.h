@@ -238,7 +238,8 @@ int spc_dense_gather(const void* dense, const int32_t* indices, int64_t n, int c
  *                      out_keys / out_values (either may be NULL; at most out_limit entries written).
  *                      assign_kind -1 keeps the values; 0 / 1 / 2 first replaces them by the rank
  *                      in that order as integer / float / double (assign_arange_, hash.py:94-99).
- *                      `count` = the stored-key count read with spc_hash_counters. */
+ *                      `count` = the stored-key count read with spc_hash_counters.  key_bits: when
+ *                      every key is in [0, 2^key_bits) the sort stops there; 0 = all 64 bits. */
 size_t spc_hash_bytes(int64_t capacity);
 int spc_hash_clear(void* table, int64_t capacity, void* stream);
 int spc_hash_insert(void* table, int64_t capacity, const void* keys, int key_bytes, const void* values,
@@ -249,9 +250,15 @@ int spc_hash_query(const void* table, int64_t capacity, const void* keys, int ke
 int spc_hash_update(void* table, int64_t capacity, const void* keys, int key_bytes, const void* values,
                     int val_bytes, int64_t n, uint8_t* found, void* stream);
 size_t spc_hash_items_workspace_bytes(int64_t count);
-int spc_hash_items(void* table, int64_t capacity, int64_t count, int assign_kind, void* ws, size_t ws_bytes,
-                   void* out_keys, int key_bytes, void* out_values, int val_bytes, int64_t out_limit,
-                   void* stream);
+int spc_hash_items(void* table, int64_t capacity, int64_t count, int assign_kind, int key_bits, void* ws,
+                   size_t ws_bytes, void* out_keys, int key_bytes, void* out_values, int val_bytes,
+                   int64_t out_limit, void* stream);
+
+/* _indice_to_scalar, spconv_triton/pytorch/functional.py:415-426: keys[i] = the row-major linear
+ * coordinate of indices[i, 0..width) over shape[0..width) (HOST array: batch size, then the spatial
+ * shape), as int32 or int64 (key_bytes 4 / 8). */
+int spc_coords_to_keys(const int32_t* indices, int64_t n, int width, const int64_t* shape, int key_bytes,
+                       void* keys, void* stream);
 
 /* The accumulation of sparse_add_hash_based, spconv_triton/pytorch/functional.py:476-480:
  *   dst[rows[i], :] += src[i, :]  and  idx_dst[rows[i], :] = idx_src[i, :]  (idx_src may be NULL)

@@ -84,7 +84,8 @@ _PROTOTYPES = {
     "spc_hash_query": (c_int, [_P, c_int64, _P, c_int, c_int64, _P, c_int, _P, _P]),
     "spc_hash_update": (c_int, [_P, c_int64, _P, c_int, _P, c_int, c_int64, _P, _P]),
     "spc_hash_items_workspace_bytes": (c_size_t, [c_int64]),
-    "spc_hash_items": (c_int, [_P, c_int64, c_int64, c_int, _P, c_size_t, _P, c_int, _P, c_int, c_int64, _P]),
+    "spc_hash_items": (c_int, [_P, c_int64, c_int64, c_int, c_int, _P, c_size_t, _P, c_int, _P, c_int, c_int64, _P]),
+    "spc_coords_to_keys": (c_int, [_P, c_int64, c_int, POINTER(c_int64), c_int, _P, _P]),
     "spc_rows_scatter_add": (c_int, [_P, _P, c_int64, c_int, c_int, c_int64, _P, _P, c_int, _P, _P]),
     "spc_rows_gather": (c_int, [_P, _P, c_int64, c_int, c_int, c_int64, _P, _P]),
     "spc_voxelize_workspace_bytes": (c_size_t, [c_int64, c_int64]),

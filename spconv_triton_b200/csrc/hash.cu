@@ -108,29 +108,39 @@ __global__ void __launch_bounds__(kHashThreads) hash_clear_kernel(HashView t) {
 __global__ void __launch_bounds__(kHashThreads)
 hash_claim_kernel(HashView t, const void* __restrict__ keys, int key_bytes, long long n, unsigned long long epoch) {
   const long long i = static_cast<long long>(blockIdx.x) * kHashThreads + threadIdx.x;
-  if (i >= n) return;
-  const long long key = load_key(keys, key_bytes, i);
-  if (key == kEmptyKey) return;
-  const unsigned long long stamp = (epoch << 40) | static_cast<unsigned long long>(i);
-  unsigned long long s = mix(key) & t.mask;
-  for (unsigned long long probe = 0; probe <= t.mask; ++probe) {
-    long long k = t.keys[s];
-    if (k == kEmptyKey) {
-      k = static_cast<long long>(atomicCAS(reinterpret_cast<unsigned long long*>(&t.keys[s]),
-                                           static_cast<unsigned long long>(kEmptyKey),
-                                           static_cast<unsigned long long>(key)));
+  const long long key = i < n ? load_key(keys, key_bytes, i) : kEmptyKey;
+  int outcome = 0;  // 1: claimed a free slot, 2: no slot left
+  if (key != kEmptyKey) {
+    const unsigned long long stamp = (epoch << 40) | static_cast<unsigned long long>(i);
+    unsigned long long s = mix(key) & t.mask;
+    outcome = 2;
+    for (unsigned long long probe = 0; probe <= t.mask; ++probe) {
+      long long k = t.keys[s];
+      bool fresh = false;
       if (k == kEmptyKey) {
-        atomicAdd(reinterpret_cast<unsigned long long*>(&t.counters[0]), 1ull);
-        k = key;
+        k = static_cast<long long>(atomicCAS(reinterpret_cast<unsigned long long*>(&t.keys[s]),
+                                             static_cast<unsigned long long>(kEmptyKey),
+                                             static_cast<unsigned long long>(key)));
+        if (k == kEmptyKey) {
+          fresh = true;
+          k = key;
+        }
       }
+      if (k == key) {
+        atomicMax(&t.stamp[s], stamp);
+        outcome = fresh ? 1 : 0;
+        break;
+      }
+      s = (s + 1) & t.mask;
     }
-    if (k == key) {
-      atomicMax(&t.stamp[s], stamp);
-      return;
-    }
-    s = (s + 1) & t.mask;
   }
-  atomicAdd(reinterpret_cast<unsigned long long*>(&t.counters[1]), 1ull);
+  // one atomic per warp on the two counters instead of one per key
+  const unsigned claimed = __ballot_sync(0xffffffffu, outcome == 1);
+  const unsigned dropped = __ballot_sync(0xffffffffu, outcome == 2);
+  if ((threadIdx.x & 31) == 0) {
+    if (claimed) atomicAdd(reinterpret_cast<unsigned long long*>(&t.counters[0]), static_cast<unsigned long long>(__popc(claimed)));
+    if (dropped) atomicAdd(reinterpret_cast<unsigned long long*>(&t.counters[1]), static_cast<unsigned long long>(__popc(dropped)));
+  }
 }
 
 // Pass 2 of insert: the occurrence whose stamp won writes its value.
@@ -174,11 +184,26 @@ hash_update_kernel(HashView t, const void* __restrict__ keys, int key_bytes, con
 __global__ void __launch_bounds__(kHashThreads)
 hash_dump_kernel(HashView t, long long limit, unsigned long long* __restrict__ cursor,
                  long long* __restrict__ dump_keys, uint32_t* __restrict__ dump_slots) {
+  // one atomic on the cursor per CTA: warp ballots, then a prefix over the CTA's eight warps
+  __shared__ unsigned int warp_count[kHashThreads / 32];
+  __shared__ unsigned long long cta_base;
   const unsigned long long s = static_cast<unsigned long long>(blockIdx.x) * kHashThreads + threadIdx.x;
-  if (s > t.mask) return;
-  const long long k = t.keys[s];
+  const long long k = s <= t.mask ? t.keys[s] : kEmptyKey;
+  const unsigned used = __ballot_sync(0xffffffffu, k != kEmptyKey);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) warp_count[warp] = __popc(used);
+  __syncthreads();
+  unsigned before = 0, total = 0;
+#pragma unroll
+  for (int w = 0; w < kHashThreads / 32; ++w) {
+    const unsigned c = warp_count[w];
+    before += w < warp ? c : 0u;
+    total += c;
+  }
+  if (threadIdx.x == 0 && total > 0) cta_base = atomicAdd(cursor, static_cast<unsigned long long>(total));
+  __syncthreads();
   if (k == kEmptyKey) return;
-  const unsigned long long pos = atomicAdd(cursor, 1ull);
+  const unsigned long long pos = cta_base + before + __popc(used & ((1u << lane) - 1u));
   if (static_cast<long long>(pos) < limit) {
     dump_keys[pos] = k;
     dump_slots[pos] = static_cast<uint32_t>(s);
@@ -288,6 +313,23 @@ int rows_add_typed(const void* src, const int32_t* rows, int64_t n, int channels
   return SPC_OK;
 }
 
+struct KeyShape {
+  int width;
+  long long stride[8];
+};
+
+// keys[i] = sum_d indices[i, d] * stride[d]: the row-major linear coordinate over [batch, *spatial].
+__global__ void __launch_bounds__(kHashThreads)
+coords_to_keys_kernel(const __grid_constant__ KeyShape g, const int32_t* __restrict__ indices, long long n,
+                      void* __restrict__ keys, int key_bytes) {
+  const long long i = static_cast<long long>(blockIdx.x) * kHashThreads + threadIdx.x;
+  if (i >= n) return;
+  long long lin = 0;
+  for (int d = 0; d < g.width; ++d) lin += g.stride[d] * __ldg(&indices[i * g.width + d]);
+  if (key_bytes == 4) static_cast<int32_t*>(keys)[i] = static_cast<int32_t>(lin);
+  else static_cast<long long*>(keys)[i] = lin;
+}
+
 // idx_dst[rows[i], :] = idx_src[i, :]: the coordinates that go with scattered feature rows.
 __global__ void __launch_bounds__(kHashThreads)
 rows_index_kernel(const int32_t* __restrict__ rows, long long n, long long dst_rows, const int32_t* __restrict__ idx_src,
@@ -385,9 +427,9 @@ extern "C" int spc_hash_update(void* table, int64_t capacity, const void* keys, 
 
 extern "C" size_t spc_hash_items_workspace_bytes(int64_t count) { return items_layout(count).total; }
 
-extern "C" int spc_hash_items(void* table, int64_t capacity, int64_t count, int assign_kind, void* ws, size_t ws_bytes,
-                              void* out_keys, int key_bytes, void* out_values, int val_bytes, int64_t out_limit,
-                              void* stream) {
+extern "C" int spc_hash_items(void* table, int64_t capacity, int64_t count, int assign_kind, int key_bits, void* ws,
+                              size_t ws_bytes, void* out_keys, int key_bytes, void* out_values, int val_bytes,
+                              int64_t out_limit, void* stream) {
   if (table == nullptr || bad_cap(capacity) || count < 0 || count > capacity || assign_kind < -1 || assign_kind > 2 ||
       (key_bytes != 4 && key_bytes != 8) || bad_bytes(val_bytes))
     return fail(SPC_ERR_INVALID_ARGUMENT, "hash_items: bad argument");
@@ -408,10 +450,28 @@ extern "C" int spc_hash_items(void* table, int64_t capacity, int64_t count, int 
   SPC_LAUNCH_OK();
   size_t cub_bytes = L.cub_bytes;
   SPC_CUDA_OK(cub::DeviceRadixSort::SortPairs(w + L.off_cub, cub_bytes, dkeys, skeys, dslots, sslots,
-                                              static_cast<int>(count), 0, 64, st));
+                                              static_cast<int>(count), 0, (key_bits > 0 && key_bits < 64) ? key_bits : 64, st));
   note_launch();
   hash_emit_kernel<<<static_cast<int>(ceil_div(count, kHashThreads)), kHashThreads, 0, st>>>(
       t, skeys, sslots, count, assign_kind, out_keys, key_bytes, out_values, val_bytes, out_limit);
+  SPC_LAUNCH_OK();
+  return SPC_OK;
+}
+
+extern "C" int spc_coords_to_keys(const int32_t* indices, int64_t n, int width, const int64_t* shape, int key_bytes,
+                                  void* keys, void* stream) {
+  if (n < 0 || width < 1 || width > 8 || shape == nullptr || (key_bytes != 4 && key_bytes != 8))
+    return fail(SPC_ERR_INVALID_ARGUMENT, "coords_to_keys: bad argument");
+  if (n == 0) return SPC_OK;
+  KeyShape g;
+  g.width = width;
+  long long stride = 1;
+  for (int d = width - 1; d >= 0; --d) {
+    g.stride[d] = stride;
+    stride *= shape[d];
+  }
+  coords_to_keys_kernel<<<static_cast<int>(ceil_div(n, kHashThreads)), kHashThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      g, indices, n, keys, key_bytes);
   SPC_LAUNCH_OK();
   return SPC_OK;
 }

@@ -227,6 +227,10 @@ class _RowsScatterAdd(Function):
 
 
 def _sparse_add_cuda(tens):
+    import ctypes
+
+    from spconv_triton_b200 import _lib
+
     from .core import SparseConvTensor
     from .hash import HashTable
 
@@ -250,14 +254,24 @@ def _sparse_add_cuda(tens):
     shape = [first.batch_size, *first.spatial_shape]
     whole_shape = int(np.prod(shape))
     k_type = torch.int64 if whole_shape >= _MAX_INT32 else torch.int32
-    table = HashTable(first.features.device, k_type, torch.int32, max(2 * table_size, 2))
+    # sized for every row of every operand (the reference doubles this; capacity only), so no insert can fill it
+    table = HashTable(first.features.device, k_type, torch.int32, max(table_size, 1))
+    table._key_bits = max(1, (whole_shape - 1).bit_length())
+    lib = _lib.load()
+    shape_arr = (ctypes.c_int64 * len(shape))(*[int(v) for v in shape])
     scalars = []
-    for ten in tens:
-        indices = ten.indices.long() if whole_shape >= _MAX_INT32 else ten.indices
-        scalar = _indice_to_scalar(indices, shape)
-        scalars.append(scalar)
-        table.insert(scalar)
-    count_val = int(table.assign_arange_().item())
+    with torch.cuda.device(first.features.device):
+        stream = _lib.current_stream(first.features.device)
+        for ten in tens:
+            indices = ten.indices.contiguous()
+            if indices.shape[1] != len(shape):
+                raise AssertionError
+            scalar = torch.empty(indices.shape[0], dtype=k_type, device=indices.device)
+            _lib.check(lib.spc_coords_to_keys(_lib.ptr(indices), int(indices.shape[0]), len(shape), shape_arr,
+                                              scalar.element_size(), _lib.ptr(scalar), stream))
+            scalars.append(scalar)
+            table._insert_unchecked(scalar)
+    count_val = table._items(0, None, None, 0)  # assign_arange_ without the device round trip of its count
     rows = [table.query(scalar)[0] for scalar in scalars]
     out_features, out_indices = _RowsScatterAdd.apply(
         count_val, len(tens), *rows, *[t.indices for t in tens], *[t.features for t in tens])

@@ -46,6 +46,7 @@ class HashTable:
         self._cap = _pow2_at_least(2 * self.max_size)
         self._buf = torch.empty(self._lib.spc_hash_bytes(self._cap), dtype=torch.uint8, device=device)
         self._epoch = 0
+        self._key_bits = 0  # set by callers that know every key is in [0, 2^bits): shortens the sort
         self._call("spc_hash_clear", _lib.ptr(self._buf), self._cap)
 
     # -- plumbing ---------------------------------------------------------------------------
@@ -74,6 +75,13 @@ class HashTable:
 
     # -- the reference's interface ----------------------------------------------------------
     def insert(self, keys: torch.Tensor, values: torch.Tensor | None = None):
+        self._insert_unchecked(keys, values)
+        stored, dropped = self._counters()
+        if dropped > 0 or stored > self.max_size:
+            raise AssertionError("hash table full")
+
+    def _insert_unchecked(self, keys: torch.Tensor, values: torch.Tensor | None = None):
+        """insert without the host read of the fill count (for callers that sized the table for all keys)."""
         keys = self._keys(keys)
         if values is not None:
             values = self._values(values)
@@ -82,9 +90,6 @@ class HashTable:
         self._epoch += 1
         self._call("spc_hash_insert", _lib.ptr(self._buf), self._cap, _lib.ptr(keys), self._kb, _lib.ptr(values),
                    self._vb, int(keys.shape[0]), self._epoch)
-        stored, dropped = self._counters()
-        if dropped > 0 or stored > self.max_size:
-            raise AssertionError("hash table full")
 
     def query(self, keys: torch.Tensor, values: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
         keys = self._keys(keys)
@@ -112,8 +117,9 @@ class HashTable:
         stored, _ = self._counters()
         if stored > 0:
             ws = torch.empty(self._lib.spc_hash_items_workspace_bytes(stored), dtype=torch.uint8, device=self.device)
-            self._call("spc_hash_items", _lib.ptr(self._buf), self._cap, stored, assign_kind, _lib.ptr(ws), ws.numel(),
-                       _lib.ptr(out_keys), self._kb, _lib.ptr(out_values), self._vb, int(limit))
+            self._call("spc_hash_items", _lib.ptr(self._buf), self._cap, stored, assign_kind, self._key_bits,
+                       _lib.ptr(ws), ws.numel(), _lib.ptr(out_keys), self._kb, _lib.ptr(out_values), self._vb,
+                       int(limit))
         return stored
 
     def _count_tensor(self, n: int) -> torch.Tensor:
