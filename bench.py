@@ -395,6 +395,31 @@ def run_op_bench(args):
 
         emit("dense_channels_first", timed(lambda: x.dense(), iters), nbytes, rows=int(idx.shape[0]), dense_elems=vol * c,
              torch_definition_ms=timed(torch_dense, iters))
+    elif args.op == "global_pool":
+        # classification head: per-sample max / mean over 4 x 100k rows of 128 fp16 channels (batch order)
+        import spconv_triton_b200.pytorch as sp
+        from spconv_triton_b200.scenes import uniform_batch
+
+        batch, shape, c = 4, [41, 400, 352], 128
+        idx = torch.from_numpy(uniform_batch(21, batch, 100000, tuple(shape))).to(dev)
+        x = sp.SparseConvTensor(torch.randn(idx.shape[0], c, device=dev).half(), idx, shape, batch)
+        n = int(idx.shape[0])
+        gmax, gavg = sp.SparseGlobalMaxPool(), sp.SparseGlobalAvgPool()
+
+        def torch_definition():
+            # the reference's formulation: rows per sample, host read of the counts, one gather + max per sample
+            b = idx[:, 0].long()
+            counts = torch.bincount(b, minlength=batch).cpu().numpy()
+            order = torch.argsort(b, stable=True)
+            res, start = [], 0
+            for s in range(batch):
+                res.append(torch.max(x.features[order[start:start + counts[s]]], dim=0)[0])
+                start += counts[s]
+            return torch.stack(res)
+
+        emit("global_max_pool_400k_c128", timed(lambda: gmax(x), iters), n * c * 2 + n * 4, rows=n,
+             torch_definition_ms=timed(torch_definition, iters))
+        emit("global_avg_pool_400k_c128", timed(lambda: gavg(x), iters), n * 32 + n * 4, rows=n)
     elif args.op == "sparse_add":
         # the residual join of two branches with different voxel sets: 2 x 400k rows of 64 fp16 channels, 4 samples
         import spconv_triton_b200.pytorch as sp
@@ -494,7 +519,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-baseline-seconds", type=float, default=20.0)
-    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm", "voxelize", "dense", "sparse_add"],
+    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm", "voxelize", "dense", "sparse_add", "global_pool"],
                     help="single-operator timings at the other configurations instead of the headline benchmark")
     ap.add_argument("--voxel-order", default="random", choices=["random", "sorted"],
                     help="--op pool: input voxel order (random = as a voxeliser emits them, sorted = as a previous layer's rulebook emits them)")

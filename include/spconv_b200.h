@@ -219,6 +219,20 @@ int spc_dense_gather(const void* dense, const int32_t* indices, int64_t n, int c
                      int batch_size, const int32_t* spatial_shape, int channels_first, int elem_size,
                      void* features, void* stream);
 
+/* Global pooling: replaces SparseGlobalMaxOrAvgPool.forward, spconv_triton/pytorch/pool.py:238-265
+ * (with global_pool_rearrange, ops.py:436-450).  features [n, channels] of dtype (fp16, bf16, fp32),
+ * indices [n, idx_width] int32 with the sample number in column 0 (rows of other samples than
+ * 0..batch-1 are ignored; any row order).
+ *   is_mean = 0: out [batch, channels] = per-sample maximum (NaN propagates), argmax [batch, channels]
+ *                (or NULL) = the smallest row that holds it, -1 for a sample without rows;
+ *   is_mean = 1: out [batch] = per-sample mean of CHANNEL 0 (what upstream returns, pool.py:258-261),
+ *                accumulated in fp64; NaN for a sample without rows.
+ * counts [batch] int32 (or NULL) receives the rows per sample. */
+size_t spc_global_pool_workspace_bytes(int batch, int channels);
+int spc_global_pool(const void* features, const int32_t* indices, int64_t n, int channels, int idx_width,
+                    int batch, int dtype, int is_mean, void* ws, size_t ws_bytes, void* out,
+                    int32_t* argmax, int32_t* counts, void* stream);
+
 /* ---- key -> value hash table and misaligned sparse add ------------------- */
 
 /* A fixed-capacity GPU hash table; replaces HashTable, spconv_triton/pytorch/hash.py:15-110

@@ -181,13 +181,54 @@ class SparseGlobalMaxOrAvgPool(SparseModule):
             raise NotImplementedError("int8 is not supported by spconv_triton")
         if not isinstance(x, SparseConvTensor):
             raise AssertionError
-        rows, counts = ops.global_pool_rearrange(x.indices, x.batch_size)
-        counts = counts.cpu().numpy()
-        res = []
-        for b in range(x.batch_size):
-            feats = x.features[rows[b, : counts[b]].long()]
-            res.append(torch.mean(feats, dim=0)[0] if self.is_mean else torch.max(feats, dim=0)[0])
-        return torch.stack(res)
+        if not x.features.is_cuda:
+            raise NotImplementedError("spconv_triton_b200 global pooling is CUDA only")
+        return _GlobalPool.apply(x.features, x.indices, int(x.batch_size), bool(self.is_mean))
+
+
+class _GlobalPool(torch.autograd.Function):
+    """One pass of ``spc_global_pool`` over the features; the gradient goes to the row that held
+    each maximum, or evenly to channel 0 of a sample's rows for the mean."""
+
+    @staticmethod
+    def forward(ctx, features, indices, batch_size, is_mean):
+        from spconv_triton_b200 import _lib
+
+        features, indices = features.contiguous(), indices.contiguous()
+        n, c = int(features.shape[0]), int(features.shape[1])
+        dev = features.device
+        lib = _lib.load()
+        out = torch.empty([batch_size] if is_mean else [batch_size, c], dtype=features.dtype, device=dev)
+        argmax = None if is_mean else torch.empty([batch_size, c], dtype=torch.int32, device=dev)
+        counts = torch.empty([batch_size], dtype=torch.int32, device=dev)
+        ws = torch.empty(lib.spc_global_pool_workspace_bytes(batch_size, c), dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(lib.spc_global_pool(
+                _lib.ptr(features), _lib.ptr(indices), n, c, int(indices.shape[1]), batch_size,
+                _lib.dtype_code(features.dtype), int(is_mean), _lib.ptr(ws), ws.numel(), _lib.ptr(out),
+                _lib.ptr(argmax), _lib.ptr(counts), _lib.current_stream(dev)))
+        if not is_mean and bool((counts == 0).any()):
+            # torch.max over zero rows raises in the reference as well (pool.py:262)
+            raise RuntimeError("SparseGlobalMaxPool: a sample has no voxels")
+        if is_mean:
+            ctx.save_for_backward(indices, counts)
+        else:
+            ctx.save_for_backward(argmax)
+        ctx.meta = (n, c, is_mean)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        n, c, is_mean = ctx.meta
+        gin = torch.zeros([n, c], dtype=grad.dtype, device=grad.device)
+        if is_mean:
+            indices, counts = ctx.saved_tensors
+            gin[:, 0] = (grad / counts.to(grad.dtype))[indices[:, 0].long()]
+        else:
+            (argmax,) = ctx.saved_tensors
+            cols = torch.arange(c, device=grad.device).expand_as(argmax)
+            gin[argmax.long().reshape(-1), cols.reshape(-1)] = grad.reshape(-1)
+        return gin, None, None, None
 
 
 class SparseGlobalAvgPool(SparseGlobalMaxOrAvgPool):
