@@ -219,6 +219,20 @@ int spc_dense_gather(const void* dense, const int32_t* indices, int64_t n, int c
                      int batch_size, const int32_t* spatial_shape, int channels_first, int elem_size,
                      void* features, void* stream);
 
+/* Dense -> sparse: replaces SparseConvTensor.from_dense, spconv_triton/pytorch/core.py:296-318
+ * (torch to_sparse(ndim - 1) there).  dense is channels-last [B, *spatial, C] with `cells` =
+ * B * prod(spatial) < 2^31 cells of `channels` elements of elem_size bytes; is_float = 1 treats -0.0
+ * as zero.  A cell is kept when any channel is non-zero; rows are numbered in ascending cell order.
+ *   spc_from_dense_count    marks and numbers the cells into ws; *count = kept cells (host value;
+ *                           synchronises the stream);
+ *   spc_from_dense_indices  writes indices [count, ndim + 1] (batch, then coordinates) from the same ws.
+ * The features of the rows are then read with spc_dense_gather(channels_first = 0). */
+size_t spc_from_dense_workspace_bytes(int64_t cells);
+int spc_from_dense_count(const void* dense, int64_t cells, int channels, int elem_size, int is_float,
+                         void* ws, size_t ws_bytes, int64_t* count, void* stream);
+int spc_from_dense_indices(const void* ws, int64_t cells, int ndim, const int32_t* spatial_shape,
+                           int32_t* indices, void* stream);
+
 /* Global pooling: replaces SparseGlobalMaxOrAvgPool.forward, spconv_triton/pytorch/pool.py:238-265
  * (with global_pool_rearrange, ops.py:436-450).  features [n, channels] of dtype (fp16, bf16, fp32),
  * indices [n, idx_width] int32 with the sample number in column 0 (rows of other samples than

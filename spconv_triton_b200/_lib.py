@@ -77,6 +77,9 @@ _PROTOTYPES = {
     "spc_pairs_to_rowmajor": (c_int, [_P, c_int, c_int64, _P, _P]),
     "spc_dense_scatter": (c_int, [_P, _P, c_int64, c_int, c_int, c_int, POINTER(ctypes.c_int32), c_int, c_int, _P, _P]),
     "spc_dense_gather": (c_int, [_P, _P, c_int64, c_int, c_int, c_int, POINTER(ctypes.c_int32), c_int, c_int, _P, _P]),
+    "spc_from_dense_workspace_bytes": (c_size_t, [c_int64]),
+    "spc_from_dense_count": (c_int, [_P, c_int64, c_int, c_int, c_int, _P, c_size_t, POINTER(c_int64), _P]),
+    "spc_from_dense_indices": (c_int, [_P, c_int64, c_int, POINTER(ctypes.c_int32), _P, _P]),
     "spc_global_pool_workspace_bytes": (c_size_t, [c_int, c_int]),
     "spc_global_pool": (c_int, [_P, _P, c_int64, c_int, c_int, c_int, c_int, c_int, _P, c_size_t, _P, _P, _P, _P]),
     "spc_hash_bytes": (c_size_t, [c_int64]),

@@ -101,16 +101,25 @@ gp_max_kernel(const T* __restrict__ feats, const int32_t* __restrict__ idx, long
   for (int c = threadIdx.x; c < channels; c += kGpThreads) {
     int cur = -1;
     unsigned long long best = 0;
-    for (int i = 0; i < rows; ++i) {
-      const int b = sample[i];
-      if (b != cur) {
-        if (cur >= 0 && cur < batch) atomicMax(&w.best[static_cast<long long>(cur) * channels + c], best);
-        cur = b, best = 0;
+    constexpr int kAhead = 8;  // loads of eight rows are issued before any of them is compared
+    for (int i0 = 0; i0 < rows; i0 += kAhead) {
+      float v[kAhead];
+#pragma unroll
+      for (int j = 0; j < kAhead; ++j)
+        v[j] = i0 + j < rows ? as_float(feats[(r0 + i0 + j) * channels + c]) : 0.f;
+#pragma unroll
+      for (int j = 0; j < kAhead; ++j) {
+        const int i = i0 + j;
+        if (i >= rows) break;
+        const int b = sample[i];
+        if (b != cur) {
+          if (cur >= 0 && cur < batch) atomicMax(&w.best[static_cast<long long>(cur) * channels + c], best);
+          cur = b, best = 0;
+        }
+        const unsigned long long cand = (static_cast<unsigned long long>(ordered(v[j])) << 32) |
+                                        (0xffffffffu - static_cast<uint32_t>(r0 + i));
+        best = cand > best ? cand : best;
       }
-      const unsigned long long cand =
-          (static_cast<unsigned long long>(ordered(as_float(feats[(r0 + i) * channels + c]))) << 32) |
-          (0xffffffffu - static_cast<uint32_t>(r0 + i));
-      best = cand > best ? cand : best;
     }
     if (cur >= 0 && cur < batch) atomicMax(&w.best[static_cast<long long>(cur) * channels + c], best);
   }

@@ -209,6 +209,10 @@ class SparseConvTensor(metaclass=SpConvTensorMeta):
     @classmethod
     def from_dense(cls, x: torch.Tensor):
         """From a channel-last dense tensor [B, *spatial, C]."""
+        if (x.is_cuda and 3 <= x.ndim <= 6 and x.element_size() in (1, 2, 4, 8) and not x.is_complex()
+                and x.dtype != torch.bool and 0 < x.numel() and x.numel() // x.shape[-1] < 2 ** 31):
+            feats, indices = _FromDense.apply(x)
+            return cls(feats, indices, list(x.shape[1:-1]), x.shape[0])
         sp = x.to_sparse(x.ndim - 1)
         return cls(sp.values(), sp.indices().permute(1, 0).contiguous().int(), list(sp.shape[1:-1]),
                    sp.shape[0])
@@ -281,6 +285,60 @@ class _DenseScatter(torch.autograd.Function):
         gfeat = torch.empty((indices.shape[0], c), dtype=grad.dtype, device=grad.device)
         _dense_call("spc_dense_gather", grad.contiguous(), indices, batch_size, spatial_shape, channels_first, gfeat)
         return gfeat, None, None, None, None
+
+
+class _FromDense(torch.autograd.Function):
+    """[B, *spatial, C] -> (features [n, C], indices [n, ndim + 1]) of the cells with a non-zero
+    channel, in ascending cell order (reference: core.py:296-304 through torch's to_sparse)."""
+
+    @staticmethod
+    def forward(ctx, x):
+        import ctypes
+
+        from spconv_triton_b200 import _lib
+
+        x = x.contiguous()
+        lib = _lib.load()
+        spatial, c = [int(v) for v in x.shape[1:-1]], int(x.shape[-1])
+        cells = x.numel() // c
+        shape = (ctypes.c_int32 * len(spatial))(*spatial)
+        ws = torch.empty(lib.spc_from_dense_workspace_bytes(cells), dtype=torch.uint8, device=x.device)
+        count = ctypes.c_int64(0)
+        with torch.cuda.device(x.device):
+            stream = _lib.current_stream(x.device)
+            _lib.check(lib.spc_from_dense_count(_lib.ptr(x), cells, c, x.element_size(), int(x.is_floating_point()),
+                                                _lib.ptr(ws), ws.numel(), ctypes.byref(count), stream))
+            n = int(count.value)
+            indices = torch.empty([n, len(spatial) + 1], dtype=torch.int32, device=x.device)
+            feats = torch.empty([n, c], dtype=x.dtype, device=x.device)
+            if n > 0:
+                _lib.check(lib.spc_from_dense_indices(_lib.ptr(ws), cells, len(spatial), shape, _lib.ptr(indices), stream))
+        if n > 0:
+            if x.element_size() == 1:
+                feats = x.reshape(cells, c)[_cell_numbers(indices, spatial)]
+            else:
+                _dense_call("spc_dense_gather", x, indices, x.shape[0], spatial, False, feats)
+        ctx.save_for_backward(indices)
+        ctx.meta = (tuple(x.shape), spatial)
+        ctx.mark_non_differentiable(indices)
+        return feats, indices
+
+    @staticmethod
+    def backward(ctx, grad, _grad_indices):
+        (indices,) = ctx.saved_tensors
+        shape, spatial = ctx.meta
+        out = torch.empty(shape, dtype=grad.dtype, device=grad.device)
+        if indices.shape[0] == 0:
+            return out.zero_()
+        _dense_call("spc_dense_scatter", grad.contiguous(), indices, shape[0], spatial, False, out)
+        return out
+
+
+def _cell_numbers(indices, spatial):
+    lin = indices[:, 0].long()
+    for d, s in enumerate(spatial):
+        lin = lin * s + indices[:, d + 1]
+    return lin
 
 
 def expand_nd(ndim: int, val) -> list[int]:

@@ -4,7 +4,7 @@ Run once where the reference checkout is readable at $SPCONV_REFERENCE_ROOT:
 
     python tests/golden/make_golden_add.py
 
-Three kinds of cases are written:
+Four kinds of cases are written:
 1. ``frozen``: the three ``sparse_add`` cases of the reference's own tests/data/golden_misc.pt
    (sparse_add, sparse_add_hash_based, add_table_misaligned), re-saved unchanged;
 2. ``add``: outputs of the reference's ``functional.sparse_add_hash_based`` itself (pure torch,
@@ -129,7 +129,10 @@ def main():
         ("query", torch.tensor([1, 2], dtype=torch.int32)), ("assign_arange_",), ("items",),
         ("insert_exist_keys", torch.tensor([1], dtype=torch.int32), torch.tensor([5], dtype=torch.int32))])
 
-    torch.save(dict(frozen=frozen, add=add, table=tables), OUT)
+    misc = torch.load(Path(REF) / "tests" / "data" / "golden_misc.pt", map_location="cpu", weights_only=False)["cases"]
+    from_dense = [dict(id=c["id"], dense=c["dense"], indices=c["expect"]["indices"], features=c["expect"]["features"])
+                  for c in misc if c.get("kind") == "from_dense"]
+    torch.save(dict(frozen=frozen, add=add, table=tables, from_dense=from_dense), OUT)
     print("frozen", [c["id"] for c in frozen], "add", [c["id"] for c in add], "table", [t["id"] for t in tables])
     print(OUT, OUT.stat().st_size)
 
