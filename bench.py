@@ -452,6 +452,23 @@ def run_op_bench(args):
 
         emit("sparse_add_hash_based_2x400k_c64", timed(lambda: sp.functional.sparse_add_hash_based(*tens), iters), nbytes,
              rows_in=n_in, rows_out=n_out, torch_definition_ms=timed(torch_definition, iters))
+    elif args.op == "from_dense":
+        # a BEV feature map back to sparse rows: [8, 200, 176, 128] fp16 channels-last, 12 % of the cells occupied
+        import spconv_triton_b200.pytorch as sp
+
+        g = torch.Generator().manual_seed(4)
+        keep = (torch.rand(8, 200, 176, 1, generator=g) < 0.12).to(dev)
+        x = (torch.randn(8, 200, 176, 128, device=dev) * keep).half()
+        t = sp.SparseConvTensor.from_dense(x)
+        rows, cells = int(t.indices.shape[0]), 8 * 200 * 176
+        nbytes = cells * 128 * 2 + cells * 8 + rows * (12 + 2 * 128 * 2)
+
+        def torch_definition():
+            s_ = x.to_sparse(x.ndim - 1)
+            return s_.values(), s_.indices().permute(1, 0).contiguous().int()
+
+        emit("from_dense_8x200x176_c128", timed(lambda: sp.SparseConvTensor.from_dense(x), iters), nbytes, rows=rows,
+             cells=cells, torch_definition_ms=timed(torch_definition, iters))
     elif args.op == "voxelize":
         # the step before the backbone: 8 LiDAR sweeps of 150k points -> voxels of 0.16 x 0.16 x 0.2 m
         from spconv_triton_b200.pytorch.utils import PointToVoxel
@@ -519,7 +536,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-baseline-seconds", type=float, default=20.0)
-    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm", "voxelize", "dense", "sparse_add", "global_pool"],
+    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm", "voxelize", "dense", "sparse_add", "global_pool", "from_dense"],
                     help="single-operator timings at the other configurations instead of the headline benchmark")
     ap.add_argument("--voxel-order", default="random", choices=["random", "sorted"],
                     help="--op pool: input voxel order (random = as a voxeliser emits them, sorted = as a previous layer's rulebook emits them)")
