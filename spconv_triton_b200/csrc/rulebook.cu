@@ -14,6 +14,7 @@
 // output coordinates, which reproduces the ascending row numbering that
 // torch.unique gives the reference.
 #include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_scan.cuh>
 
 #include <algorithm>
 #include <climits>
@@ -56,6 +57,16 @@ struct Table<false> {
   using key_t = uint32_t;
   unsigned long long* slots;
   uint32_t cap_mask;
+  // Dense numbering (output side of strided layers on a grid small enough for a bitmap): one bit per
+  // cell and, per 32-bit word, the number of set bits before it.  The value of a key is then its
+  // rank among the set bits = its row in ascending key order, with no hash table and no sort.
+  uint32_t* obits = nullptr;
+  const uint32_t* oprefix = nullptr;
+  __device__ __forceinline__ int rank_of(key_t key) const {
+    const uint32_t w = __ldg(&obits[key >> 5]);
+    if (!((w >> (key & 31u)) & 1u)) return -1;
+    return static_cast<int>(__ldg(&oprefix[key >> 5]) + __popc(w & ((1u << (key & 31u)) - 1u)));
+  }
   static constexpr unsigned long long kEmpty = ~0ull;
 
   // Four consecutive keys (neighbours along the fastest coordinate) share one
@@ -94,6 +105,7 @@ struct Table<false> {
     return -1;
   }
   __device__ int find(key_t key) const {
+    if (obits != nullptr) return rank_of(key);
     uint32_t s = home(key);
     for (uint32_t probe = 0; probe <= (cap_mask >> 2); ++probe) {
       const unsigned long long v = __ldg(&slots[s]);
@@ -316,6 +328,32 @@ insert_inputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ 
 // inserts, the warp reserves room for all of them in `uniq` with ONE atomicAdd
 // per group (a per-insert counter serialises on a single address), and a
 // second walk over the group writes the keys.
+__device__ __forceinline__ uint32_t* dense_bits(const Table<false>& t) { return t.obits; }
+__device__ __forceinline__ uint32_t* dense_bits(const Table<true>&) { return nullptr; }
+
+// Dense numbering, step 2: set bits per word (scanned in place afterwards).
+__global__ void __launch_bounds__(kThreads)
+count_bits_kernel(const uint32_t* __restrict__ bits, long long words, uint32_t* __restrict__ counts) {
+  const long long i = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  if (i < words) counts[i] = __popc(bits[i]);
+}
+
+// Dense numbering, step 3: the keys of the set bits in ascending order, and their total.
+__global__ void __launch_bounds__(kThreads)
+expand_bits_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict__ prefix, long long words,
+                   long long limit, uint32_t* __restrict__ sorted, int* counters) {
+  const long long i = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  if (i >= words) return;
+  uint32_t w = bits[i];
+  long long at = prefix[i];
+  if (i == words - 1) counters[kUniqueCount] = static_cast<int>(at + __popc(w));
+  while (w != 0 && at < limit) {
+    const int b = __ffs(w) - 1;
+    sorted[at++] = static_cast<uint32_t>(i * 32 + b);
+    w &= w - 1;
+  }
+}
+
 template <int ND, bool K64>
 __global__ void __launch_bounds__(kThreads)
 enumerate_outputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n,
@@ -336,9 +374,15 @@ enumerate_outputs_kernel(const __grid_constant__ Geo g, const int32_t* __restric
       for (int kk = 0; kk < gcount; ++kk) {
         const long long key = out_key_from_input<ND>(g, c, od.pos);
         if (key >= 0) {
-          const int r = tout.insert_unique(static_cast<key_t>(key));
-          if (r < 0) atomicExch(&counters[kStatus], SPC_ERR_HASH_TABLE_FULL);
-          fresh |= static_cast<uint32_t>(r > 0) << kk;
+          if (dense_bits(tout) != nullptr) {
+            uint32_t* word = dense_bits(tout) + (key >> 5);
+            const uint32_t bit = 1u << (key & 31);
+            if (!(*word & bit)) atomicOr(word, bit);
+          } else {
+            const int r = tout.insert_unique(static_cast<key_t>(key));
+            if (r < 0) atomicExch(&counters[kStatus], SPC_ERR_HASH_TABLE_FULL);
+            fresh |= static_cast<uint32_t>(r > 0) << kk;
+          }
         }
         od.next(g);
       }
@@ -690,6 +734,8 @@ struct Layout {
   int key_bits;
   int mic;
   int64_t bound;  // upper bound on n_out
+  int64_t obits_words = 0;  // dense numbering of the outputs: words of the bitmap (0 = hash table + sort)
+  size_t off_obits = 0, off_oprefix = 0, off_scan = 0, scan_bytes = 0;
   uint32_t cap_in, cap_out;
   int64_t n_blocks_native;
   size_t off_counters, off_tin, off_tin_vals, off_tout, off_tout_vals, off_uniq, off_sorted;
@@ -802,6 +848,17 @@ Layout make_layout(const Geo& g, int64_t n_in) {
   // answers "absent" without a hash probe.
   L.bitmap_bytes = (!L.k64 && vol_in / 8.0 <= 24.0 * 1024 * 1024) ? align_up(static_cast<size_t>(vol_in / 8.0) + 4, 256) : 0;
   L.off_bitmap = take(L.bitmap_bytes);
+  // The same for the output grid of a strided layer; there the bitmap also numbers the outputs.
+  L.obits_words = (!g.subm && !L.k64 && vol_out / 8.0 <= 24.0 * 1024 * 1024) ? static_cast<int64_t>(vol_out / 32.0) + 1 : 0;
+  L.off_obits = take(static_cast<size_t>(L.obits_words) * 4);
+  L.off_oprefix = take(static_cast<size_t>(L.obits_words) * 4);
+  if (L.obits_words) {
+    size_t scan_bytes = 0;
+    cub::DeviceScan::ExclusiveSum(nullptr, scan_bytes, static_cast<uint32_t*>(nullptr), static_cast<uint32_t*>(nullptr),
+                                  static_cast<int>(L.obits_words));
+    L.off_scan = take(scan_bytes);
+    L.scan_bytes = scan_bytes;
+  }
   L.total = off;
   return L;
 }
@@ -822,6 +879,22 @@ Table<true> table_at<true>(char* ws, size_t off_slots, size_t off_vals, uint32_t
   t.vals = reinterpret_cast<int*>(ws + off_vals);
   t.cap_mask = cap ? cap - 1 : 0;
   return t;
+}
+
+template <bool K64>
+Table<K64> tout_at(char* ws, const Layout& L);
+template <>
+Table<false> tout_at<false>(char* ws, const Layout& L) {
+  Table<false> t = table_at<false>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
+  if (L.obits_words) {
+    t.obits = reinterpret_cast<uint32_t*>(ws + L.off_obits);
+    t.oprefix = reinterpret_cast<const uint32_t*>(ws + L.off_oprefix);
+  }
+  return t;
+}
+template <>
+Table<true> tout_at<true>(char* ws, const Layout& L) {
+  return table_at<true>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
 }
 
 inline unsigned blocks_for(int64_t n) { return static_cast<unsigned>(ceil_div(std::max<int64_t>(n, 1), kThreads)); }
@@ -846,13 +919,30 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
     *n_out_host = n_in;
     return SPC_OK;
   }
-  SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tout, 0xFF, static_cast<size_t>(L.cap_out) * 8, st));
-  if (K64) SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tout_vals, 0x7F, static_cast<size_t>(L.cap_out) * 4, st));
-  Table<K64> tout = table_at<K64>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
+  const bool dense_out = L.obits_words != 0;
+  if (dense_out) {
+    SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_obits, 0, static_cast<size_t>(L.obits_words) * 4, st));
+  } else {
+    SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tout, 0xFF, static_cast<size_t>(L.cap_out) * 8, st));
+    if (K64) SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tout_vals, 0x7F, static_cast<size_t>(L.cap_out) * 4, st));
+  }
+  Table<K64> tout = tout_at<K64>(ws, L);
   key_t* uniq = reinterpret_cast<key_t*>(ws + L.off_uniq);
   key_t* sorted = reinterpret_cast<key_t*>(ws + L.off_sorted);
   enumerate_outputs_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, tout, uniq, counters);
   SPC_LAUNCH_OK();
+  if (dense_out) {
+    uint32_t* bits = reinterpret_cast<uint32_t*>(ws + L.off_obits);
+    uint32_t* prefix = reinterpret_cast<uint32_t*>(ws + L.off_oprefix);
+    count_bits_kernel<<<blocks_for(L.obits_words), kThreads, 0, st>>>(bits, L.obits_words, prefix);
+    SPC_LAUNCH_OK();
+    size_t scan_bytes = L.scan_bytes;
+    SPC_CUDA_OK(cub::DeviceScan::ExclusiveSum(ws + L.off_scan, scan_bytes, prefix, prefix,
+                                              static_cast<int>(L.obits_words), st));
+    expand_bits_kernel<<<blocks_for(L.obits_words), kThreads, 0, st>>>(
+        bits, prefix, L.obits_words, L.bound, reinterpret_cast<uint32_t*>(sorted), counters);
+    SPC_LAUNCH_OK();
+  }
   int host[2] = {0, 0};
   SPC_CUDA_OK(cudaMemcpyAsync(host, counters, sizeof(host), cudaMemcpyDeviceToHost, st));
   SPC_CUDA_OK(cudaStreamSynchronize(st));
@@ -862,6 +952,7 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
   if (n_out == 0) return SPC_OK;
   if (n_out > L.bound) return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "rulebook: %lld outputs exceed bound %lld",
                                    static_cast<long long>(n_out), static_cast<long long>(L.bound));
+  if (dense_out) return SPC_OK;  // numbered and listed in ascending order already
   size_t cub_bytes = L.cub_bytes;
   SPC_CUDA_OK(cub::DeviceRadixSort::SortKeys(ws + L.off_cub, cub_bytes, uniq, sorted, n_out, 0,
                                               std::min<int>(L.key_bits, sizeof(key_t) * 8), st));
@@ -915,7 +1006,7 @@ int igemm_backward_impl(const Geo& g, const Layout& L, const int32_t* idx, int64
                         int32_t* pair_bwd, int32_t* mask_bwd, int32_t* argsort_bwd, const uint32_t* split_masks,
                         int n_split, int do_sort, int32_t* bwd_rm, cudaStream_t st) {
   const int kvp = (g.kv + 3) & ~3;
-  Table<K64> tout = table_at<K64>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
+  Table<K64> tout = tout_at<K64>(ws, L);
   uint32_t* words = reinterpret_cast<uint32_t*>(ws + L.off_words);
   fill_bwd_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(
       g, idx, n_in, n_out, tout, pair_bwd, mask_bwd ? words : nullptr, L.mic, bwd_rm, kvp);
@@ -933,7 +1024,7 @@ int igemm_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, 
   using key_t = typename Table<K64>::key_t;
   const int kvp = (g.kv + 3) & ~3;
   Table<K64> tin = table_at<K64>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
-  Table<K64> tout = table_at<K64>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
+  Table<K64> tout = tout_at<K64>(ws, L);
   const key_t* sorted = reinterpret_cast<const key_t*>(ws + L.off_sorted);
   uint32_t* words = reinterpret_cast<uint32_t*>(ws + L.off_words);
   const uint32_t* bitmap = L.bitmap_bytes ? reinterpret_cast<const uint32_t*>(ws + L.off_bitmap) : nullptr;
@@ -957,7 +1048,7 @@ int native_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in,
                 int32_t* out_indices, int32_t* pair, int32_t* npl, cudaStream_t st) {
   using key_t = typename Table<K64>::key_t;
   Table<K64> tin = table_at<K64>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
-  Table<K64> tout = table_at<K64>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
+  Table<K64> tout = tout_at<K64>(ws, L);
   const Table<K64>& lookup = g.subm ? tin : tout;
   const key_t* sorted = reinterpret_cast<const key_t*>(ws + L.off_sorted);
   int* block_counts = reinterpret_cast<int*>(ws + L.off_native);
