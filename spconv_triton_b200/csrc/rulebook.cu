@@ -62,6 +62,12 @@ struct Table<false> {
   // rank among the set bits = its row in ascending key order, with no hash table and no sort.
   uint32_t* obits = nullptr;
   const uint32_t* oprefix = nullptr;
+  // Input side: rows equal ranks only when the rows came in ascending key order (the outputs of an
+  // earlier layer do); `unsorted` points at a device flag that says they did not.
+  const int* unsorted = nullptr;
+  __device__ __forceinline__ bool ranked() const {
+    return obits != nullptr && (unsorted == nullptr || *unsorted == 0);
+  }
   __device__ __forceinline__ int rank_of(key_t key) const {
     const uint32_t w = __ldg(&obits[key >> 5]);
     if (!((w >> (key & 31u)) & 1u)) return -1;
@@ -105,7 +111,7 @@ struct Table<false> {
     return -1;
   }
   __device__ int find(key_t key) const {
-    if (obits != nullptr) return rank_of(key);
+    if (ranked()) return rank_of(key);
     uint32_t s = home(key);
     for (uint32_t probe = 0; probe <= (cap_mask >> 2); ++probe) {
       const unsigned long long v = __ldg(&slots[s]);
@@ -302,7 +308,7 @@ __device__ __forceinline__ void delinearize_out(const Geo& g, long long lin, int
   c[0] = static_cast<int>(lin);
 }
 
-enum Counter { kUniqueCount = 0, kStatus = 1 };
+enum Counter { kUniqueCount = 0, kStatus = 1, kUnsorted = 2 };
 
 // ------------------------------------------------------------------------
 // Phase 1 kernels
@@ -313,13 +319,32 @@ insert_inputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ 
                      Table<K64> tin, int* counters, uint32_t* __restrict__ bitmap) {
   const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
   if (j >= n) return;
+  if (bitmap != nullptr && counters[kUnsorted] == 0) return;  // rows are ranks of the bitmap
   int c[ND + 1];
   load_coord<ND>(idx, j, c);
   using key_t = typename Table<K64>::key_t;
   const long long key = in_key_of<ND>(g, c);
   if (!tin.insert_min(static_cast<key_t>(key), static_cast<uint32_t>(j)))
     atomicExch(&counters[kStatus], SPC_ERR_HASH_TABLE_FULL);
-  if (bitmap != nullptr) atomicOr(&bitmap[key >> 5], 1u << (key & 31));
+}
+
+// With a bitmap of the input grid: sets the bit of every input cell and notes whether the rows are in
+// strictly ascending key order.  If they are, a row number is the rank of its bit and the hash table
+// is not needed (insert_inputs_kernel then returns at once).
+template <int ND>
+__global__ void __launch_bounds__(kThreads)
+mark_inputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n,
+                   uint32_t* __restrict__ bitmap, int* counters) {
+  const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  if (j >= n) return;
+  int c[ND + 1];
+  load_coord<ND>(idx, j, c);
+  const long long key = in_key_of<ND>(g, c);
+  atomicOr(&bitmap[key >> 5], 1u << (key & 31));
+  if (j > 0) {
+    load_coord<ND>(idx, j - 1, c);
+    if (in_key_of<ND>(g, c) >= key) counters[kUnsorted] = 1;
+  }
 }
 
 // One thread per input row walks the kv offsets and inserts each candidate
@@ -330,6 +355,11 @@ insert_inputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ 
 // second walk over the group writes the keys.
 __device__ __forceinline__ uint32_t* dense_bits(const Table<false>& t) { return t.obits; }
 __device__ __forceinline__ uint32_t* dense_bits(const Table<true>&) { return nullptr; }
+
+__device__ __forceinline__ bool table_ranked(const Table<false>& t) { return t.ranked(); }
+__device__ __forceinline__ bool table_ranked(const Table<true>&) { return false; }
+__device__ __forceinline__ uint32_t rank_prefix(const Table<false>& t, long long key) { return __ldg(&t.oprefix[key >> 5]); }
+__device__ __forceinline__ uint32_t rank_prefix(const Table<true>&, long long) { return 0; }
 
 // Dense numbering, step 2: set bits per word (scanned in place afterwards).
 __global__ void __launch_bounds__(kThreads)
@@ -481,6 +511,8 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
   // kernel): their bitmap words, then their first hash probes, are requested together, so a row
   // has up to three L2 accesses in flight instead of one after the other.
   constexpr int kBatch = 3;
+  // rows in ascending key order: a neighbour's row is the rank of its bit (one load of the word's prefix)
+  const bool ranked = bitmap != nullptr && table_ranked(tin);
   for (int k0 = 0; k0 < g.kv; k0 += kBatch) {
     long long key[kBatch];
     uint32_t bits[kBatch];
@@ -510,13 +542,17 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
 #pragma unroll
     for (int b = 0; b < kBatch; ++b) {
       if (key[b] >= 0 && !((bits[b] >> (key[b] & 31)) & 1u)) key[b] = -1;
-      probe[b] = key[b] >= 0 ? tin.first_probe(static_cast<key_t>(key[b])) : 0ull;
+      probe[b] = key[b] < 0 ? 0ull
+                 : ranked  ? static_cast<unsigned long long>(rank_prefix(tin, key[b]))
+                           : tin.first_probe(static_cast<key_t>(key[b]));
     }
 #pragma unroll
     for (int b = 0; b < kBatch; ++b) {
       const int k = k0 + b;
       if (k >= g.kv) break;
-      const int j = key[b] >= 0 ? tin.finish(static_cast<key_t>(key[b]), probe[b]) : -1;
+      const int j = key[b] < 0 ? -1
+                    : ranked  ? static_cast<int>(probe[b]) + __popc(bits[b] & ((1u << (key[b] & 31)) - 1u))
+                              : tin.finish(static_cast<key_t>(key[b]), probe[b]);
       pair_fwd[static_cast<long long>(k) * n_out + r] = j;
       if (SUBM_BWD) {
         pair_bwd[static_cast<long long>(g.kv - 1 - k) * n_out + r] = j;
@@ -735,7 +771,7 @@ struct Layout {
   int mic;
   int64_t bound;  // upper bound on n_out
   int64_t obits_words = 0;  // dense numbering of the outputs: words of the bitmap (0 = hash table + sort)
-  size_t off_obits = 0, off_oprefix = 0, off_scan = 0, scan_bytes = 0;
+  size_t off_obits = 0, off_oprefix = 0, off_scan = 0, scan_bytes = 0, off_iprefix = 0;
   uint32_t cap_in, cap_out;
   int64_t n_blocks_native;
   size_t off_counters, off_tin, off_tin_vals, off_tout, off_tout_vals, off_uniq, off_sorted;
@@ -848,14 +884,16 @@ Layout make_layout(const Geo& g, int64_t n_in) {
   // answers "absent" without a hash probe.
   L.bitmap_bytes = (!L.k64 && vol_in / 8.0 <= 24.0 * 1024 * 1024) ? align_up(static_cast<size_t>(vol_in / 8.0) + 4, 256) : 0;
   L.off_bitmap = take(L.bitmap_bytes);
+  L.off_iprefix = take(L.bitmap_bytes);  // set bits before each word of the input bitmap
   // The same for the output grid of a strided layer; there the bitmap also numbers the outputs.
   L.obits_words = (!g.subm && !L.k64 && vol_out / 8.0 <= 24.0 * 1024 * 1024) ? static_cast<int64_t>(vol_out / 32.0) + 1 : 0;
   L.off_obits = take(static_cast<size_t>(L.obits_words) * 4);
   L.off_oprefix = take(static_cast<size_t>(L.obits_words) * 4);
-  if (L.obits_words) {
+  const int64_t scan_words = std::max<int64_t>(L.obits_words, static_cast<int64_t>(L.bitmap_bytes / 4));
+  if (scan_words) {
     size_t scan_bytes = 0;
     cub::DeviceScan::ExclusiveSum(nullptr, scan_bytes, static_cast<uint32_t*>(nullptr), static_cast<uint32_t*>(nullptr),
-                                  static_cast<int>(L.obits_words));
+                                  static_cast<int>(scan_words));
     L.off_scan = take(scan_bytes);
     L.scan_bytes = scan_bytes;
   }
@@ -879,6 +917,23 @@ Table<true> table_at<true>(char* ws, size_t off_slots, size_t off_vals, uint32_t
   t.vals = reinterpret_cast<int*>(ws + off_vals);
   t.cap_mask = cap ? cap - 1 : 0;
   return t;
+}
+
+template <bool K64>
+Table<K64> tin_at(char* ws, const Layout& L);
+template <>
+Table<false> tin_at<false>(char* ws, const Layout& L) {
+  Table<false> t = table_at<false>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
+  if (L.bitmap_bytes) {
+    t.obits = reinterpret_cast<uint32_t*>(ws + L.off_bitmap);
+    t.oprefix = reinterpret_cast<const uint32_t*>(ws + L.off_iprefix);
+    t.unsorted = reinterpret_cast<const int*>(ws + L.off_counters) + kUnsorted;
+  }
+  return t;
+}
+template <>
+Table<true> tin_at<true>(char* ws, const Layout& L) {
+  return table_at<true>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
 }
 
 template <bool K64>
@@ -910,9 +965,19 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
   SPC_CUDA_OK(cudaMemsetAsync(counters, 0, 256, st));
   SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin, 0xFF, static_cast<size_t>(L.cap_in) * 8, st));
   if (K64) SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin_vals, 0x7F, static_cast<size_t>(L.cap_in) * 4, st));
-  Table<K64> tin = table_at<K64>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
+  Table<K64> tin = tin_at<K64>(ws, L);
   uint32_t* bitmap = L.bitmap_bytes ? reinterpret_cast<uint32_t*>(ws + L.off_bitmap) : nullptr;
-  if (bitmap != nullptr) SPC_CUDA_OK(cudaMemsetAsync(bitmap, 0, L.bitmap_bytes, st));
+  if (bitmap != nullptr) {
+    SPC_CUDA_OK(cudaMemsetAsync(bitmap, 0, L.bitmap_bytes, st));
+    mark_inputs_kernel<ND><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, bitmap, counters);
+    SPC_LAUNCH_OK();
+    const int64_t words = static_cast<int64_t>(L.bitmap_bytes / 4);
+    uint32_t* iprefix = reinterpret_cast<uint32_t*>(ws + L.off_iprefix);
+    count_bits_kernel<<<blocks_for(words), kThreads, 0, st>>>(bitmap, words, iprefix);
+    SPC_LAUNCH_OK();
+    size_t scan_bytes = L.scan_bytes;
+    SPC_CUDA_OK(cub::DeviceScan::ExclusiveSum(ws + L.off_scan, scan_bytes, iprefix, iprefix, static_cast<int>(words), st));
+  }
   insert_inputs_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, tin, counters, bitmap);
   SPC_LAUNCH_OK();
   if (g.subm) {
@@ -1023,7 +1088,7 @@ int igemm_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, 
                cudaStream_t st) {
   using key_t = typename Table<K64>::key_t;
   const int kvp = (g.kv + 3) & ~3;
-  Table<K64> tin = table_at<K64>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
+  Table<K64> tin = tin_at<K64>(ws, L);
   Table<K64> tout = tout_at<K64>(ws, L);
   const key_t* sorted = reinterpret_cast<const key_t*>(ws + L.off_sorted);
   uint32_t* words = reinterpret_cast<uint32_t*>(ws + L.off_words);
@@ -1047,7 +1112,7 @@ template <int ND, bool K64>
 int native_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, int64_t n_out, char* ws,
                 int32_t* out_indices, int32_t* pair, int32_t* npl, cudaStream_t st) {
   using key_t = typename Table<K64>::key_t;
-  Table<K64> tin = table_at<K64>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
+  Table<K64> tin = tin_at<K64>(ws, L);
   Table<K64> tout = tout_at<K64>(ws, L);
   const Table<K64>& lookup = g.subm ? tin : tout;
   const key_t* sorted = reinterpret_cast<const key_t*>(ws + L.off_sorted);

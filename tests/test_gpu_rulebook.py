@@ -78,10 +78,18 @@ BIG = [
 ]
 
 
+@pytest.mark.parametrize("order", ["given", "ascending"])
 @pytest.mark.parametrize("case", range(len(BIG)))
-def test_igemm_and_native_match_oracle_on_larger_inputs(case):
+def test_igemm_and_native_match_oracle_on_larger_inputs(case, order):
+    """``ascending``: rows sorted by linear coordinate, as the outputs of an earlier layer are; the
+    library then numbers input rows through its bitmap instead of the hash table."""
     shape, batch, n, k, s, p, d, op, subm, tr = BIG[case]
     idx_np = unique_coords(500 + case, n, batch, shape)
+    if order == "ascending":
+        lin = np.zeros(idx_np.shape[0], np.int64)
+        for col, extent in enumerate([batch, *shape]):
+            lin = lin * extent + idx_np[:, col]
+        idx_np = np.ascontiguousarray(idx_np[np.argsort(lin)])
     idx = torch.from_numpy(idx_np).to(DEV)
     P = _pairs()
     kv = int(np.prod(k))
