@@ -225,10 +225,80 @@ wgrad_reduce_kernel(const float* __restrict__ partial, T* __restrict__ dw, long 
   dw[e] = from_acc<T, float>(s);
 }
 
+// Thin layers (the 4 -> 16 stem of a LiDAR backbone): a 64x64x16 tile would be three quarters
+// padding in two dimensions.  Here one thread owns one output row and all of its n_dim <= NP
+// outputs in registers; the whole weight tensor sits in shared memory as fp32 [kv][r_dim][NP] and
+// is read as broadcasts; the table column pairs[k, row] is read coalesced.  Same sums in the same
+// offset order as the tiled kernel (fp32 accumulation).
+constexpr int kThinThreads = 128;
+
+template <typename T, typename TO, int NP>
+__global__ void __launch_bounds__(kThinThreads)
+gather_gemm_thin_kernel(const T* __restrict__ src, const T* __restrict__ w, const Epilogue epi,
+                        const int32_t* __restrict__ pairs, TO* __restrict__ out, long long m_rows, int n_dim,
+                        int r_dim, int kv, long long s_wk, long long s_wr, long long s_wn) {
+  extern __shared__ float w_s[];  // [kv][r_dim][NP]
+  for (int i = threadIdx.x; i < kv * r_dim * NP; i += kThinThreads) {
+    const int n = i % NP, r = (i / NP) % r_dim, k = i / (NP * r_dim);
+    w_s[i] = n < n_dim ? to_float(w[n * s_wn + k * s_wk + r * s_wr]) : 0.f;
+  }
+  __syncthreads();
+  const long long row = static_cast<long long>(blockIdx.x) * kThinThreads + threadIdx.x;
+  if (row >= m_rows) return;
+  float acc[NP];
+#pragma unroll
+  for (int n = 0; n < NP; ++n) acc[n] = 0.f;
+  int j_next = __ldg(&pairs[row]);
+  for (int k = 0; k < kv; ++k) {
+    const int j = j_next;
+    if (k + 1 < kv) j_next = __ldg(&pairs[static_cast<long long>(k + 1) * m_rows + row]);
+    if (j < 0) continue;
+    const T* f = src + static_cast<long long>(j) * r_dim;
+    const float* wk = w_s + k * r_dim * NP;
+    for (int r = 0; r < r_dim; ++r) {
+      const float a = to_float(f[r]);
+      const float4* wr = reinterpret_cast<const float4*>(wk + r * NP);
+#pragma unroll
+      for (int q = 0; q < NP / 4; ++q) {
+        const float4 v = wr[q];
+        acc[4 * q + 0] += a * v.x;
+        acc[4 * q + 1] += a * v.y;
+        acc[4 * q + 2] += a * v.z;
+        acc[4 * q + 3] += a * v.w;
+      }
+    }
+  }
+  TO* o = out + row * n_dim;
+#pragma unroll
+  for (int n = 0; n < NP; ++n)
+    if (n < n_dim) o[n] = from_acc<TO>(apply_epilogue<T>(acc[n], epi, n));
+}
+
+template <typename T, typename TO>
+int launch_thin(const void* src, const void* w, const Epilogue& epi, const int32_t* pairs, void* out,
+                long long m_rows, int n_dim, int r_dim, int kv, long long s_wk, long long s_wr, long long s_wn,
+                cudaStream_t st) {
+  const int np = n_dim <= 8 ? 8 : n_dim <= 16 ? 16 : 32;
+  const size_t smem = static_cast<size_t>(kv) * r_dim * np * sizeof(float);
+  const unsigned blocks = static_cast<unsigned>(ceil_div(m_rows, kThinThreads));
+#define SPC_THIN(NP)                                                                                         \
+  gather_gemm_thin_kernel<T, TO, NP><<<blocks, kThinThreads, smem, st>>>(                                    \
+      static_cast<const T*>(src), static_cast<const T*>(w), epi, pairs, static_cast<TO*>(out), m_rows, n_dim, \
+      r_dim, kv, s_wk, s_wr, s_wn)
+  if (np == 8) SPC_THIN(8);
+  else if (np == 16) SPC_THIN(16);
+  else SPC_THIN(32);
+#undef SPC_THIN
+  SPC_LAUNCH_OK();
+  return SPC_OK;
+}
+
 template <typename T, typename TO>
 int launch_gather(const void* src, const void* w, const Epilogue& epi, const int32_t* pairs,
                   const int32_t* order, void* out, long long m_rows, int n_dim, int r_dim, int kv,
                   long long s_wk, long long s_wr, long long s_wn, cudaStream_t st) {
+  if (r_dim <= 8 && n_dim <= 32 && static_cast<size_t>(kv) * r_dim * 32 * sizeof(float) <= 40 * 1024 && m_rows > 0)
+    return launch_thin<T, TO>(src, w, epi, pairs, out, m_rows, n_dim, r_dim, kv, s_wk, s_wr, s_wn, st);
   dim3 grid(static_cast<unsigned>(ceil_div(m_rows, BM)), static_cast<unsigned>(ceil_div(n_dim, BN)));
   gather_gemm_simt_kernel<T, TO><<<grid, kGemmThreads, 0, st>>>(
       static_cast<const T*>(src), static_cast<const T*>(w), epi, pairs, order,

@@ -77,6 +77,11 @@ SHAPES = [
     (24, 40, torch.float32, False),
     (256, 256, torch.float16, True),
     (136, 130, torch.float16, True),
+    # thin layers (one thread per output row): odd widths, every dtype, strided
+    (3, 8, torch.float32, True),
+    (5, 20, torch.bfloat16, False),
+    (8, 32, torch.float16, False),
+    (1, 1, torch.float32, True),
 ]
 
 
