@@ -75,6 +75,9 @@ BIG = [
     ([20, 20, 20, 20], 2, 20000, [3, 3, 3, 3], [1, 1, 1, 1], [1, 1, 1, 1], [1, 1, 1, 1], [0, 0, 0, 0], True, False),
     ([512, 600], 3, 40000, [3, 3], [2, 2], [1, 1], [1, 1], [0, 0], False, False),
     ([5000], 4, 3000, [5], [3], [2], [1], [0], False, False),
+    # grids between 2^27.6 and 2^31 cells: too large for an input bitmap, 32-bit keys, hash table only
+    ([1000, 1000, 500], 2, 50000, [3, 3, 3], [1, 1, 1], [1, 1, 1], [1, 1, 1], [0, 0, 0], True, False),
+    ([1000, 1000, 500], 2, 50000, [3, 3, 3], [2, 2, 2], [1, 1, 1], [1, 1, 1], [0, 0, 0], False, False),
 ]
 
 
@@ -84,7 +87,12 @@ def test_igemm_and_native_match_oracle_on_larger_inputs(case, order):
     """``ascending``: rows sorted by linear coordinate, as the outputs of an earlier layer are; the
     library then numbers input rows through its bitmap instead of the hash table."""
     shape, batch, n, k, s, p, d, op, subm, tr = BIG[case]
-    idx_np = unique_coords(500 + case, n, batch, shape)
+    if int(np.prod(shape)) > 1 << 27:
+        # a dense cluster in the far corner of a huge grid: large keys, and neighbours that exist
+        idx_np = unique_coords(500 + case, n, batch, [40, 40, 40])
+        idx_np[:, 1:] += np.array(shape, np.int32) - 40
+    else:
+        idx_np = unique_coords(500 + case, n, batch, shape)
     if order == "ascending":
         lin = np.zeros(idx_np.shape[0], np.int64)
         for col, extent in enumerate([batch, *shape]):
