@@ -384,6 +384,57 @@ expand_bits_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict
   }
 }
 
+// Dense numbering, step 1: the bits of every output cell an input row reaches.  Per axis only the
+// kernel offsets that land on an output coordinate are kept (a bitmask over the offsets of that axis:
+// with stride 2 and a 3-wide kernel one or two of three), and the cells are the product of the axes,
+// so a k3 s2 layer visits at most 8 candidates per input instead of testing all 27.
+template <int D, int ND>
+__device__ __forceinline__ void mark_cells(const Geo& g, const int* c, const uint32_t* mask, long long lin,
+                                           uint32_t* __restrict__ bits) {
+  if constexpr (D == ND) {
+    uint32_t* word = bits + (lin >> 5);
+    const uint32_t bit = 1u << (lin & 31);
+    if (!(*word & bit)) atomicOr(word, bit);
+  } else {
+    for (uint32_t m = mask[D]; m != 0; m &= m - 1) {
+      const int k = __ffs(m) - 1;
+      const int o = g.transpose ? c[D + 1] * g.stride[D] + k * g.dil[D] - g.pad[D]
+                                : (c[D + 1] + g.pad[D] - k * g.dil[D]) / g.stride[D];
+      mark_cells<D + 1, ND>(g, c, mask, lin * g.out_shape[D] + o, bits);
+    }
+  }
+}
+
+template <int ND>
+__global__ void __launch_bounds__(kThreads)
+mark_outputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n,
+                    uint32_t* __restrict__ bits) {
+  const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
+  if (j >= n) return;
+  int c[ND + 1];
+  load_coord<ND>(idx, j, c);
+  uint32_t mask[ND];
+#pragma unroll
+  for (int d = 0; d < ND; ++d) {
+    uint32_t m = 0;
+    for (int k = 0; k < g.ksize[d]; ++k) {
+      int o;
+      if (g.transpose) {
+        o = c[d + 1] * g.stride[d] + k * g.dil[d] - g.pad[d];
+      } else {
+        const int num = c[d + 1] + g.pad[d] - k * g.dil[d];
+        if (num < 0) continue;
+        o = num / g.stride[d];
+        if (o * g.stride[d] != num) continue;
+      }
+      if (o >= 0 && o < g.out_shape[d]) m |= 1u << k;
+    }
+    if (m == 0) return;
+    mask[d] = m;
+  }
+  mark_cells<0, ND>(g, c, mask, c[0], bits);
+}
+
 template <int ND, bool K64>
 __global__ void __launch_bounds__(kThreads)
 enumerate_outputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n,
@@ -994,7 +1045,14 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
   Table<K64> tout = tout_at<K64>(ws, L);
   key_t* uniq = reinterpret_cast<key_t*>(ws + L.off_uniq);
   key_t* sorted = reinterpret_cast<key_t*>(ws + L.off_sorted);
-  enumerate_outputs_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, tout, uniq, counters);
+  bool axes_fit = true;  // mark_outputs_kernel keeps one bit per kernel offset of an axis
+  for (int d = 0; d < ND; ++d) axes_fit = axes_fit && g.ksize[d] <= 32;
+  if (dense_out && axes_fit) {
+    mark_outputs_kernel<ND><<<blocks_for(n_in), kThreads, 0, st>>>(
+        g, idx, n_in, reinterpret_cast<uint32_t*>(ws + L.off_obits));
+  } else {
+    enumerate_outputs_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, tout, uniq, counters);
+  }
   SPC_LAUNCH_OK();
   if (dense_out) {
     uint32_t* bits = reinterpret_cast<uint32_t*>(ws + L.off_obits);
