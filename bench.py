@@ -113,6 +113,122 @@ def make_scenes(rank, n_scenes=N_SCENES, batch=BATCH):
     return scenes
 
 
+UNET_GRID = [512, 512, 64]
+UNET_BATCH = 8
+UNET_N_RANGE = (100000, 200000)
+UNET_WIDTHS = (32, 64, 128, 256)
+
+
+def build_unet(c_in=4, widths=UNET_WIDTHS):
+    """BASELINE configs[3]: encoder of SubM / stride-2 convolutions at 32 / 64 / 128 / 256
+    channels, decoder of SparseInverseConv3d layers that reuse the encoder's
+    indice_keys, BatchNorm + ReLU after every convolution."""
+    import spconv_triton_b200.pytorch as sp
+
+    def block(conv, c):
+        return [conv, torch.nn.BatchNorm1d(c, eps=1e-3, momentum=0.01), torch.nn.ReLU()]
+
+    mods = block(sp.SubMConv3d(c_in, widths[0], 3, padding=1, bias=False, indice_key="subm0"), widths[0])
+    for lvl in range(1, len(widths)):
+        mods += block(sp.SparseConv3d(widths[lvl - 1], widths[lvl], 3, stride=2, padding=1, bias=False,
+                                      indice_key=f"down{lvl}"), widths[lvl])
+        mods += block(sp.SubMConv3d(widths[lvl], widths[lvl], 3, padding=1, bias=False, indice_key=f"subm{lvl}"),
+                      widths[lvl])
+    for lvl in range(len(widths) - 1, 0, -1):
+        mods += block(sp.SparseInverseConv3d(widths[lvl], widths[lvl - 1], 3, indice_key=f"down{lvl}", bias=False),
+                      widths[lvl - 1])
+        mods += block(sp.SubMConv3d(widths[lvl - 1], widths[lvl - 1], 3, padding=1, bias=False,
+                                    indice_key=f"subm{lvl - 1}"), widths[lvl - 1])
+    return sp.SparseSequential(*mods)
+
+
+def make_unet_scenes(n_scenes=2, batch=UNET_BATCH, n_range=UNET_N_RANGE, grid=UNET_GRID):
+    """Indoor-like surface scenes; the same on every rank (each rank then keeps its samples)."""
+    from spconv_triton_b200.scenes import indoor_like_batch
+
+    scenes = []
+    for s in range(n_scenes):
+        idx = indoor_like_batch(500 + s, batch, n_range, tuple(grid))
+        g = torch.Generator().manual_seed(900 + s)
+        scenes.append((torch.from_numpy(idx), torch.rand(idx.shape[0], 4, generator=g)))
+    return scenes
+
+
+def run_train_arm(dev, rank, world, steps, warmup):
+    """BASELINE configs[3]: one training step = forward + backward of the sparse
+    UNet under fp16 autocast, the data-parallel all-reduce of the parameter
+    gradients (bucketed, overlapped with backward) and an SGD update.  The batch
+    of 8 samples is sharded by sample over the ranks (strong scaling); returns
+    the record rank 0 adds to the JSON line."""
+    import torch.distributed as dist
+
+    import spconv_triton_b200.pytorch as sp
+    from spconv_triton_b200.parallel import GradientReducer, shard_by_sample
+
+    torch.manual_seed(1234)
+    net = build_unet().to(dev).train()
+    opt = torch.optim.SGD(net.parameters(), lr=1e-3, momentum=0.0)
+    n_params = sum(p.numel() for p in net.parameters())
+    scenes, voxels = [], []
+    for idx, feats in make_unet_scenes():
+        li, lf, lb = shard_by_sample(idx, feats, UNET_BATCH, rank, world)
+        scenes.append((li.to(dev), lf.to(dev), lb))
+        voxels.append(int(idx.shape[0]))
+
+    def step(i, reducer):
+        idx, feats, lb = scenes[i % len(scenes)]
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.float16):
+            out = net(sp.SparseConvTensor(feats, idx, UNET_GRID, lb))
+            loss = out.features.float().pow(2).mean() * 64.0
+        loss.backward()
+        if reducer is not None:
+            reducer.finish()
+        opt.step()
+        return loss
+
+    def timed(reducer):
+        for i in range(warmup):
+            step(i, reducer)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            loss = step(i, reducer)
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, float(loss)
+
+    reducer = GradientReducer(net.parameters(), bucket_bytes=4 << 20) if world > 1 else None
+    ms, loss = timed(reducer)
+    rec = {
+        "workload": "BASELINE configs[3]: sparse UNet 32/64/128/256 with SparseInverseConv3d decoder, fp16 autocast, "
+                    "forward + backward + gradient all-reduce + SGD step, grid [512,512,64], batch 8 over all ranks",
+        "scaling": "strong", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "voxels_per_step": int(np.mean(voxels)), "ms_per_step": ms / steps,
+        "mvoxels_per_s": sum(voxels[i % len(voxels)] for i in range(steps)) / (ms * 1e-3) / 1e6,
+        "parameters": n_params, "loss": loss,
+    }
+    if reducer is not None:
+        # the same steps without the exchange: the difference is what the all-reduce costs when overlapped
+        reducer.remove()
+        ms_local, _ = timed(None)
+        rec["allreduce"] = {"backend": "nccl", "buckets": len(reducer.buckets), "bytes_per_step": 4 * n_params,
+                            "launched_during_backward": bool(reducer.launched_during_backward),
+                            "ms_per_step_without": ms_local / steps,
+                            "exposed_ms_per_step": (ms - ms_local) / steps}
+    return rec
+
+
 class ClockSampler:
     """SM clock, power and throttle reasons of one GPU, sampled every 100 ms by
     an ``nvidia-smi`` child process (a separate process, so that the queries do
@@ -185,9 +301,21 @@ class ClockSampler:
         return out
 
 
-# DRAM bytes (read + write) of one forward gather-GEMM launch of this workload, averaged over the
-# launches of one ncu capture of this file (see profiles/).
-GEMM_DRAM_BYTES_PER_LAUNCH = 283.4e6
+def captured_gemm_traffic():
+    """DRAM bytes (read + write) per forward gather-GEMM launch of this workload,
+    from the committed summary of an ncu capture of this file, or None."""
+    f = ROOT / "profiles" / "gather_gemm_backbone_dram_traffic.txt"
+    if not f.exists():
+        return None, None
+    vals = {}
+    for line in f.read_text().splitlines():
+        if ":" in line and not line.lstrip().startswith("#"):
+            k, v = line.split(":", 1)
+            vals[k.strip()] = v.strip()
+    try:
+        return float(vals["dram_bytes_per_launch"]), vals.get("source")
+    except (KeyError, ValueError):
+        return None, None
 
 
 class GemmProfiler:
@@ -220,25 +348,67 @@ class GemmProfiler:
             if self.count_pairs:  # untimed warm-up pass: remember the pair count of this call slot
                 self.pairs[(self.scene, self.call)] = int((pair_fwd >= 0).sum().item())
             self.records.append((e0, e1, self.scene, self.call, tuple(pair_fwd.shape), features.shape[1],
-                                 w.shape[0], features.element_size(), out.element_size()))
+                                 w.shape[0], features.element_size(), out.element_size(), features.shape[0]))
             self.call += 1
             return out
 
         self.ops._gemm.conv_forward = wrapped
 
     def summarize(self):
-        """Aggregate over all recorded launches: algorithmic bytes = gathered
-        rows (pairs*C_in*e) + stored rows (n_out*C_out*e) + table (kv*n_out*4)
-        + weights (kv*C_in*C_out*e); FLOPs = 2*pairs*C_in*C_out."""
-        tot_ms = tot_bytes = tot_flops = 0.0
-        for e0, e1, scene, call, (kv, n_out), cin, cout, e_in, e_out in self.records:
+        """Aggregate over all recorded launches: FLOPs = 2*pairs*C_in*C_out;
+        gathered bytes = gathered rows (pairs*C_in*e) + stored rows
+        (n_out*C_out*e) + table (kv*n_out*4) + weights (kv*C_in*C_out*e);
+        compulsory bytes = the same with every input row counted once
+        (n_in*C_in*e), i.e. what has to cross the HBM interface when the
+        repeated gathers hit in L2."""
+        tot_ms = tot_bytes = tot_flops = tot_compulsory = 0.0
+        for e0, e1, scene, call, (kv, n_out), cin, cout, e_in, e_out, n_in in self.records:
             pairs = self.pairs[(scene, call)]
             tot_ms += e0.elapsed_time(e1)
             tot_bytes += pairs * cin * e_in + n_out * cout * e_out + kv * n_out * 4 + kv * cin * cout * e_in
+            # every input row once, however many outputs gather it
+            tot_compulsory += n_in * cin * e_in + n_out * cout * e_out + kv * n_out * 4 + kv * cin * cout * e_in
             tot_flops += 2.0 * pairs * cin * cout
         n = max(len(self.records), 1)
         return dict(launches=len(self.records), ms=tot_ms, bytes=tot_bytes, flops=tot_flops,
-                    avg_ms=tot_ms / n)
+                    compulsory=tot_compulsory, avg_ms=tot_ms / n)
+
+
+class RulebookProfiler:
+    """CUDA events around every rulebook generation (one per distinct indice_key
+    and forward) on the stream it is issued on; used with the run-ahead off."""
+
+    def __init__(self, keys):
+        from spconv_triton_b200.pytorch import ops
+
+        self.ops, self.keys = ops, keys
+        self.enabled = False
+        self.call = 0
+        self.records = []
+        self._orig = ops.get_indice_pairs_implicit_gemm
+
+    def install(self):
+        orig = self._orig
+
+        def wrapped(*a, **kw):
+            if not self.enabled:
+                return orig(*a, **kw)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            res = orig(*a, **kw)
+            e1.record()
+            self.records.append((self.keys[self.call % len(self.keys)], e0, e1))
+            self.call += 1
+            return res
+
+        self.ops.get_indice_pairs_implicit_gemm = wrapped
+
+    def summarize(self, steps):
+        per_key = {}
+        for key, e0, e1 in self.records:
+            per_key[key] = per_key.get(key, 0.0) + e0.elapsed_time(e1)
+        per_key = {k: v / steps for k, v in per_key.items()}
+        return per_key, sum(per_key.values())
 
 
 def measured_peaks():
@@ -287,6 +457,129 @@ def run_reference_arm(args):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def import_reference_gpu():
+    """The reference project's own package (its Triton kernels, JIT-compiled for
+    this GPU) from the git-ignored copy under baseline/_ref/, or None.  The
+    package reads its version from installed-distribution metadata, which a
+    plain copy does not have, so that one lookup is answered here."""
+    ref = ROOT / "baseline" / "_ref" / "reference"
+    if not (ref / "spconv_triton" / "__init__.py").is_file():
+        return None
+    import importlib
+    import importlib.metadata as md
+
+    orig = md.version
+    md.version = lambda name: "1.0.0" if name == "spconv-triton" else orig(name)
+    if str(ref) not in sys.path:
+        sys.path.insert(0, str(ref))
+    try:
+        return importlib.import_module("spconv_triton.pytorch")
+    finally:
+        md.version = orig
+
+
+def published_shape_scene(seed=42, n=50000):
+    """The shape the reference's README quotes its timings on: one sample of ~50k
+    voxels in a [41, 1600, 1408] grid (plane + clusters generator)."""
+    from spconv_triton_b200.scenes import lidar_like_batch
+
+    return torch.from_numpy(lidar_like_batch(seed, 1, (n, n), tuple(GRID)))
+
+
+def run_published(sp, tag, dev, iters, constants_mod):
+    """One layer, forward only, C_in = C_out = 256, k = 3, batch 1, ~50k voxels:
+    SubMConv3d with its rulebook cached, SparseConv3d s2 and SparseConvTranspose3d
+    s2 with the rulebook rebuilt every pass; fp16, TF32 and fp32.  ``sp`` is the
+    ``...pytorch`` module of the implementation under test (same API for both)."""
+    idx = published_shape_scene().to(dev)
+    n = int(idx.shape[0])
+
+    def timed(fn):
+        for _ in range(max(10, iters // 5)):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / iters)
+        return statistics.median(ts)
+
+    for prec in ("fp16", "tf32", "fp32"):
+        dtype = torch.float16 if prec == "fp16" else torch.float32
+        constants_mod.SPCONV_ALLOW_TF32 = prec == "tf32"
+        torch.manual_seed(0)
+        feats = torch.randn(n, 256, device=dev).to(dtype)
+        layers = {
+            "subm_cached": sp.SubMConv3d(256, 256, 3, padding=1, bias=False, indice_key="k"),
+            "sparse_s2": sp.SparseConv3d(256, 256, 3, stride=2, padding=1, bias=False),
+            "transpose_s2": sp.SparseConvTranspose3d(256, 256, 3, stride=2, padding=1, bias=False),
+        }
+        for name, layer in layers.items():
+            layer = layer.to(dev).to(dtype).eval()
+            x = sp.SparseConvTensor(feats, idx, GRID, 1)
+            with torch.no_grad():
+                out = layer(x)
+                if name == "subm_cached":
+                    x.indice_dict["k"] = out.indice_dict["k"]  # later passes reuse the rulebook
+                ms = timed(lambda: layer(x))
+            print(json.dumps({"op": f"published_{name}_{prec}", "impl": tag, "ms": ms, "voxels": n,
+                              "n_out": int(out.features.shape[0]), "channels": 256}), flush=True)
+    constants_mod.SPCONV_ALLOW_TF32 = False
+
+
+def run_backbone_reference_gpu(dev, steps, warmup):
+    """The reference's own modules and Triton kernels on this GPU over the
+    headline workload (same network, weights, scenes and timing as the device-
+    resident arm of the headline line)."""
+    sp_ref = import_reference_gpu()
+    if sp_ref is None:
+        print(json.dumps({"op": "backbone_reference_gpu", "unavailable": "no copy of the reference under baseline/_ref"}))
+        return
+    ours = init_backbone(build_backbone())
+    mods = []
+    for L in LAYERS:
+        if L["kind"] == "subm":
+            mods.append(sp_ref.SubMConv3d(L["cin"], L["cout"], L["k"], padding=L["p"], bias=False, indice_key=L["key"]))
+        else:
+            mods.append(sp_ref.SparseConv3d(L["cin"], L["cout"], L["k"], stride=L["s"], padding=L["p"], bias=False,
+                                            indice_key=L["key"]))
+        mods.append(torch.nn.BatchNorm1d(L["cout"], eps=1e-3, momentum=0.01))
+        mods.append(torch.nn.ReLU())
+    net = sp_ref.SparseSequential(*mods)
+    net.load_state_dict(ours.state_dict())
+    net = net.half().eval().to(dev)
+    scenes = [(i.to(dev), f.to(dev)) for i, f in make_scenes(0)]
+    voxels = [int(i.shape[0]) for i, _ in scenes]
+
+    def forward(s):
+        idx, feats = scenes[s % len(scenes)]
+        with torch.no_grad():
+            return net(sp_ref.SparseConvTensor(feats, idx, GRID, BATCH))
+
+    t0 = time.perf_counter()
+    for w in range(max(warmup, 2 * len(scenes))):  # JIT compilation and autotuning happen here
+        forward(w)
+    torch.cuda.synchronize()
+    warm_s = time.perf_counter() - t0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(steps):
+        forward(s)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    total = sum(voxels[s % len(voxels)] for s in range(steps))
+    print(json.dumps({"op": "backbone_reference_gpu", "impl": "reference (Triton kernels on this GPU)",
+                      "metric": "voxelnet_backbone_fwd_mvoxels_per_s", "value": total / (ms * 1e-3) / 1e6,
+                      "unit": "Mvoxels/s", "ms_per_step": ms / steps, "steps": steps,
+                      "warmup_and_compile_s": warm_s}), flush=True)
 
 
 def blob_scene(seed, batch, n_per_sample, grid=256):
@@ -345,6 +638,49 @@ def run_op_bench(args):
         print(json.dumps(line), flush=True)
 
     iters = max(args.steps, 5)
+    if args.op == "published":
+        import spconv_triton_b200.pytorch as sp
+        from spconv_triton_b200 import constants
+
+        run_published(sp, "spconv_triton_b200", dev, max(args.steps, 50), constants)
+        return
+    if args.op == "published_reference":
+        sp_ref = import_reference_gpu()
+        if sp_ref is None:
+            print(json.dumps({"op": "published_reference", "unavailable": "no copy of the reference under baseline/_ref"}))
+            return
+        import spconv_triton.constants as ref_constants
+
+        run_published(sp_ref, "reference (Triton kernels on this GPU)", dev, max(args.steps, 50), ref_constants)
+        return
+    if args.op == "backbone_reference_gpu":
+        run_backbone_reference_gpu(dev, max(args.steps, 5), args.warmup)
+        return
+    if args.op == "conv_k5":
+        # BASELINE configs[4]: SubMConv3d k5 256 -> 256 fp16 (kv 125, Native rulebook) on 4 x 400k blob voxels
+        batch, c, n_per = 4, 256, args.k5_voxels
+        idx = blob_scene(7, batch, n_per).to(dev)
+        n = int(idx.shape[0])
+        t0 = time.perf_counter()
+        _, pair, npl = P.native_pairs(idx, batch, [256] * 3, [5] * 3, [1] * 3, [2] * 3, [1] * 3, [0] * 3, True, False)
+        pf, pb = P.native_pair_to_tables(pair, npl, n, n, False)
+        torch.cuda.synchronize()
+        rb_ms = 1e3 * (time.perf_counter() - t0)
+        del pair
+        kv = int(pf.shape[0])
+        pairs = int((pf >= 0).sum())
+        x = torch.randn(n, c, device=dev).half()
+        w = (torch.randn(c, kv, c, device=dev) * 0.01).half()
+        g = torch.randn(n, c, device=dev).half()
+        flops = 2.0 * pairs * c * c
+        compulsory = 2 * n * c * 2 + kv * n * 4 + kv * c * c * 2
+        it = max(3, min(iters, 10))
+        emit("subm_k5_fwd_256_256", timed(lambda: G.conv_forward(x, w, pf, n), it), compulsory, flops, voxels=n,
+             pairs=pairs, kv=kv, rulebook_first_call_ms=rb_ms)
+        emit("subm_k5_dgrad_256_256", timed(lambda: G.conv_backward_input(g, w, pb, n), it), compulsory, flops)
+        emit("subm_k5_wgrad_256_256", timed(lambda: G.conv_backward_weight(x, g, pf, (c, kv, c)), it),
+             2 * n * c * 2 + kv * n * 4 + kv * c * c * 2, flops)
+        return
     if args.op == "pool":
         batch, c = 4, 256
         idx = blob_scene(7, batch, 400000)
@@ -536,8 +872,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-baseline-seconds", type=float, default=20.0)
-    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm", "voxelize", "dense", "sparse_add", "global_pool", "from_dense"],
+    ap.add_argument("--op", default=None, choices=["pool", "conv_s2", "conv_subm", "conv_k5", "published", "published_reference",
+                             "backbone_reference_gpu", "voxelize", "dense", "sparse_add", "global_pool", "from_dense"],
                     help="single-operator timings at the other configurations instead of the headline benchmark")
+    ap.add_argument("--k5-voxels", type=int, default=400000, help="--op conv_k5: voxels per sample (4 samples)")
+    ap.add_argument("--no-train", action="store_true",
+                    help="skip the training-step record (BASELINE configs[3]) that follows the headline measurement")
     ap.add_argument("--voxel-order", default="random", choices=["random", "sorted"],
                     help="--op pool: input voxel order (random = as a voxeliser emits them, sorted = as a previous layer's rulebook emits them)")
     args = ap.parse_args()
@@ -572,6 +912,12 @@ def main():
     voxels_per_scene = [int(i.shape[0]) for i, _ in scenes_host]
     prof = GemmProfiler()
     prof.install()
+    generating = []
+    for L in LAYERS:
+        if L["key"] not in generating:
+            generating.append(L["key"])
+    rb_prof = RulebookProfiler(generating)
+    rb_prof.install()
 
     def forward(idx, feats, scene=0):
         prof.scene, prof.call = scene, 0
@@ -601,79 +947,50 @@ def main():
     prof.enabled = prof.count_pairs = True
     for s in range(N_SCENES):  # untimed: algorithmic pair counts of every (scene, layer)
         out = forward(*scenes_dev[s], scene=s)
-    prof.count_pairs = False
+    prof.enabled = prof.count_pairs = False
     # warm-up with the timed loop's own allocation pattern (each step's output is
     # released before the next step starts), over every scene, so that the caching
     # allocator makes no cudaMalloc inside the timed region
     for w in range(max(args.warmup, 3 * N_SCENES)):
         out = None
         out = forward(*scenes_dev[w % N_SCENES], scene=w % N_SCENES)
-    prof.records.clear()
     barrier()
     launches0 = lib.spc_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     clocks.open_window()
     e0.record()
-    dbg = []
     for s in range(args.steps):
-        t_a = time.perf_counter()
         out = None
         out = forward(*scenes_dev[s % N_SCENES], scene=s % N_SCENES)
-        if os.environ.get("BENCH_DEBUG"):
-            st = torch.cuda.memory_stats()
-            dbg.append((round(1e3 * (time.perf_counter() - t_a), 2), st["num_device_alloc"], st["num_device_free"],
-                        st["reserved_bytes.all.current"] >> 20))
     e1.record()
     barrier()
-    if dbg:
-        print("step (host ms, cudaMallocs, cudaFrees, reserved MB):", dbg, file=sys.stderr)
-    prof.enabled = False
     launches = lib.spc_launch_count() - launches0
     dev_ms = max_over_ranks(e0.elapsed_time(e1))
     voxels = sum(voxels_per_scene[s % N_SCENES] for s in range(args.steps))
     total_voxels = sum_over_ranks(voxels)
     value = total_voxels / (dev_ms * 1e-3) / 1e6
-    gemm_overlapped = prof.summarize()
 
-    # ---- the dominant kernel alone: the same steps once more with the rulebook run-ahead off,
-    # so that no rulebook kernel shares the SMs with the GEMM launches the events bracket ------
-    from spconv_triton_b200 import constants as spc_constants
-
-    runahead = spc_constants.SPCONV_RULEBOOK_RUNAHEAD
-    spc_constants.SPCONV_RULEBOOK_RUNAHEAD = False
-    prof.records.clear()
-    for w in range(N_SCENES):
-        out = None
-        out = forward(*scenes_dev[w % N_SCENES], scene=w % N_SCENES)
-    prof.records.clear()
-    prof.enabled = True
-    torch.cuda.synchronize()
-    ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ea.record()
-    for s in range(args.steps):
-        out = None
-        out = forward(*scenes_dev[s % N_SCENES], scene=s % N_SCENES)
-    eb.record()
-    torch.cuda.synchronize()
-    prof.enabled = False
-    gemm = prof.summarize()
-    serial_ms = ea.elapsed_time(eb)
-    spc_constants.SPCONV_RULEBOOK_RUNAHEAD = runahead
-
-    # ---- end-to-end arm: pinned host buffers in, checksum out ----------------------------
+    # ---- end-to-end arm: pinned host buffers in, the output tensor (features + indices) out ----
     h2d = int(np.mean([i.numel() * 4 + f.numel() * 2 for i, f in scenes_host]))
-    host_result = torch.empty(64, dtype=torch.float32).pin_memory()
+    max_rows = int(out.features.shape[0] * 1.5) + 1024
+    host_feats = torch.empty((max_rows, out.features.shape[1]), dtype=out.features.dtype).pin_memory()
+    host_inds = torch.empty((max_rows, 4), dtype=torch.int32).pin_memory()
+    d2h_bytes = []
 
     def e2e_step(s):
         idx_h, feats_h = scenes_host[s % N_SCENES]
         idx = idx_h.to(dev, non_blocking=True)
         feats = feats_h.to(dev, non_blocking=True)
         o = forward(idx, feats)
-        host_result.copy_(o.features.float().sum(0), non_blocking=True)  # per-channel checksum of the output
+        n = o.features.shape[0]
+        host_feats[:n].copy_(o.features, non_blocking=True)
+        host_inds[:n].copy_(o.indices, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller consumes the result on the host
+        d2h_bytes.append(n * (o.features.shape[1] * o.features.element_size() + 16))
 
     for w in range(args.warmup):
         e2e_step(w)
+    d2h_bytes.clear()
     barrier()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
@@ -686,10 +1003,43 @@ def main():
     e2e_ms = max_over_ranks(e2.elapsed_time(e3))
     e2e_value = total_voxels / (e2e_ms * 1e-3) / 1e6
 
+    # ---- the kernels alone: the same steps once more with the rulebook run-ahead off, so that no
+    # rulebook kernel shares the SMs with the GEMM launches (and no GEMM with the rulebooks) that
+    # the events bracket -------------------------------------------------------------------------
+    from spconv_triton_b200 import constants as spc_constants
+
+    runahead = spc_constants.SPCONV_RULEBOOK_RUNAHEAD
+    spc_constants.SPCONV_RULEBOOK_RUNAHEAD = False
+    for w in range(N_SCENES):
+        out = None
+        out = forward(*scenes_dev[w % N_SCENES], scene=w % N_SCENES)
+    prof.records.clear()
+    prof.enabled = rb_prof.enabled = True
+    torch.cuda.synchronize()
+    ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ea.record()
+    for s in range(args.steps):
+        out = None
+        out = forward(*scenes_dev[s % N_SCENES], scene=s % N_SCENES)
+    eb.record()
+    torch.cuda.synchronize()
+    prof.enabled = rb_prof.enabled = False
+    gemm = prof.summarize()
+    rulebook_ms, rulebook_total_ms = rb_prof.summarize(args.steps)
+    serial_ms = ea.elapsed_time(eb)
+    spc_constants.SPCONV_RULEBOOK_RUNAHEAD = runahead
+
     # ---- footprint: shows the per-step working set exceeds L2 ------------------------------
     idict = out.indice_dict
     table_bytes = sum(d.pair_fwd.numel() * 4 + (d.pair_bwd.numel() * 4 if d.pair_bwd is not None else 0)
                       for d in idict.values())
+    out = None
+
+    # ---- BASELINE configs[3]: the training step with the gradient all-reduce ---------------
+    train = None
+    if not args.no_train:
+        torch.cuda.empty_cache()
+        train = run_train_arm(dev, rank, world, steps=max(3, min(args.steps, 10)), warmup=3)
 
     if rank != 0:
         clocks.summary()
@@ -698,8 +1048,10 @@ def main():
         return
 
     hbm_peak, tensor_peak, peak_kind = measured_peaks()
-    achieved_gbs = gemm["bytes"] / (gemm["ms"] * 1e-3) / 1e9 if gemm["ms"] else 0.0
     achieved_tflops = gemm["flops"] / (gemm["ms"] * 1e-3) / 1e12 if gemm["ms"] else 0.0
+    compulsory_gbs = gemm["compulsory"] / (gemm["ms"] * 1e-3) / 1e9 if gemm["ms"] else 0.0
+    gathered_gbs = gemm["bytes"] / (gemm["ms"] * 1e-3) / 1e9 if gemm["ms"] else 0.0
+    traffic, traffic_source = captured_gemm_traffic()
 
     cpu_baseline = None
     if world == 1:
@@ -718,29 +1070,38 @@ def main():
             "parallelism": f"replicas x{world} (sharded by sample, no collective)",
         },
         "e2e": {"value": e2e_value, "unit": "Mvoxels/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": host_result.numel() * 4, "ms_per_step": e2e_ms / args.steps},
+                "d2h_bytes_per_step": int(np.mean(d2h_bytes)), "ms_per_step": e2e_ms / args.steps,
+                "result": "output features and indices copied to pinned host memory every step"},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
+        "rulebook_ms": {"per_indice_key": rulebook_ms, "per_step": rulebook_total_ms,
+                        "timing": "CUDA events around each rulebook generation, run-ahead off (host read of the "
+                                  "output count included)"},
         "roofline": {
             "kernel": "gather-GEMM forward (every launch of the timed steps, aggregated)",
             "timing": "CUDA events around each launch on its stream, in a repeat of the timed steps with the "
-                      "rulebook run-ahead off so the kernel runs alone; overlapped_* are the same events inside "
-                      "the timed region, where rulebook kernels of the next layer share the SMs",
-            "bound": "hbm", "achieved": achieved_gbs, "peak": hbm_peak, "unit": "GB/s",
-            "frac": achieved_gbs / hbm_peak if hbm_peak else None, "traffic": GEMM_DRAM_BYTES_PER_LAUNCH,
-            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, average of the 68 gather-GEMM "
-                              "launches captured on this workload (profiles/voxelnet_backbone_launch_list.md)",
-            "algorithmic_bytes_per_launch": gemm["bytes"] / gemm["launches"] if gemm["launches"] else None,
-            "peak_kind": peak_kind,
+                      "rulebook run-ahead off so that the kernel runs alone",
+            "bound": "tensor", "achieved": achieved_tflops, "peak": tensor_peak, "unit": "TFLOP/s",
+            "frac": achieved_tflops / tensor_peak if tensor_peak else None,
+            "traffic": traffic, "traffic_source": traffic_source,
+            "flops_per_launch": gemm["flops"] / gemm["launches"] if gemm["launches"] else None,
+            "peak_kind": peak_kind + " (bf16 cuBLAS burst)",
             "launches": gemm["launches"], "avg_launch_ms": gemm["avg_ms"],
             "share_of_step": gemm["ms"] / serial_ms if serial_ms else None,
             "serial_ms_per_step": serial_ms / args.steps,
-            "overlapped_avg_launch_ms": gemm_overlapped["avg_ms"],
             "rulebook_runahead": bool(runahead),
-            "tflops": achieved_tflops, "tensor_frac": achieved_tflops / tensor_peak if tensor_peak else None,
+            "hbm": {"peak": hbm_peak, "unit": "GB/s",
+                    "compulsory_bytes_per_launch": gemm["compulsory"] / gemm["launches"] if gemm["launches"] else None,
+                    "compulsory_GBps": compulsory_gbs, "compulsory_frac": compulsory_gbs / hbm_peak if hbm_peak else None,
+                    "gathered_bytes_per_launch": gemm["bytes"] / gemm["launches"] if gemm["launches"] else None,
+                    "gathered_GBps": gathered_gbs,
+                    "note": "gathered = every (pair, row) read counted, mostly L2 hits; compulsory = every input "
+                            "row once + table + stored rows + weights"},
         },
         "cpu_baseline": cpu_baseline,
     }
+    if train is not None:
+        line["train"] = train
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -50,9 +50,9 @@ typedef enum { SPC_F16 = 0, SPC_BF16 = 1, SPC_F32 = 2, SPC_F64 = 3 } spc_dtype;
 typedef enum { SPC_PREC_IEEE = 0, SPC_PREC_TF32 = 1 } spc_precision;
 
 /* Which implementation a GEMM entry point may use.  AUTO picks a tcgen05
- * kernel whenever the shape allows it (fed by TMA gather4 when the channel
- * widths fit a swizzle span, by cp.async otherwise) and the CUDA-core kernel
- * for the rest.  SIMT forces the CUDA-core kernels; TCGEN05 demands a
+ * kernel whenever the shape allows it (gathered rows copied with cp.async;
+ * weight slabs loaded by tiled TMA when the channel widths fit a swizzle span,
+ * by cp.async otherwise) and the CUDA-core kernel for the rest.  SIMT forces the CUDA-core kernels; TCGEN05 demands a
  * tensor-core kernel (SPC_ERR_UNSUPPORTED if the shape does not fit);
  * TCGEN05_CPASYNC behaves like AUTO but never uses the TMA-fed kernel. */
 typedef enum {
@@ -97,6 +97,15 @@ long long spc_launch_count(void);
  * the flag is cleared.  No counterpart in the reference (its kernels have no
  * device-side waits). */
 int spc_check_device_status(void* stream);
+/* Queues, on `stream`, a copy of the current device's status word into
+ * `pinned_host_word` (page-locked host memory owned by the caller) and returns
+ * without waiting.  The word is non-zero when a kernel gave up on a bounded wait
+ * (SPC_ERR_DEVICE_WAIT_EXPIRED) or a rulebook kernel met an index row outside
+ * batch_size / spatial_shape (SPC_ERR_INVALID_ARGUMENT).  The host reads the
+ * mailbox after work it synchronises on anyway, e.g. at the start of the next
+ * forward pass, and then calls spc_check_device_status to clear the word.  No
+ * counterpart in the reference (its errors are all raised before launch). */
+int spc_post_device_status(int* pinned_host_word, void* stream);
 
 /* ---- output-shape formulas --------------------------------------------- */
 
@@ -346,10 +355,15 @@ int spc_conv_backward_weight(const void* features, const void* grad_out,
                              void* stream);
 
 /* Weight gradient for callers that cannot provide a workspace and must not
- * allocate: same result as spc_conv_backward_weight, but the fp32 partial sums
+ * allocate: the same sum as spc_conv_backward_weight, but the fp32 partial sums
  * of the split reduction live in a 16 MiB array built into the library (held
  * by every GPU that loads it, until the process exits).  It has no counterpart
  * in the reference.
+ *   - it always runs the CUDA-core kernel, so its result is bit-identical to
+ *     spc_conv_backward_weight called with path = SPC_GEMM_SIMT, and equal only
+ *     within rounding to the default path, which uses the tensor cores (another
+ *     split and summation order) for 16-bit shapes; for those shapes it is also
+ *     roughly ten times slower than the default path;
  *   - shapes whose partial sums exceed spc_conv_backward_weight_noalloc_max_bytes()
  *     are rejected with SPC_ERR_SIZE_LIMIT (compare with
  *     spc_conv_backward_weight_workspace_bytes() for the same arguments);

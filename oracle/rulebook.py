@@ -47,6 +47,19 @@ def deconv_output_size(input_size, kernel_size, stride, padding, dilation, outpu
     return out
 
 
+def rows_in_grid(indices, batch_size, spatial_shape):
+    """Boolean [N]: rows whose batch index lies in [0, batch_size) and whose
+    coordinates lie inside ``spatial_shape``.  The reference linearises whatever
+    it is given (spconv_triton/pytorch/_impl/pairs.py:91-95); the CUDA path
+    rejects the rows for which this is False, because their linear coordinate
+    would index outside its occupancy bitmaps."""
+    idx = np.asarray(indices)
+    ok = (idx[:, 0] >= 0) & (idx[:, 0] < int(batch_size))
+    for d, extent in enumerate(spatial_shape):
+        ok &= (idx[:, d + 1] >= 0) & (idx[:, d + 1] < int(extent))
+    return ok
+
+
 def kernel_offsets(ksize):
     """[kv, ndim] offsets, row-major with the last dimension fastest (pairs.py:43-48)."""
     grids = np.meshgrid(*[np.arange(k, dtype=np.int64) for k in ksize], indexing="ij")

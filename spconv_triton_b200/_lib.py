@@ -17,6 +17,8 @@ SPC_F16, SPC_BF16, SPC_F32, SPC_F64 = 0, 1, 2, 3
 SPC_PREC_IEEE, SPC_PREC_TF32 = 0, 1
 SPC_ACT_NONE, SPC_ACT_RELU, SPC_ACT_SIGMOID, SPC_ACT_LEAKY_RELU = 0, 1, 2, 3
 SPC_GEMM_AUTO, SPC_GEMM_SIMT, SPC_GEMM_TCGEN05, SPC_GEMM_TCGEN05_CPASYNC = 0, 1, 2, 3
+(SPC_OK, SPC_ERR_INVALID_ARGUMENT, SPC_ERR_CUDA, SPC_ERR_WORKSPACE_TOO_SMALL, SPC_ERR_HASH_TABLE_FULL,
+ SPC_ERR_UNSUPPORTED, SPC_ERR_DEVICE_WAIT_EXPIRED, SPC_ERR_SIZE_LIMIT) = range(8)
 
 _I4 = c_int32 * SPC_MAX_NDIM
 
@@ -64,6 +66,7 @@ _PROTOTYPES = {
     "spc_last_error": (c_char_p, []),
     "spc_launch_count": (ctypes.c_longlong, []),
     "spc_check_device_status": (c_int, [_P]),
+    "spc_post_device_status": (c_int, [_P, _P]),
     "spc_conv_output_size": (c_int, [c_int, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32),
                                      POINTER(c_int32), POINTER(c_int32), POINTER(c_int32)]),
     "spc_deconv_output_size": (c_int, [c_int, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32),
@@ -155,6 +158,61 @@ def check(status):
     if status != 0:
         msg = load().spc_last_error()
         raise SpconvB200Error(status, msg.decode() if msg else "")
+
+
+# ---- device status mailbox -------------------------------------------------------------------
+# Kernels of the library record failures they cannot raise themselves (a bounded wait that
+# expired, an index row outside the grid met by a submanifold rulebook, which has no host read)
+# in a per-device status word.  A forward pass ends by queueing a copy of that word into a
+# page-locked host word (no wait); the next forward pass on that device starts by looking at
+# the host word and raises if it is set.
+_mailboxes: dict = {}
+
+
+def status_mailbox(index: int):
+    """(torch tensor [1] int32, numpy view) shared with the device through spc_post_device_status."""
+    import torch
+
+    box = _mailboxes.get(index)
+    if box is None:
+        t = torch.zeros(1, dtype=torch.int32)
+        if torch.cuda.is_available():
+            t = t.pin_memory()
+        box = (t, t.numpy())
+        _mailboxes[index] = box
+    return box
+
+
+def post_device_status(device) -> None:
+    """Queue the copy of ``device``'s status word into its mailbox on the current stream."""
+    import torch
+
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    t, _ = status_mailbox(index)
+    with torch.cuda.device(index):
+        check(load().spc_post_device_status(c_void_p(t.data_ptr()), current_stream(device)))
+
+
+def raise_posted_status(device=None) -> None:
+    """Raise SpconvB200Error if a status posted by an earlier pass has arrived (never waits)."""
+    import torch
+
+    if device is None or device.index is None:
+        index = torch.cuda.current_device() if torch.cuda.is_available() else 0
+    else:
+        index = device.index
+    box = _mailboxes.get(index)
+    if box is None or box[1][0] == 0:
+        return
+    code = int(box[1][0])
+    box[1][0] = 0
+    if torch.cuda.is_available():
+        with torch.cuda.device(index):
+            load().spc_check_device_status(current_stream(torch.device("cuda", index)))  # clears the word
+    text = ("an index row outside batch_size / spatial_shape was met by a rulebook kernel (the row got no pairs)"
+            if code == SPC_ERR_INVALID_ARGUMENT else
+            "a bounded device-side wait expired in a kernel of an earlier pass: its output is incomplete")
+    raise SpconvB200Error(code, text + "; reported by an earlier forward pass on this device")
 
 
 def ptr(t):

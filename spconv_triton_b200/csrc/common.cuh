@@ -46,15 +46,37 @@ inline int fail(int status, const char* fmt, ...) {
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+constexpr int kMaxDevices = 64;
+
+// Ordinal of the current device, or -1 when it is outside the per-device tables below.
+inline int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
+// Multiprocessor count of the CURRENT device (remembered per device ordinal).
 inline int sm_count() {
-  static int cached = 0;
-  if (cached == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
-    if (cached <= 0) cached = 148;
+  static int cached[kMaxDevices] = {0};
+  const int dev = current_device_slot();
+  if (dev < 0) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = n > 0 ? n : 148;
   }
-  return cached;
+  return cached[dev];
+}
+
+// The dynamic shared memory opt-in of a kernel is a per-device attribute: `done` (one flag per
+// device ordinal, owned by the launcher of that kernel) remembers where it has been set.
+template <typename Kernel>
+inline cudaError_t ensure_dynamic_smem(Kernel kernel, int bytes, bool (&done)[kMaxDevices]) {
+  const int dev = current_device_slot();
+  if (dev >= 0 && done[dev]) return cudaSuccess;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && dev >= 0) done[dev] = true;
+  return e;
 }
 
 // What happens to an accumulator row before it is stored:

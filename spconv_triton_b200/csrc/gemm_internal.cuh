@@ -46,8 +46,8 @@ int wgrad_tc(const void* feats, const void* gout, const int32_t* pair_fwd, float
 
 int* device_status_ptr();
 
-// TMA-fed variant of the tcgen05 kernel (gemm_tma.cu): feature rows arrive by
-// cp.async.bulk.tensor tile::gather4, weight slabs by tiled TMA loads.
+// Variant of the tcgen05 kernel (gemm_tma.cu) whose weight slabs arrive by tiled TMA loads;
+// the gathered feature rows are copied with cp.async.
 bool gather_gemm_tma_supported(int n_dim, int r_dim, int kv, int dtype, int out_dtype, int precision,
                                bool transposed_weight);
 int gather_gemm_tma(const void* src, const void* w, const Epilogue& epi, const int32_t* pairs,

@@ -13,6 +13,7 @@
 // reference's tile-bitmask trick (gemm.py:282-296) without needing the mask
 // words, so it also works for kernel volumes above 32.
 #include <algorithm>
+#include <atomic>
 
 #include "common.cuh"
 #include "gemm_internal.cuh"
@@ -328,7 +329,7 @@ int gather_gemm_simt(const void* src, const void* w, const Epilogue& epi, const 
 WgradSplit wgrad_split(int64_t n_out, int c_in, int c_out, int kv) {
   WgradSplit s;
   const int64_t tiles = static_cast<int64_t>(kv) * ceil_div(c_in, BN) * ceil_div(c_out, BM);
-  int64_t want = ceil_div(2 * 148, std::max<int64_t>(tiles, 1));
+  int64_t want = ceil_div(2 * static_cast<int64_t>(sm_count()), std::max<int64_t>(tiles, 1));
   const int64_t by_len = std::max<int64_t>(1, n_out / 2048);
   want = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(want, by_len), 64));
   s.splits = static_cast<int>(want);
@@ -400,18 +401,22 @@ static __device__ __align__(256) float g_wgrad_scratch[kNoAllocScratchFloats];
 
 // In host code `g_wgrad_scratch` is only a handle for the symbol, not an
 // address a kernel could use; the device address is looked up once per device
-// (with that device current) and remembered.
+// (with that device current) and remembered.  Two host threads that make the
+// first call on a device at the same time both look the address up and store
+// the same value (atomic pointer-sized stores), so no lock is taken.
 int wgrad_scratch_address(float** out) {
-  static float* per_device[64] = {nullptr};
+  static std::atomic<float*> per_device[64];
   int dev = 0;
   SPC_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(SPC_ERR_SIZE_LIMIT, "device ordinal %d out of range", dev);
-  if (per_device[dev] == nullptr) {
+  float* addr = per_device[dev].load(std::memory_order_acquire);
+  if (addr == nullptr) {
     void* raw = nullptr;
     SPC_CUDA_OK(cudaGetSymbolAddress(&raw, g_wgrad_scratch));
-    per_device[dev] = static_cast<float*>(raw);
+    addr = static_cast<float*>(raw);
+    per_device[dev].store(addr, std::memory_order_release);
   }
-  *out = per_device[dev];
+  *out = addr;
   return SPC_OK;
 }
 

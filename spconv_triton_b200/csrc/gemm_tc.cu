@@ -336,12 +336,8 @@ int launch_tc(const TcParams& base, cudaStream_t st) {
   p.stages = pl.stages;
   p.b_stage_bytes = pl.b_stage_bytes;
   p.tmem_cols = pl.tmem_cols;
-  static bool configured = false;  // per instantiation
-  if (!configured) {
-    SPC_CUDA_OK(cudaFuncSetAttribute(gather_gemm_tc_kernel<T, TO, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     200 * 1024));
-    configured = true;
-  }
+  static bool configured[kMaxDevices] = {false};  // per instantiation and device
+  SPC_CUDA_OK(ensure_dynamic_smem(gather_gemm_tc_kernel<T, TO, B_MN>, 200 * 1024, configured));
   const unsigned grid = static_cast<unsigned>(ceil_div(p.m_rows, kTileM));
   gather_gemm_tc_kernel<T, TO, B_MN><<<grid, kThreadsTc, pl.smem_bytes, st>>>(p);
   SPC_LAUNCH_OK();
@@ -415,10 +411,21 @@ int read_device_status(cudaStream_t st, int* host_value) {
 
 }  // namespace spc
 
+extern "C" int spc_post_device_status(int* pinned_host_word, void* stream) {
+  if (pinned_host_word == nullptr) return spc::fail(SPC_ERR_INVALID_ARGUMENT, "post_device_status: null mailbox");
+  int* ptr = spc::device_status_ptr();
+  if (ptr == nullptr) return SPC_OK;
+  SPC_CUDA_OK(cudaMemcpyAsync(pinned_host_word, ptr, sizeof(int), cudaMemcpyDeviceToHost,
+                              static_cast<cudaStream_t>(stream)));
+  return SPC_OK;
+}
+
 extern "C" int spc_check_device_status(void* stream) {
   int value = 0;
   const int rc = spc::read_device_status(static_cast<cudaStream_t>(stream), &value);
   if (rc != SPC_OK) return rc;
+  if (value == SPC_ERR_INVALID_ARGUMENT)
+    return spc::fail(value, "a rulebook kernel met an index row outside batch_size / spatial_shape (device status %d)", value);
   if (value != 0) return spc::fail(value, "a kernel of this library recorded device status %d (a bounded wait expired)", value);
   return SPC_OK;
 }

@@ -4,8 +4,9 @@
 // Same computation and tiling as gemm_tc.cu (128 output rows per CTA, fp32
 // accumulator in tensor memory).  What differs is how a shared-memory stage is
 // filled:
-//   * the 128 gathered feature rows are copied by EIGHT warps with 16-byte
-//     cp.async (8 lanes per row, zero fill for absent rows); each thread's
+//   * the 128 gathered feature rows are copied by four warps with 16-byte
+//     cp.async (8 lanes per row, a thread copies one 16-byte piece of 8 rows,
+//     zero fill for absent rows); each thread's
 //     completion is delivered to the stage's mbarrier by
 //     cp.async.mbarrier.arrive.noinc, so nobody waits for data;
 //   * the weight slab W[:, k, chunk] arrives through one tiled 3-D TMA load
@@ -21,10 +22,10 @@
 // sustains roughly one 512-byte operation per ~30 cycles per SM, below what
 // the LSU path reaches, so the rows go through cp.async.
 //
-// Warp roles: warps 0-3 load the tile's table entries, vote on the active
-// kernel offsets (32 at a time) and later run the epilogue; warps 0-7 issue the
-// row copies; thread 0 issues the TMA weight loads; warp 8 issues tcgen05.mma.
-// All waits are bounded.
+// Warp roles (160 threads): warps 0-3 load the tile's table entries, vote on the
+// active kernel offsets (32 at a time), issue the row copies and later run the
+// epilogue; thread 0 also issues the TMA weight loads; warp 4 issues
+// tcgen05.mma.  All waits are bounded.
 #include <cuda.h>
 
 #include <algorithm>
@@ -53,14 +54,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
-
-#ifdef SPC_TRACE
-// Development aid (not compiled into the library): clock64 stamps of one CTA.
-__device__ long long g_trace[1024];
-#define SPC_STAMP(slot) do { if (blockIdx.x == gridDim.x / 2 && (slot) < 1024) g_trace[(slot)] = clock64(); } while (0)
-#else
-#define SPC_STAMP(slot) do { } while (0)
-#endif
 
 struct TmaParams {
   const void* src;
@@ -179,9 +172,6 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
     const uint8_t* src_chunk = static_cast<const uint8_t*>(p.src) + chunk * 16;
     const uint32_t src_pitch = static_cast<uint32_t>(p.r_dim) * ELEM;
 
-    int trace_n = 0;
-    (void)trace_n;
-    if (tid == 0) SPC_STAMP(0);
     for (int k0 = 0; k0 < p.kv; k0 += kGroup) {
       const int gcount = min(kGroup, p.kv - k0);
       if (tile_warp) {
@@ -213,7 +203,6 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
         mine = __reduce_or_sync(0xffffffffu, mine);
         if (lane == 0) vote[warp] = mine;
       }
-      if (tid == 0) SPC_STAMP(1);
       named_bar_sync(1, kIssueThreads);
       const uint32_t active = vote[0] | vote[1] | vote[2] | vote[3];
       real_stages += __popc(active) * n_rchunks;
@@ -225,11 +214,8 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
 #pragma unroll
         for (int i = 0; i < kRowsPerThread; ++i) j[i] = idx_s[kk * kTileM + row_lo + kRowStep * i];
         for (int rc = 0; rc < n_rchunks; ++rc) {
-          if (tid == 0) SPC_STAMP(16 + 2 * trace_n);
           if (ok && !mbar_wait(bar_empty + 8 * stage, empty_parity)) ok = false;
           if (ok) {
-            if (tid == 0) SPC_STAMP(17 + 2 * trace_n);
-            ++trace_n;
             const int r0 = rc * epr;
             const uint32_t a_dst = smem_u32(stage_base + static_cast<size_t>(stage) * stage_bytes);
             const uint32_t full = bar_full + 8 * stage;
@@ -285,9 +271,7 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
 
     // ---------------- epilogue (warps 0-3) ----------------
     if (tile_warp) {
-      if (tid == 0) SPC_STAMP(2);
       bool have_acc = mbar_wait(bar_accum, 0);
-      if (tid == 0) SPC_STAMP(3);
       if (!have_acc) atomicExch(p.status, SPC_ERR_DEVICE_WAIT_EXPIRED);
       have_acc = __all_sync(0xffffffffu, have_acc);
       tc_fence_after();
@@ -312,7 +296,6 @@ if (has_epilogue) finish_epilogue16(v, epi_scale + c0, epi_shift + c0, p.epi.act
           }
         }
       }
-      if (tid == 0) SPC_STAMP(4);
       tc_fence_before();
     }
   } else {
@@ -342,8 +325,6 @@ if (has_epilogue) finish_epilogue16(v, epi_scale + c0, epi_shift + c0, p.epi.act
         uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full, empty = bar_empty, inf = info0;
         uint32_t full_parity = 0, accumulate = 0;
         int stage = 0;
-        int mma_n = 0;
-        (void)mma_n;
         while (true) {
           // a wait that expires here is either a real failure or the producers having aborted
           if (!mbar_wait(full, full_parity)) {
@@ -354,8 +335,6 @@ if (has_epilogue) finish_epilogue16(v, epi_scale + c0, epi_shift + c0, p.epi.act
           // those writes before the tensor core's async-proxy reads
           fence_proxy_async();
           tc_fence_after();
-          SPC_STAMP(512 + mma_n);
-          ++mma_n;
           uint32_t ksteps;
           asm volatile("ld.shared.u32 %0, [%1];" : "=r"(ksteps) : "r"(inf) : "memory");
           if (ksteps == 0) {  // terminator
@@ -445,12 +424,8 @@ int row_span(int elems, int elem_size) {
 
 template <typename T, typename TO, bool B_MN>
 int launch_tma(TmaParams p, const CUtensorMap& map_b, size_t smem_bytes, cudaStream_t st) {
-  static bool configured = false;
-  if (!configured) {
-    SPC_CUDA_OK(cudaFuncSetAttribute(gather_gemm_tma_kernel<T, TO, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     200 * 1024));
-    configured = true;
-  }
+  static bool configured[kMaxDevices] = {false};  // per instantiation and device
+  SPC_CUDA_OK(ensure_dynamic_smem(gather_gemm_tma_kernel<T, TO, B_MN>, 200 * 1024, configured));
   const unsigned grid = static_cast<unsigned>(ceil_div(p.m_rows, kTileM));
   gather_gemm_tma_kernel<T, TO, B_MN><<<grid, kThreadsHybrid, smem_bytes, st>>>(p, map_b);
   SPC_LAUNCH_OK();
@@ -566,9 +541,3 @@ int gather_gemm_tma(const void* src, const void* w, const Epilogue& epi, const i
 }
 
 }  // namespace spc
-
-#ifdef SPC_TRACE
-extern "C" int spc_dev_read_trace(long long* host, int n) {
-  return cudaMemcpyFromSymbol(host, spc::g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : 1;
-}
-#endif

@@ -361,11 +361,8 @@ int span_of(int elems, int elem_size) {
 
 template <typename T, int W>
 int launch_wgrad_tc(const WgParams& p, size_t smem_bytes, cudaStream_t st) {
-  static bool configured = false;
-  if (!configured) {
-    SPC_CUDA_OK(cudaFuncSetAttribute(wgrad_tc_kernel<T, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    configured = true;
-  }
+  static bool configured[kMaxDevices] = {false};  // per instantiation and device
+  SPC_CUDA_OK(ensure_dynamic_smem(wgrad_tc_kernel<T, W>, 200 * 1024, configured));
   dim3 grid(static_cast<unsigned>(p.kv * p.splits), static_cast<unsigned>(ceil_div(p.c_out, kTileM)));
   wgrad_tc_kernel<T, W><<<grid, W * 32 + 32, smem_bytes, st>>>(p);
   SPC_LAUNCH_OK();
@@ -391,7 +388,7 @@ WgradSplit wgrad_tc_split(int64_t n_out, int c_in, int c_out, int kv) {
   const int64_t tiles = static_cast<int64_t>(kv) * ceil_div(c_out, tc::kTileM);
   // several CTAs per resident slot: offsets differ a lot in how many pairs they have (the centre
   // offset of a submanifold layer has all of them), and surplus CTAs even that out
-  int64_t want = ceil_div(16 * 148, std::max<int64_t>(tiles, 1));
+  int64_t want = ceil_div(16 * static_cast<int64_t>(sm_count()), std::max<int64_t>(tiles, 1));
   const int64_t by_len = std::max<int64_t>(1, n_out / 4096);
   want = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(want, by_len), 64));
   s.splits = static_cast<int>(want);

@@ -1,9 +1,13 @@
 // Sparse max / average pooling over implicit-gemm pair tables.
 //
-// HBM-bound gather-reduce: one thread owns one 16-byte channel vector of one
-// output row, walks the entries of that row that are present (compacted per
-// CTA in shared memory), loads the gathered rows with 16-byte accesses, four
-// independent rows in flight, and writes the result with one 16-byte store.
+// HBM-bound gather-reduce.  pool_group_kernel: an output row is owned by a group
+// of 4..32 lanes, each holding up to four 16-byte channel vectors; the group
+// reads 32 table entries of the row with one round of loads, a ballot per load
+// builds the presence mask and the lanes walk only the set bits (the entry is
+// passed around by shuffle), with the gathers of two rows in flight and the
+// table entries of the next row group fetched ahead.  pool_compact_kernel
+// (entries compacted per CTA in shared memory, one thread per 16-byte vector)
+// takes the channel counts the group shape cannot.
 // Algorithmic bytes per output row: kv*4 (table) + pairs*C*e (gathered
 // rows) + C*e (store).
 //

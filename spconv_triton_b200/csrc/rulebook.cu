@@ -21,6 +21,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "gemm_internal.cuh"
 
 namespace spc {
 namespace {
@@ -290,6 +291,21 @@ __device__ __forceinline__ void load_coord(const int32_t* __restrict__ idx, long
   for (int d = 0; d <= ND; ++d) c[d] = __ldg(&idx[row * (ND + 1) + d]);
 }
 
+// A row whose batch index or coordinates lie outside [0, batch) x [0, in_shape) must not be
+// turned into a bitmap or table index.  Kernels skip such rows (they get no pairs); the phase-1
+// kernels also record SPC_ERR_INVALID_ARGUMENT so that the host raises.
+template <int ND>
+__device__ __forceinline__ bool coord_in_grid(const Geo& g, const int* c) {
+  bool ok = c[0] >= 0 && c[0] < g.batch;
+#pragma unroll
+  for (int d = 0; d < ND; ++d) ok = ok && c[d + 1] >= 0 && c[d + 1] < g.in_shape[d];
+  return ok;
+}
+__device__ __forceinline__ void flag_bad_row(int* counters, int* dev_status) {
+  atomicExch(&counters[1], SPC_ERR_INVALID_ARGUMENT);  // counters[kStatus]
+  if (dev_status != nullptr) atomicExch(dev_status, SPC_ERR_INVALID_ARGUMENT);
+}
+
 template <int ND>
 __device__ __forceinline__ long long in_key_of(const Geo& g, const int* c) {
   long long lin = c[0];
@@ -316,12 +332,16 @@ enum Counter { kUniqueCount = 0, kStatus = 1, kUnsorted = 2 };
 template <int ND, bool K64>
 __global__ void __launch_bounds__(kThreads)
 insert_inputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n,
-                     Table<K64> tin, int* counters, uint32_t* __restrict__ bitmap) {
+                     Table<K64> tin, int* counters, uint32_t* __restrict__ bitmap, int* dev_status) {
   const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
   if (j >= n) return;
   if (bitmap != nullptr && counters[kUnsorted] == 0) return;  // rows are ranks of the bitmap
   int c[ND + 1];
   load_coord<ND>(idx, j, c);
+  if (!coord_in_grid<ND>(g, c)) {
+    flag_bad_row(counters, dev_status);
+    return;
+  }
   using key_t = typename Table<K64>::key_t;
   const long long key = in_key_of<ND>(g, c);
   if (!tin.insert_min(static_cast<key_t>(key), static_cast<uint32_t>(j)))
@@ -334,11 +354,16 @@ insert_inputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ 
 template <int ND>
 __global__ void __launch_bounds__(kThreads)
 mark_inputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n,
-                   uint32_t* __restrict__ bitmap, int* counters) {
+                   uint32_t* __restrict__ bitmap, int* counters, int* dev_status) {
   const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
   if (j >= n) return;
   int c[ND + 1];
   load_coord<ND>(idx, j, c);
+  if (!coord_in_grid<ND>(g, c)) {
+    flag_bad_row(counters, dev_status);
+    counters[kUnsorted] = 1;  // a skipped row breaks "row number = rank of its bit"
+    return;
+  }
   const long long key = in_key_of<ND>(g, c);
   atomicOr(&bitmap[key >> 5], 1u << (key & 31));
   if (j > 0) {
@@ -413,6 +438,7 @@ mark_outputs_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ i
   if (j >= n) return;
   int c[ND + 1];
   load_coord<ND>(idx, j, c);
+  if (!coord_in_grid<ND>(g, c)) return;  // recorded by the input pass
   uint32_t mask[ND];
 #pragma unroll
   for (int d = 0; d < ND; ++d) {
@@ -442,9 +468,12 @@ enumerate_outputs_kernel(const __grid_constant__ Geo g, const int32_t* __restric
                          int* counters) {
   using key_t = typename Table<K64>::key_t;
   const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
-  const bool live = j < n;
+  bool live = j < n;
   int c[ND + 1];
-  if (live) load_coord<ND>(idx, j, c);
+  if (live) {
+    load_coord<ND>(idx, j, c);
+    live = coord_in_grid<ND>(g, c);  // a row outside the grid (recorded by the input pass) reaches no output
+  }
   const unsigned lane = threadIdx.x & 31u;
   for (int k0 = 0; k0 < g.kv; k0 += 32) {
     const int gcount = min(32, g.kv - k0);
@@ -519,8 +548,10 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
   if (r >= n_out) return;
   int o[ND + 1];
   int quad[4] = {-1, -1, -1, -1};  // four consecutive offsets of the row-major copy
+  bool row_ok = true;
   if (g.subm) {
     load_coord<ND>(idx, r, o);
+    row_ok = coord_in_grid<ND>(g, o);  // a row outside the grid gets no pairs
   } else {
     delinearize_out<ND>(g, static_cast<long long>(sorted_out[r]), o);
 #pragma unroll
@@ -572,7 +603,8 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
     for (int b = 0; b < kBatch; ++b) {
       key[b] = -1;
       if (k0 + b < g.kv) {
-        if (fast) {
+        if (!row_ok) {
+        } else if (fast) {
           uint32_t ok = 1u;
           long long kk = base;
 #pragma unroll
@@ -640,11 +672,12 @@ fill_bwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, 
   int quad[4] = {-1, -1, -1, -1};
   int c[ND + 1];
   load_coord<ND>(idx, j, c);
+  const bool row_ok = coord_in_grid<ND>(g, c);  // a row outside the grid contributes to no output
   Odometer<ND> od;
   od.reset();
   uint32_t word = 0;
   for (int k = 0; k < g.kv; ++k) {
-    const long long key = out_key_from_input<ND>(g, c, od.pos);
+    const long long key = row_ok ? out_key_from_input<ND>(g, c, od.pos) : -1;
     int r = key >= 0 ? tout.find(static_cast<key_t>(key)) : -1;
     if (r >= n_out) r = -1;  // rows cut off by num_out_act_bound
     pair_bwd[static_cast<long long>(k) * n_in + j] = r;
@@ -705,6 +738,7 @@ __device__ __forceinline__ int native_out_row(const Geo& g, const int32_t* __res
   using key_t = typename Table<K64>::key_t;
   int c[ND + 1];
   load_coord<ND>(idx, j, c);
+  if (!coord_in_grid<ND>(g, c)) return -1;
   Odometer<ND> od;
   od.set(g, k);
   const long long key = out_key_from_input<ND>(g, c, od.pos);
@@ -1013,6 +1047,9 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
                  int64_t* n_out_host, cudaStream_t st) {
   using key_t = typename Table<K64>::key_t;
   int* counters = reinterpret_cast<int*>(ws + L.off_counters);
+  // Submanifold layers return without a host read, so a row outside the grid is also recorded in the
+  // device status word, which the host reads at its next synchronisation point.
+  int* dev_status = device_status_ptr();
   SPC_CUDA_OK(cudaMemsetAsync(counters, 0, 256, st));
   SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin, 0xFF, static_cast<size_t>(L.cap_in) * 8, st));
   if (K64) SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin_vals, 0x7F, static_cast<size_t>(L.cap_in) * 4, st));
@@ -1020,7 +1057,7 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
   uint32_t* bitmap = L.bitmap_bytes ? reinterpret_cast<uint32_t*>(ws + L.off_bitmap) : nullptr;
   if (bitmap != nullptr) {
     SPC_CUDA_OK(cudaMemsetAsync(bitmap, 0, L.bitmap_bytes, st));
-    mark_inputs_kernel<ND><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, bitmap, counters);
+    mark_inputs_kernel<ND><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, bitmap, counters, dev_status);
     SPC_LAUNCH_OK();
     const int64_t words = static_cast<int64_t>(L.bitmap_bytes / 4);
     uint32_t* iprefix = reinterpret_cast<uint32_t*>(ws + L.off_iprefix);
@@ -1029,7 +1066,8 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
     size_t scan_bytes = L.scan_bytes;
     SPC_CUDA_OK(cub::DeviceScan::ExclusiveSum(ws + L.off_scan, scan_bytes, iprefix, iprefix, static_cast<int>(words), st));
   }
-  insert_inputs_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, tin, counters, bitmap);
+  insert_inputs_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, tin, counters, bitmap,
+                                                                       dev_status);
   SPC_LAUNCH_OK();
   if (g.subm) {
     *n_out_host = n_in;
@@ -1067,9 +1105,19 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
     SPC_LAUNCH_OK();
   }
   int host[2] = {0, 0};
+  int sticky = 0;  // the device status word: a bounded wait of an earlier kernel, or a bad row of an earlier layer
   SPC_CUDA_OK(cudaMemcpyAsync(host, counters, sizeof(host), cudaMemcpyDeviceToHost, st));
+  if (dev_status != nullptr) SPC_CUDA_OK(cudaMemcpyAsync(&sticky, dev_status, sizeof(int), cudaMemcpyDeviceToHost, st));
   SPC_CUDA_OK(cudaStreamSynchronize(st));
-  if (host[kStatus] != 0) return fail(host[kStatus], "rulebook: hash table full (status %d)", host[kStatus]);
+  if (host[kStatus] != 0 || sticky != 0) {
+    if (dev_status != nullptr && sticky != 0) SPC_CUDA_OK(cudaMemsetAsync(dev_status, 0, sizeof(int), st));
+    const int code = host[kStatus] != 0 ? host[kStatus] : sticky;
+    if (code == SPC_ERR_INVALID_ARGUMENT)
+      return fail(code, "rulebook: an index row lies outside batch_size / spatial_shape");
+    if (code == SPC_ERR_DEVICE_WAIT_EXPIRED)
+      return fail(code, "a bounded device-side wait of an earlier kernel expired; its output is incomplete");
+    return fail(code, "rulebook: hash table full (status %d)", code);
+  }
   const int64_t n_out = host[kUniqueCount];
   *n_out_host = n_out;
   if (n_out == 0) return SPC_OK;

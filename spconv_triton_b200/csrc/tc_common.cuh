@@ -15,7 +15,10 @@ constexpr int kProducers = 128;
 constexpr int kThreadsTc = 160;
 constexpr int kGroup = 32;  // kernel offsets voted on together
 constexpr int kMaxStages = 8;
-constexpr uint32_t kSpinLimit = 1u << 20;
+// A wait polls kSpinLimit times, then keeps polling against a wall-clock limit, so that a slow
+// tile (a long reduction, a preempted SM) is not mistaken for a failure while every wait still ends.
+constexpr uint32_t kSpinLimit = 1u << 16;
+constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // one second
 
 // ---- PTX wrappers --------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -38,11 +41,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
+  const unsigned long long t0 = global_timer_ns();
+  do {
+    for (uint32_t it = 0; it < 1024; ++it)
+      if (mbar_try_wait(bar, parity)) return true;
+  } while (global_timer_ns() - t0 < kWaitLimitNs);
+  return false;
+}
 // Bounded wait; false means the limit was reached.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t it = 0; it < kSpinLimit; ++it)
     if (mbar_try_wait(bar, parity)) return true;
-  return false;
+  return mbar_wait_slow(bar, parity);
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");

@@ -23,8 +23,8 @@ def shard_by_sample(indices: torch.Tensor, features: torch.Tensor, batch_size: i
 
 
 def allreduce_gradients(parameters, world: int | None = None):
-    """Sum-then-average the gradients of ``parameters`` over the default process
-    group (one flat bucket; the parameter volume of sparse backbones is small)."""
+    """Average the gradients of ``parameters`` over the default process group,
+    blocking (one flat bucket).  ``GradientReducer`` is the overlapped form."""
     import torch.distributed as dist
 
     grads = [p.grad for p in parameters if p.grad is not None]
@@ -39,6 +39,128 @@ def allreduce_gradients(parameters, world: int | None = None):
         n = g.numel()
         g.copy_(flat[off:off + n].view_as(g).to(g.dtype))
         off += n
+
+
+class _Bucket:
+    __slots__ = ("params", "views", "flat", "pending", "work", "ready")
+
+
+class GradientReducer:
+    """Data-parallel gradient averaging, bucketed and overlapped with backward.
+
+    The reference leaves data parallelism to the user (its README tells users
+    to wrap the model in DistributedDataParallel); this is the same exchange --
+    one all-reduce (sum) of the parameter gradients per step, nothing else ever
+    crosses GPUs -- arranged for sparse backbones, whose backward is a chain of
+    short kernels: parameters are grouped into buckets in the order backward
+    finishes them (last layer first); the moment the last gradient of a bucket
+    has been accumulated, the bucket is flattened and its all-reduce is queued
+    on a communication stream, so that NCCL runs beside the remaining input- and
+    weight-gradient kernels.  ``finish()`` (after ``backward()``) makes the
+    current stream wait for the buckets, divides by the world size and writes
+    the averages back into ``p.grad``.
+
+        reducer = GradientReducer(model.parameters())
+        loss.backward()
+        reducer.finish()
+        optimizer.step()
+
+    Works on CPU tensors with the gloo backend (no streams) for tests.
+    """
+
+    def __init__(self, parameters, bucket_bytes: int = 8 << 20, process_group=None):
+        import torch.distributed as dist
+
+        self.group = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        params = [p for p in parameters if p.requires_grad]
+        self.buckets: list[_Bucket] = []
+        self._bucket_of: dict = {}
+        self._comm_stream = None
+        self._handles = []
+        self.launched_during_backward = 0
+        cur, cur_bytes = [], 0
+        for p in reversed(params):  # backward reaches the last layer's parameters first
+            cur.append(p)
+            cur_bytes += p.numel() * 4
+            if cur_bytes >= bucket_bytes:
+                self._add_bucket(cur)
+                cur, cur_bytes = [], 0
+        if cur:
+            self._add_bucket(cur)
+        for p in params:
+            self._handles.append(p.register_post_accumulate_grad_hook(self._on_grad))
+
+    def _add_bucket(self, params):
+        b = _Bucket()
+        b.params = list(params)
+        dev = params[0].device
+        b.flat = torch.zeros(sum(p.numel() for p in params), dtype=torch.float32, device=dev)
+        b.views, off = [], 0
+        for p in params:
+            b.views.append(b.flat[off:off + p.numel()].view_as(p))
+            off += p.numel()
+        b.pending, b.work, b.ready = len(params), None, None
+        for p in params:
+            self._bucket_of[id(p)] = b
+        self.buckets.append(b)
+
+    def _stream(self, device):
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=device, priority=-1)
+        return self._comm_stream
+
+    def _on_grad(self, p):
+        b = self._bucket_of[id(p)]
+        b.pending -= 1
+        if b.pending == 0:
+            self.launched_during_backward += 1
+            self._launch(b)
+
+    def _launch(self, b):
+        import torch.distributed as dist
+
+        grads = [p.grad if p.grad is not None else torch.zeros_like(p) for p in b.params]
+        torch._foreach_copy_(b.views, grads)
+        if self.world == 1:
+            return
+        if b.flat.is_cuda:
+            comm = self._stream(b.flat.device)
+            comm.wait_stream(torch.cuda.current_stream(b.flat.device))
+            with torch.cuda.stream(comm):
+                b.work = dist.all_reduce(b.flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        else:
+            b.work = dist.all_reduce(b.flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+
+    def finish(self):
+        """Call after ``backward()``: every bucket averaged and written back."""
+        for b in self.buckets:
+            if b.pending > 0:
+                # parameters that took no part in this backward keep a zero (or their old) gradient
+                if all(p.grad is None for p in b.params):
+                    b.pending = len(b.params)
+                    continue
+                self._launch(b)
+            if b.work is not None:
+                if b.flat.is_cuda:
+                    with torch.cuda.stream(self._stream(b.flat.device)):
+                        b.work.wait()
+                    torch.cuda.current_stream(b.flat.device).wait_stream(self._stream(b.flat.device))
+                else:
+                    b.work.wait()
+                b.work = None
+            if self.world > 1:
+                b.flat.div_(self.world)
+            targets = [p.grad for p in b.params if p.grad is not None]
+            sources = [v for p, v in zip(b.params, b.views) if p.grad is not None]
+            if targets:
+                torch._foreach_copy_(targets, sources)
+            b.pending = len(b.params)
+
+    def remove(self):
+        for h in self._handles:
+            h.remove()
+        self._handles.clear()
 
 
 def aggregate_throughput(local_units: float, local_ms: float, device=None):

@@ -2,13 +2,18 @@
 
 from __future__ import annotations
 
+import threading
 import time
 from collections import OrderedDict
 
 import torch
 from torch import nn
 
+from spconv_triton_b200 import _lib
+
 from .core import SparseConvTensor
+
+_depth = threading.local()  # nesting depth of SparseSequential.forward on this thread
 
 
 class SparseModule(nn.Module):
@@ -66,15 +71,25 @@ class SparseSequential(SparseModule):
     def forward(self, x):
         from . import runahead
 
+        # the outermost container of a CUDA pass looks at the status its device posted during an
+        # earlier pass (raises without waiting) and posts the status of this pass when it is done
+        device = None
+        if isinstance(x, SparseConvTensor) and x.features.is_cuda and not getattr(_depth, "n", 0):
+            device = x.features.device
+            _lib.raise_posted_status(device)
+        _depth.n = getattr(_depth, "n", 0) + 1
         entered, owned = x, runahead.begin(self, x)
         try:
             x = self._run(x)
         finally:
+            _depth.n -= 1
             if owned is not None:
                 owned.join_late()
                 entered._planner = None
         if owned is not None and isinstance(x, SparseConvTensor):
             x._planner = None
+        if device is not None and not torch.cuda.is_current_stream_capturing():
+            _lib.post_device_status(device)
         return x
 
     def _run(self, x):

@@ -52,17 +52,23 @@ def _reject_int8(t: torch.Tensor):
         raise NotImplementedError("int8 is not supported by spconv_triton")
 
 
+_INPLACE_ACTIVATIONS = {
+    "None_": lambda t, alpha: t,
+    "ReLU": lambda t, alpha: t.relu_(),
+    "Sigmoid": lambda t, alpha: t.sigmoid_(),
+    "LeakyReLU": lambda t, alpha: torch.nn.functional.leaky_relu_(t, alpha),
+}
+
+
 def _apply_act_inplace(out: torch.Tensor, act_type, act_alpha: float, act_beta: float):
+    """The activation enum applied to ``out`` in place (the reference applies it
+    after its kernel the same way, spconv_triton/pytorch/ops.py:63-73; here it is
+    only used where the activation is not fused into the GEMM's store)."""
     name = getattr(act_type, "name", "None_")
-    if name == "None_":
-        return out
-    if name == "ReLU":
-        return torch.relu_(out)
-    if name == "Sigmoid":
-        return torch.sigmoid_(out)
-    if name == "LeakyReLU":
-        return torch.nn.functional.leaky_relu_(out, act_alpha)
-    raise NotImplementedError(f"activation {name} not supported")
+    fn = _INPLACE_ACTIVATIONS.get(name)
+    if fn is None:
+        raise NotImplementedError(f"activation {name} not supported")
+    return fn(out, act_alpha)
 
 
 def _act_code(act_type) -> int:

@@ -62,3 +62,46 @@ def uniform_batch(seed, batch, n_per_sample, grid):
         c = np.stack(np.unravel_index(lin, grid), 1).astype(np.int32)
         rows.append(np.concatenate([np.full((n_per_sample, 1), b, np.int32), c], 1))
     return np.concatenate(rows, 0)
+
+
+def indoor_like_sample(rng, n_target, grid=(512, 512, 64)):
+    """(x, y, z) int32 [n_target, 3], unique: the six walls of 3-6 random
+    axis-aligned boxes plus 2-4 random tilted planes, rasterised to voxels and
+    sub-sampled to ``n_target`` (fewer if the surfaces hold fewer voxels)."""
+    gx, gy, gz = (int(g) for g in grid)
+    parts = []
+    for _ in range(int(rng.integers(3, 7))):
+        lo = np.array([rng.integers(0, gx - 64), rng.integers(0, gy - 64), rng.integers(0, max(gz - 24, 1))])
+        ext = np.array([rng.integers(48, 256), rng.integers(48, 256), rng.integers(12, max(gz // 2, 13))])
+        hi = np.minimum(lo + ext, [gx - 1, gy - 1, gz - 1])
+        xs, ys, zs = (np.arange(lo[d], hi[d] + 1) for d in range(3))
+        for d, (a, b) in enumerate(((ys, zs), (xs, zs), (xs, ys))):
+            u, v = np.meshgrid(a, b, indexing="ij")
+            for face in (lo[d], hi[d]):
+                cols = [None, None, None]
+                cols[d] = np.full(u.size, face)
+                others = [c for c in range(3) if c != d]
+                cols[others[0]], cols[others[1]] = u.ravel(), v.ravel()
+                parts.append(np.stack(cols, 1))
+    xs, ys = np.meshgrid(np.arange(gx), np.arange(gy), indexing="ij")
+    for _ in range(int(rng.integers(2, 5))):
+        a, b = rng.uniform(-0.08, 0.08, 2)
+        c = rng.uniform(0.2, 0.8) * gz
+        z = np.rint(a * (xs - gx / 2) + b * (ys - gy / 2) + c).astype(np.int64)
+        ok = (z >= 0) & (z < gz)
+        parts.append(np.stack([xs[ok], ys[ok], z[ok]], 1))
+    pts = _unique_rows(np.concatenate(parts, 0).astype(np.int64), (gx, gy, gz))
+    pts = pts[rng.permutation(pts.shape[0])[:n_target]]
+    return pts.astype(np.int32)
+
+
+def indoor_like_batch(seed, batch, n_range, grid=(512, 512, 64)):
+    """int32 indices [N, 4] (batch, x, y, z), rows grouped by sample; the
+    per-sample voxel count is an integer drawn uniformly from ``n_range``."""
+    rng = np.random.default_rng(seed)
+    rows = []
+    for b in range(batch):
+        n = int(rng.integers(n_range[0], n_range[1] + 1))
+        c = indoor_like_sample(rng, n, grid)
+        rows.append(np.concatenate([np.full((c.shape[0], 1), b, np.int32), c], 1))
+    return np.concatenate(rows, 0)

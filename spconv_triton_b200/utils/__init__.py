@@ -1,48 +1,32 @@
-"""Utility namespace (reference: spconv_triton/utils/__init__.py): the
-``Point2Voxel{CPU,GPU}{1-4}d`` classes.  The CPU classes exist for import
-compatibility and raise when constructed: voxelisation runs on CUDA only."""
+"""``spconv_triton_b200.utils``: the eight ``Point2Voxel{CPU,GPU}{1..4}d`` names
+of the reference's utils namespace (spconv_triton/utils/__init__.py) over the
+CUDA voxeliser of this package.  The CPU names exist so that imports keep
+working; constructing one raises, because voxelisation here runs on CUDA only."""
 
-from contextlib import AbstractContextManager
+from contextlib import nullcontext  # noqa: F401  (re-exported, as the reference's namespace does)
 
 import torch
+
+from spconv_triton_b200.pytorch.utils import PointToVoxel as _PointToVoxel
 
 CPU_ONLY_BUILD = False
 
 
-class nullcontext(AbstractContextManager):
-    """Context manager that does no additional processing."""
+class _FixedRank(_PointToVoxel):
+    """PointToVoxel bound to one dimensionality and one device type (class attributes)."""
 
-    def __init__(self, enter_result=None):
-        self.enter_result = enter_result
+    _ndim = 0
+    _device_type = "cuda"
 
-    def __enter__(self):
-        return self.enter_result
-
-    def __exit__(self, *excinfo):
-        pass
-
-
-from spconv_triton_b200.pytorch.utils import PointToVoxel as _PointToVoxel  # noqa: E402
+    def __init__(self, vsize_xyz, coors_range_xyz, num_point_features, max_num_voxels, max_num_points_per_voxel):
+        if len(vsize_xyz) != self._ndim:
+            raise AssertionError
+        super().__init__(vsize_xyz, coors_range_xyz, num_point_features, max_num_voxels, max_num_points_per_voxel,
+                         device=torch.device(self._device_type))
 
 
-def _make_p2v(ndim: int, device_type: str):
-    class _Point2Voxel(_PointToVoxel):
-        def __init__(self, vsize_xyz, coors_range_xyz, num_point_features, max_num_voxels,
-                     max_num_points_per_voxel):
-            if len(vsize_xyz) != ndim:
-                raise AssertionError
-            super().__init__(vsize_xyz, coors_range_xyz, num_point_features, max_num_voxels,
-                             max_num_points_per_voxel, device=torch.device(device_type))
-
-    _Point2Voxel.__name__ = _Point2Voxel.__qualname__ = f"Point2Voxel{device_type.upper()}{ndim}d"
-    return _Point2Voxel
-
-
-Point2VoxelCPU1d = _make_p2v(1, "cpu")
-Point2VoxelCPU2d = _make_p2v(2, "cpu")
-Point2VoxelCPU3d = _make_p2v(3, "cpu")
-Point2VoxelCPU4d = _make_p2v(4, "cpu")
-Point2VoxelGPU1d = _make_p2v(1, "cuda")
-Point2VoxelGPU2d = _make_p2v(2, "cuda")
-Point2VoxelGPU3d = _make_p2v(3, "cuda")
-Point2VoxelGPU4d = _make_p2v(4, "cuda")
+for _dev in ("cpu", "cuda"):
+    for _nd in (1, 2, 3, 4):
+        _name = f"Point2Voxel{'CPU' if _dev == 'cpu' else 'GPU'}{_nd}d"
+        globals()[_name] = type(_name, (_FixedRank,), {"_ndim": _nd, "_device_type": _dev, "__module__": __name__})
+del _dev, _nd, _name

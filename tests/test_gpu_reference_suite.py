@@ -1,0 +1,74 @@
+"""Runs the reference project's OWN test files, unmodified, against this package.
+
+The reference's suite selects the implementation under test with the
+environment variable ``SPCONV_TEST_IMPL`` (its ``tests/helpers.py:24-47``);
+``spconv_triton_b200`` exposes every module that loader imports.  The test
+files are taken from a checkout of the reference: ``$SPCONV_REFERENCE_ROOT`` or
+the git-ignored copy ``baseline/_ref/reference`` made by
+``baseline/install_reference.py``; without either the tests are skipped.
+
+Files whose golden vectors are listed in the reference's
+``.MISSING_LARGE_BLOBS`` (not part of the checkout) cannot be collected and
+are not listed here; single tests that load such a file are deselected by name.
+"""
+
+from __future__ import annotations
+
+import os
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+# file -> tests deselected because they load a golden file that is not in the checkout
+FILES = {
+    "test_network.py": [],
+    "test_ext_pool.py": [],
+    "test_misc_modules.py": [],
+    "test_sparse_conv_tensor.py": [],
+    "test_large_batch.py": [],
+    "test_int64_linearize.py": [],
+    "test_train_convergence.py": [],
+    "test_api_surface.py": [],
+    "test_ext_misc.py": [],
+    "test_ext_p2v.py": [],
+    "test_module_protocol.py": ["test_half_cast_forward_matches_fp16_golden", "test_state_dict_save_load_forward",
+                                "test_optimizer_smoke", "test_once_differentiable_backward"],
+    "test_conv_edge.py": ["test_duplicate_indice_key_asserts"],
+}
+
+
+def _reference_root():
+    env = os.environ.get("SPCONV_REFERENCE_ROOT")
+    for cand in ([Path(env)] if env else []) + [ROOT / "baseline" / "_ref" / "reference"]:
+        if (cand / "tests" / "helpers.py").is_file():
+            return cand
+    return None
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(FILES))
+def test_reference_file(name, tmp_path):
+    ref = _reference_root()
+    if ref is None:
+        pytest.skip("no checkout of the reference project (SPCONV_REFERENCE_ROOT or baseline/_ref/reference)")
+    env = dict(os.environ)
+    env["SPCONV_TEST_IMPL"] = "spconv_triton_b200"
+    env["PYTHONPATH"] = os.pathsep.join([str(ROOT)] + ([env["PYTHONPATH"]] if env.get("PYTHONPATH") else []))
+    env.pop("SPCONV_TEST_EXPECT_WARM", None)
+    cmd = [sys.executable, "-m", "pytest", str(ref / "tests" / name), "-q", "-p", "no:cacheprovider",
+           "--rootdir", str(ref), "-c", str(ref / "pyproject.toml"), "--basetemp", str(tmp_path / "t")]
+    for t in FILES[name]:
+        cmd += ["--deselect", f"{ref / 'tests' / name}::{t}"]
+    res = subprocess.run(cmd, cwd=str(ref), env=env, capture_output=True, text=True, timeout=1500)
+    tail = "\n".join((res.stdout + "\n" + res.stderr).splitlines()[-40:])
+    summary = re.findall(r"(\d+) (passed|failed|error|errors|skipped|deselected)", res.stdout)
+    out_dir = ROOT / "gpurun_out"
+    if out_dir.is_dir():
+        with open(out_dir / "reference_suite.txt", "a") as f:
+            f.write(f"{name}: rc={res.returncode} " + " ".join(f"{n} {k}" for n, k in summary) + "\n")
+    assert res.returncode == 0, f"{name} against spconv_triton_b200:\n{tail}"

@@ -162,3 +162,37 @@ def test_host_side_errors():
     far[:, 1:] = far[:, 1:] % 7 + 1
     with pytest.raises(ValueError, match="points vanished"):
         P.igemm_pairs(far, 1, [8, 8, 8], three(1), three(8), three(0), three(1), three(0), False, False, True, False)
+
+
+def test_rows_outside_the_grid_are_skipped_and_reported():
+    """A batch index >= batch_size or a coordinate outside spatial_shape must not become a bitmap or
+    table index.  Strided layers read their counters on the host and raise at once; submanifold
+    layers have no host read: the row gets no pairs and the device status word carries the error
+    to the next status check."""
+    from spconv_triton_b200 import _lib
+    from spconv_triton_b200.pytorch._impl import gemm as G
+
+    P = _pairs()
+    shape, batch = [16, 20, 24], 2
+    good = unique_coords(3, 4000, batch, shape)
+    three = lambda v: [v] * 3  # noqa: E731
+    G.check_device_status()
+    for bad in ([2, 1, 1, 1], [0, 16, 0, 0], [0, -1, 3, 3], [-1, 0, 0, 0], [1, 5, 5, 1 << 20]):
+        rows = good.copy()
+        rows[123] = bad
+        idx = torch.from_numpy(rows).to(DEV)
+        with pytest.raises(_lib.SpconvB200Error, match="outside batch_size") as e:
+            P.igemm_pairs(idx, batch, shape, three(3), three(2), three(1), three(1), three(0), False, False, True, False)
+        assert e.value.status == _lib.SPC_ERR_INVALID_ARGUMENT
+        res = P.igemm_pairs(idx, batch, shape, three(3), three(1), three(1), three(1), three(0), True, False, True, False)
+        assert bool((res[2][:, 123] == -1).all()) and bool((res[3][:, 123] == -1).all())
+        assert not bool((res[2] == 123).any())
+        with pytest.raises(_lib.SpconvB200Error, match="outside batch_size"):
+            G.check_device_status()
+        G.check_device_status()  # reported once, then clear
+    # the rest of the rows are unaffected
+    exp = orb.igemm_pairs(np.delete(good, 123, 0), batch, shape, three(3), three(1), three(1), three(1), three(0), True,
+                          False, True, False)
+    got = P.igemm_pairs(torch.from_numpy(np.delete(good, 123, 0)).to(DEV), batch, shape, three(3), three(1), three(1),
+                        three(1), three(0), True, False, True, False)
+    check_igemm_against(got, exp, True, good.shape[0] - 1)

@@ -128,3 +128,24 @@ def test_runahead_plan_walk():
 
     x = sp.SparseConvTensor(torch.zeros(1, 4), torch.zeros(1, 4, dtype=torch.int32), [4, 4, 4], 1)
     assert runahead.begin(net, x) is None and x._planner is None
+
+
+def test_posted_device_status_raises_at_the_next_pass():
+    """A failure recorded by a kernel (a bounded wait that expired, an index row
+    outside the grid) reaches the host through a mailbox word that the next
+    forward pass looks at; here the word is set on the host side of the wrapper."""
+    import pytest
+
+    from spconv_triton_b200 import _lib
+
+    _, view = _lib.status_mailbox(0)
+    _lib.raise_posted_status()  # nothing posted: no error
+    view[0] = _lib.SPC_ERR_DEVICE_WAIT_EXPIRED
+    with pytest.raises(_lib.SpconvB200Error, match="bounded device-side wait") as e:
+        _lib.raise_posted_status()
+    assert e.value.status == _lib.SPC_ERR_DEVICE_WAIT_EXPIRED
+    assert view[0] == 0  # delivered once
+    _lib.raise_posted_status()
+    view[0] = _lib.SPC_ERR_INVALID_ARGUMENT
+    with pytest.raises(_lib.SpconvB200Error, match="outside batch_size"):
+        _lib.raise_posted_status()

@@ -29,7 +29,7 @@ def _worker(rank, world, port, out_dir):
     from gpu_util import unique_coords
     from oracle import features as of
     from oracle import rulebook as orb
-    from spconv_triton_b200.parallel import aggregate_throughput, allreduce_gradients, shard_by_sample
+    from spconv_triton_b200.parallel import GradientReducer, aggregate_throughput, allreduce_gradients, shard_by_sample
 
     dist.init_process_group("gloo", rank=rank, world_size=world)
     shape, batch, n = [12, 16, 14], 4, 1200
@@ -58,6 +58,29 @@ def _worker(rank, world, port, out_dir):
     allreduce_gradients([p], world)
     dw_full = of.conv_backward_weight(feats, gout_full, full[2], (6, 27, 8))
     assert torch.allclose(p.grad * world, dw_full, atol=1e-5)
+
+    # bucketed reducer: hooks fire during backward, finish() leaves the average in p.grad
+    torch.manual_seed(3)
+    net = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
+    reducer = GradientReducer(net.parameters(), bucket_bytes=256)
+    assert len(reducer.buckets) >= 2
+    for step in range(2):  # twice: the buckets re-arm
+        net.zero_grad()
+        x = torch.randn(5, 8, generator=torch.Generator().manual_seed(10 * step + rank))
+        net(x).pow(2).sum().backward()
+        reducer.finish()
+        assert reducer.launched_during_backward == len(reducer.buckets) * (step + 1)
+        expect = [torch.zeros_like(q) for q in net.parameters()]
+        for r in range(world):
+            ref = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
+            ref.load_state_dict(net.state_dict())
+            xr = torch.randn(5, 8, generator=torch.Generator().manual_seed(10 * step + r))
+            ref(xr).pow(2).sum().backward()
+            for e, q in zip(expect, ref.parameters()):
+                e += q.grad / world
+        for e, q in zip(expect, net.parameters()):
+            assert torch.allclose(q.grad, e, atol=1e-5), (q.grad - e).abs().max()
+    reducer.remove()
 
     units, ms = aggregate_throughput(float(li.shape[0]), 10.0 + rank)
     assert units == n and ms == 11.0

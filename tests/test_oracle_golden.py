@@ -121,3 +121,10 @@ def test_output_size_known_answers():
     assert orb.deconv_output_size([8, 8, 8], [3, 3, 3], [2, 2, 2], [1, 1, 1], [1, 1, 1], [1, 1, 1]) == [16, 16, 16]
     with pytest.raises(ValueError):
         orb.deconv_output_size([8], [-1], [1], [0], [1], [0])
+
+
+def test_rows_in_grid():
+    from oracle import rulebook as orb
+
+    idx = np.array([[0, 0, 0, 0], [1, 15, 19, 23], [2, 1, 1, 1], [0, 16, 0, 0], [0, -1, 3, 3], [-1, 0, 0, 0]], np.int32)
+    assert orb.rows_in_grid(idx, 2, [16, 20, 24]).tolist() == [True, True, False, False, False, False]

@@ -15,6 +15,7 @@ import pytest
 import torch
 
 from gpu_util import DEV, unique_coords
+from oracle import features as of
 from oracle import rulebook as orb
 
 pytestmark = pytest.mark.gpu
@@ -60,6 +61,11 @@ def test_matches_regular_entry_point_on_two_calls_in_a_row():
         assert torch.equal(ref, got)
         scale = ref.float().abs().max().item()
         assert np.isfinite(scale) and scale > 0
+        # and the sum itself, against the fp64 oracle over the same table
+        expect = of.conv_backward_weight(feats.cpu().double(), gout.cpu().double(), pf.cpu().numpy(),
+                                         (c_out, pf.shape[0], c_in))
+        err = (got.cpu().double() - expect).abs().max().item() / expect.abs().max().item()
+        assert err <= (2e-3 if dtype == torch.float16 else 1e-5), f"{dtype}: {err:.2e}"
 
 
 def test_rejects_shapes_beyond_the_built_in_scratch():
