@@ -49,6 +49,9 @@ typedef enum { SPC_F16 = 0, SPC_BF16 = 1, SPC_F32 = 2, SPC_F64 = 3 } spc_dtype;
  * exactly and accumulate in fp32. */
 typedef enum { SPC_PREC_IEEE = 0, SPC_PREC_TF32 = 1 } spc_precision;
 
+/* Operand preparations for fp32 layers on the tensor cores (spc_tf32_prepare). */
+typedef enum { SPC_TF32_ROUND = 0, SPC_TF32_SPLIT_A = 1, SPC_TF32_SPLIT_B = 2 } spc_tf32_mode;
+
 /* Which implementation a GEMM entry point may use.  AUTO picks a tcgen05
  * kernel whenever the shape allows it (gathered rows copied with cp.async;
  * weight slabs loaded by tiled TMA when the channel widths fit a swizzle span,
@@ -337,6 +340,26 @@ int spc_conv_backward_input(const void* grad_out, const void* weight,
                             const int32_t* mask_argsort, void* din,
                             int64_t n_in, int64_t n_out, int c_in, int c_out, int kv,
                             int dtype, int precision, int path, void* stream);
+
+/* fp32 layers on the tensor cores.  The TF32 tensor-core path uses the upper 19
+ * bits of each fp32 operand.  spc_tf32_prepare writes a prepared copy of a
+ * row-major fp32 matrix [rows, cols]:
+ *   SPC_TF32_ROUND    dst [rows, cols]     every value rounded to the nearest TF32
+ *                     number, the rounding the reference's tl.dot applies when
+ *                     SPCONV_ALLOW_TF32 is set (_impl/gemm.py:55-62);
+ *   SPC_TF32_SPLIT_A  dst [rows, 3 cols]   rows [hi | lo | hi], x = hi + lo;
+ *   SPC_TF32_SPLIT_B  dst [rows, 3 cols]   rows [hi | hi | lo].
+ * A convolution whose gathered operand was split with SPLIT_A and whose weight
+ * with SPLIT_B (reduction length 3 c_in, precision SPC_PREC_TF32) computes
+ * hi hi + lo hi + hi lo, i.e. the fp32 product to 2^-22: this is how IEEE-mode
+ * fp32 layers (the reference's default, _impl/gemm.py:11-13) run on tcgen05.
+ * spc_tf32_prepare_weight does the same for a KRSC weight [c_out, kv, c_in] ->
+ * [c_out, kv, m c_in], or with `transpose` -> [c_in, kv, m c_out] (the operand
+ * of the input gradient written as a forward convolution of grad_out), m = 1
+ * (ROUND) or 3 (SPLIT_*).  No counterpart in the reference. */
+int spc_tf32_prepare(const float* src, float* dst, int64_t rows, int cols, int mode, void* stream);
+int spc_tf32_prepare_weight(const float* weight, float* dst, int c_out, int kv, int c_in,
+                            int transpose, int mode, void* stream);
 
 /* Bytes of device scratch spc_conv_backward_weight needs (fp32 partial sums
  * of the split reduction). */

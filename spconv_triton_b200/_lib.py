@@ -15,6 +15,7 @@ LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libspconv_b200.so"
 SPC_MAX_NDIM = 4
 SPC_F16, SPC_BF16, SPC_F32, SPC_F64 = 0, 1, 2, 3
 SPC_PREC_IEEE, SPC_PREC_TF32 = 0, 1
+SPC_TF32_ROUND, SPC_TF32_SPLIT_A, SPC_TF32_SPLIT_B = 0, 1, 2
 SPC_ACT_NONE, SPC_ACT_RELU, SPC_ACT_SIGMOID, SPC_ACT_LEAKY_RELU = 0, 1, 2, 3
 SPC_GEMM_AUTO, SPC_GEMM_SIMT, SPC_GEMM_TCGEN05, SPC_GEMM_TCGEN05_CPASYNC = 0, 1, 2, 3
 (SPC_OK, SPC_ERR_INVALID_ARGUMENT, SPC_ERR_CUDA, SPC_ERR_WORKSPACE_TOO_SMALL, SPC_ERR_HASH_TABLE_FULL,
@@ -67,6 +68,8 @@ _PROTOTYPES = {
     "spc_launch_count": (ctypes.c_longlong, []),
     "spc_check_device_status": (c_int, [_P]),
     "spc_post_device_status": (c_int, [_P, _P]),
+    "spc_tf32_prepare": (c_int, [_P, _P, c_int64, c_int, c_int, _P]),
+    "spc_tf32_prepare_weight": (c_int, [_P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "spc_conv_output_size": (c_int, [c_int, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32),
                                      POINTER(c_int32), POINTER(c_int32), POINTER(c_int32)]),
     "spc_deconv_output_size": (c_int, [c_int, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32),

@@ -33,13 +33,71 @@ def _precision(t: torch.Tensor) -> int:
     return _lib.SPC_PREC_IEEE
 
 
-def _rowmajor(pair_table, t):
-    """Row-major table copy for the tensor-core kernels (the CUDA-core kernels,
-    which serve IEEE fp32, do not use it, so none is built for them)."""
+def _rowmajor(pair_table, t, tensor_cores=None):
+    """Row-major table copy for the tensor-core kernels (the CUDA-core kernels
+    do not use it, so none is built for them)."""
     rm = getattr(pair_table, "_spc_rowmajor", None)
-    if rm is None and (t.dtype in (torch.float16, torch.bfloat16) or _precision(t) == _lib.SPC_PREC_TF32):
+    if tensor_cores is None:
+        tensor_cores = t.dtype in (torch.float16, torch.bfloat16) or _precision(t) == _lib.SPC_PREC_TF32
+    if rm is None and tensor_cores:
         rm = rowmajor_of(pair_table)
     return rm
+
+
+# fp32 layers on the tensor cores.  With SPCONV_ALLOW_TF32 the operands are rounded to TF32
+# (round to nearest, as the reference's tl.dot does) and multiplied once; without it (IEEE mode,
+# the reference's default) each operand is split into two TF32 numbers and the reduction runs over
+# [hi | lo | hi] . [hi | hi | lo], which carries fp32 accuracy at three times the TF32 work.  Set to
+# False to keep IEEE-mode fp32 layers on the CUDA cores.
+FP32_ON_TENSOR_CORES = True
+# The tensor cores add into their fp32 accumulator with truncation, so the error of the split path
+# grows with the number of accumulated terms: measured 4e-6 of the largest output at kv * c_in = 864,
+# 9e-6 at 1728, 1.7e-5 at 3456 (about 5e-9 per term).  IEEE mode promises 1e-5, so longer
+# reductions stay on the CUDA cores (IEEE fused multiply-add, 1e-6).
+FP32_SPLIT_MAX_REDUCTION = 1024
+
+
+def _fp32_plan(n_dim, r_dim, kv):
+    """(mode for the gathered operand, mode for the weight, reduction multiplier) if an fp32 layer
+    with ``n_dim`` outputs and reduction ``r_dim`` per kernel offset can run on the tcgen05
+    kernels, else None."""
+    if GEMM_PATH == _lib.SPC_GEMM_SIMT or n_dim % 16 or not 16 <= n_dim <= 256 or r_dim % 8:
+        return None
+    if bool(constants.SPCONV_ALLOW_TF32):
+        return _lib.SPC_TF32_ROUND, _lib.SPC_TF32_ROUND, 1
+    if FP32_ON_TENSOR_CORES and kv * r_dim <= FP32_SPLIT_MAX_REDUCTION:
+        return _lib.SPC_TF32_SPLIT_A, _lib.SPC_TF32_SPLIT_B, 3
+    return None
+
+
+def _prepared_rows(x, mode, mult):
+    out = torch.empty((x.shape[0], mult * x.shape[1]), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().spc_tf32_prepare(_lib.ptr(x), _lib.ptr(out), x.shape[0], x.shape[1], mode,
+                                            _lib.current_stream(x.device)))
+    return out
+
+
+def _prepared_weight(w, transpose, mode, mult):
+    """Prepared copy of the KRSC weight, remembered on the tensor until it changes."""
+    owner = w._base if w._base is not None else w  # the layer's parameter when ``w`` is a reshaped view of it
+    key = (w._version, w.data_ptr(), tuple(w.shape), bool(transpose), mode)
+    cache = getattr(owner, "_spc_tf32", None)
+    if cache is None:
+        cache = {}
+        try:
+            owner._spc_tf32 = cache
+        except AttributeError:
+            pass
+    hit = cache.get((bool(transpose), mode))
+    if hit is not None and hit[0] == key:
+        return hit[1]
+    k_out, kv, c_in = w.shape
+    shape = (c_in, kv, mult * k_out) if transpose else (k_out, kv, mult * c_in)
+    out = torch.empty(shape, dtype=torch.float32, device=w.device)
+    _lib.check(_lib.load().spc_tf32_prepare_weight(_lib.ptr(w), _lib.ptr(out), k_out, kv, c_in, int(bool(transpose)),
+                                                   mode, _lib.current_stream(w.device)))
+    cache[(bool(transpose), mode)] = (key, out)
+    return out
 
 
 def _order(kv, pair_mask, mask_argsort):
@@ -86,11 +144,17 @@ def conv_forward(features, filters_krsc, pair_fwd, n_out, bias=None, out_dtype=N
         act, alpha = _lib.SPC_ACT_NONE, 0.0
         if epilogue is not None:
             scale, shift, act, alpha = epilogue
+        precision, tensor_cores = _precision(feats), None
+        plan = _fp32_plan(k_out, c_in, kv) if feats.dtype == torch.float32 and out_dtype == torch.float32 else None
+        if plan is not None:
+            feats = _prepared_rows(feats, plan[0], plan[2])
+            w = _prepared_weight(w, False, plan[1], plan[2])
+            c_in, precision, tensor_cores = plan[2] * c_in, _lib.SPC_PREC_TF32, True
         _lib.check(_lib.load().spc_conv_forward(
-            _lib.ptr(feats), _lib.ptr(w), _lib.ptr(b), _lib.ptr(pf), _lib.ptr(_rowmajor(pair_fwd, feats)), _lib.ptr(order),
-            _lib.ptr(out),
+            _lib.ptr(feats), _lib.ptr(w), _lib.ptr(b), _lib.ptr(pf), _lib.ptr(_rowmajor(pair_fwd, feats, tensor_cores)),
+            _lib.ptr(order), _lib.ptr(out),
             feats.shape[0], n_out, c_in, k_out, kv, _lib.dtype_code(feats.dtype), _lib.dtype_code(out_dtype),
-            _precision(feats), GEMM_PATH, _lib.ptr(scale), _lib.ptr(shift), int(act), float(alpha),
+            precision, GEMM_PATH, _lib.ptr(scale), _lib.ptr(shift), int(act), float(alpha),
             _lib.current_stream(dev)))
     return out
 
@@ -110,6 +174,16 @@ def conv_backward_input(grad_out, filters_krsc, pair_bwd, n_in, pair_mask=None, 
             w = w.to(g.dtype)
         pb = pair_bwd if pair_bwd.is_contiguous() else pair_bwd.contiguous()
         order = _order(kv, pair_mask, mask_argsort)
+        plan = _fp32_plan(c_in, k_out, kv) if g.dtype == torch.float32 else None
+        if plan is not None:
+            # the input gradient as a forward convolution of grad_out with the transposed weight
+            gp = _prepared_rows(g, plan[0], plan[2])
+            wt = _prepared_weight(w, True, plan[1], plan[2])
+            _lib.check(_lib.load().spc_conv_forward(
+                _lib.ptr(gp), _lib.ptr(wt), None, _lib.ptr(pb), _lib.ptr(_rowmajor(pair_bwd, g, True)), _lib.ptr(order),
+                _lib.ptr(din), g.shape[0], n_in, plan[2] * k_out, c_in, kv, _lib.SPC_F32, _lib.SPC_F32,
+                _lib.SPC_PREC_TF32, GEMM_PATH, None, None, _lib.SPC_ACT_NONE, 0.0, _lib.current_stream(dev)))
+            return din
         _lib.check(_lib.load().spc_conv_backward_input(
             _lib.ptr(g), _lib.ptr(w), _lib.ptr(pb), _lib.ptr(_rowmajor(pair_bwd, g)), _lib.ptr(order), _lib.ptr(din), n_in, g.shape[0], c_in,
             k_out, kv, _lib.dtype_code(g.dtype), _precision(g), GEMM_PATH, _lib.current_stream(dev)))

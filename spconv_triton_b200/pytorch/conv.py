@@ -486,5 +486,8 @@ for _nd in (1, 2, 3, 4):
         globals()[_cls_name] = _leaf(_cls_name, _nd, _flavour)
 del _nd, _prefix, _flavour, _cls_name
 
+DEFAULT_SPARSE_CONV_TYPES = {globals()[f"{p}{d}d"] for p in ("SubMConv", "SparseConv", "SparseInverseConv",
+                                                              "SparseConvTranspose") for d in (1, 2, 3, 4)}
+
 __all__ = ["SparseConvolution", "SparseConvolutionBase"] + [
     f"{p}{d}d" for p in ("SparseConv", "SparseConvTranspose", "SparseInverseConv", "SubMConv") for d in (1, 2, 3, 4)]

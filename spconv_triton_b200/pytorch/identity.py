@@ -9,3 +9,6 @@ class Identity(nn.Module):
 
     def forward(self, input):
         return input
+
+    def input_spatial_size(self, out_size):
+        return out_size

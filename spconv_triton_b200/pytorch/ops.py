@@ -26,6 +26,7 @@ from ._impl import pairs as _pairs
 from ._impl import pool as _pool
 from ._impl.pairs import get_conv_output_size, get_deconv_output_size
 from .core import ThrustSortAllocator
+from .cppcore import get_current_stream  # noqa: F401
 
 INT32_MAX = 2147483647
 DEBUG = False
