@@ -38,7 +38,8 @@ typedef enum {
   SPC_ERR_HASH_TABLE_FULL = 4,
   SPC_ERR_UNSUPPORTED = 5,
   SPC_ERR_DEVICE_WAIT_EXPIRED = 6,
-  SPC_ERR_SIZE_LIMIT = 7
+  SPC_ERR_SIZE_LIMIT = 7,
+  SPC_ERR_POINTS_VANISHED = 8
 } spc_status;
 
 typedef enum { SPC_F16 = 0, SPC_BF16 = 1, SPC_F32 = 2, SPC_F64 = 3 } spc_dtype;
@@ -421,6 +422,64 @@ int spc_avgpool_forward(const void* features, const int32_t* pair_fwd, void* out
 int spc_avgpool_backward(const void* grad_out, const int32_t* pair_bwd, const int32_t* count,
                          void* din, int64_t n_in, int channels, int kv, int dtype,
                          void* stream);
+
+/* ---- a chain of convolutions in one call --------------------------------- */
+
+/* One layer of spc_sequence_forward: a sparse convolution with kernel volume <= 32
+ * (the implicit-gemm algorithm), optionally followed by a folded inference
+ * BatchNorm (scale / shift) and an activation, as spc_conv_forward applies them.
+ * `rulebook` is the index of the layer whose rulebook this layer uses: its own
+ * index if it generates one; the index of an earlier SUBMANIFOLD layer of the
+ * same level to share that one (the reference's indice_key reuse,
+ * spconv_triton/pytorch/conv.py:211-219). */
+typedef struct {
+  spc_geometry geom;
+  int32_t rulebook;
+  int32_t c_in, c_out;
+  const void* weight;   /* [c_out, kv, c_in], dtype of the features */
+  const void* bias;     /* [c_out] or NULL */
+  const float* scale;   /* [c_out] fp32 or NULL (with shift) */
+  const float* shift;
+  int32_t act;          /* spc_activation */
+  float act_alpha;
+} spc_seq_layer;
+
+/* What a layer produced: row counts and byte offsets into the arena
+ * (UINT64_MAX = not produced: a layer that shares a rulebook has only
+ * `features`; submanifold layers have no out_indices). */
+typedef struct {
+  int64_t n_in, n_out;
+  uint64_t workspace, workspace_bytes;   /* rulebook workspace, as spc_rulebook_prepare left it */
+  uint64_t out_indices;                  /* [n_out, ndim+1] int32 */
+  uint64_t pair_fwd;                     /* [kv, n_out] int32 */
+  uint64_t pair_fwd_rowmajor;            /* [n_out, kvp] int32 */
+  uint64_t pair_mask;                    /* [n_out] int32 (one split, one word) */
+  uint64_t mask_argsort;                 /* [n_out] int32 */
+  uint64_t num_per_loc;                  /* [kv] int32, zeros (as igemm_pairs returns) */
+  uint64_t features;                     /* [n_out, c_out], dtype */
+} spc_seq_result;
+
+/* Inference forward of `n_layers` convolutions applied one after the other to
+ * (indices [n_in, ndim+1], features [n_in, layers[0].c_in]); replaces the
+ * layer-by-layer loop of SparseSequential.forward
+ * (spconv_triton/pytorch/modules.py:30-100) over ops.get_indice_pairs_implicit_gemm
+ * and ops.implicit_gemm for such a chain.  Every output, table and workspace is
+ * placed in `arena` (256-byte aligned device memory owned by the caller, which
+ * must stay alive while the results are used); `results[i]` says where.
+ * Rulebooks of strided layers are generated on `stream_chain`, those of
+ * submanifold layers on `stream_side`, the GEMMs on `stream_main`, ordered by
+ * events; on return `stream_main` has been made to wait for both other streams.
+ * The call blocks on `stream_chain` once per strided layer (the read of its
+ * output count, as _impl/pairs.py:209 does).
+ * Returns SPC_ERR_WORKSPACE_TOO_SMALL with *arena_needed set to a larger size to
+ * retry with when the arena is too small (nothing useful has been produced
+ * then), SPC_ERR_POINTS_VANISHED when a layer has no output rows.
+ * 16-bit features only; the input-side tables of strided layers are not built
+ * (spc_rulebook_igemm_backward builds them from results[i].workspace). */
+int spc_sequence_forward(const spc_seq_layer* layers, int n_layers, const int32_t* indices,
+                         const void* features, int64_t n_in, int dtype, void* arena,
+                         size_t arena_bytes, size_t* arena_needed, spc_seq_result* results,
+                         void* stream_main, void* stream_chain, void* stream_side);
 
 #ifdef __cplusplus
 }

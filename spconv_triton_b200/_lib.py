@@ -69,6 +69,7 @@ _PROTOTYPES = {
     "spc_check_device_status": (c_int, [_P]),
     "spc_post_device_status": (c_int, [_P, _P]),
     "spc_tf32_prepare": (c_int, [_P, _P, c_int64, c_int, c_int, _P]),
+    "spc_sequence_forward": (c_int, [_P, c_int, _P, _P, c_int64, c_int, _P, c_size_t, _P, _P, _P, _P, _P]),
     "spc_tf32_prepare_weight": (c_int, [_P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "spc_conv_output_size": (c_int, [c_int, POINTER(c_int32), POINTER(c_int32), POINTER(c_int32),
                                      POINTER(c_int32), POINTER(c_int32), POINTER(c_int32)]),

@@ -9,6 +9,7 @@ Read by this package:
   SPCONV_ALLOW_TF32                 live switch: fp32 GEMMs use TF32 tensor cores
   SPCONV_FOLD_BN_RELU (env)         fold inference BatchNorm + ReLU into the conv kernel
   SPCONV_RULEBOOK_RUNAHEAD (env)    build the next layer's rulebook beside the current GEMM
+  SPCONV_NATIVE_SEQUENCE (env)      run an inference SparseSequential of convolutions as one library call
   SPCONV_ALLOW_FP16_ACCUM (env)     accepted; 16-bit GEMMs always accumulate in
                                     fp32 on B200 (full rate, more accurate)
 Everything else is kept only so that ``from ...constants import X`` works.
@@ -37,6 +38,10 @@ SPCONV_FOLD_BN_RELU = os.getenv("SPCONV_FOLD_BN_RELU", "1") == "1"
 # a second CUDA stream while the GEMM of the current layer runs (same results).
 # Read at call time.
 SPCONV_RULEBOOK_RUNAHEAD = os.getenv("SPCONV_RULEBOOK_RUNAHEAD", "1") == "1"
+# Not in the reference.  An inference pass of a SparseSequential made only of implicit-gemm
+# convolutions (+ BatchNorm1d + ReLU) runs as one call into the library (pytorch/sequence.py)
+# instead of layer by layer from Python; same kernels and results.  Read at call time.
+SPCONV_NATIVE_SEQUENCE = os.getenv("SPCONV_NATIVE_SEQUENCE", "1") == "1"
 NDIM_DONT_CARE = 3
 
 ALL_WEIGHT_IS_KRSC = True

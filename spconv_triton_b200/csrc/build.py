@@ -17,7 +17,7 @@ from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-SOURCES = ["capi.cu", "rulebook.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_tma.cu", "gemm_wgrad_tc.cu", "gemm.cu", "pool.cu", "voxelize.cu", "dense.cu", "hash.cu", "global_pool.cu", "from_dense.cu", "tf32_prep.cu"]
+SOURCES = ["capi.cu", "rulebook.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_tma.cu", "gemm_wgrad_tc.cu", "gemm.cu", "pool.cu", "voxelize.cu", "dense.cu", "hash.cu", "global_pool.cu", "from_dense.cu", "tf32_prep.cu", "sequence.cu"]
 LIB = HERE / "libspconv_b200.so"
 STAMP = HERE / "build" / "sources.sha256"
 

@@ -77,6 +77,14 @@ class SparseSequential(SparseModule):
         if isinstance(x, SparseConvTensor) and x.features.is_cuda and not getattr(_depth, "n", 0):
             device = x.features.device
             _lib.raise_posted_status(device)
+        if isinstance(x, SparseConvTensor) and getattr(x, "_planner", None) is None:
+            from . import sequence
+
+            done = sequence.forward(self, x)  # the whole pass as one library call, where it applies
+            if done is not None:
+                if device is not None:
+                    _lib.post_device_status(device)
+                return done
         _depth.n = getattr(_depth, "n", 0) + 1
         entered, owned = x, runahead.begin(self, x)
         try:
