@@ -22,6 +22,7 @@
 
 #include "common.cuh"
 #include "gemm_internal.cuh"
+#include "rulebook_internal.cuh"
 
 namespace spc {
 namespace {
@@ -863,6 +864,11 @@ struct Layout {
   size_t off_words, off_keys_a, off_keys_b, off_vals_a, off_vals_b, off_cub, off_native;
   size_t cub_bytes, total;
   size_t off_bitmap, bitmap_bytes;  // occupancy bitmap of the input grid (0 bytes: not used)
+  // Chained rulebooks: the input rows are exactly the output rows of an earlier strided layer whose
+  // output bitmap and prefix (in ITS workspace) then serve as this layer's input bitmap; rows are
+  // ranks by construction, and no input hash table is built.
+  const uint32_t* shared_bits = nullptr;
+  const uint32_t* shared_prefix = nullptr;
 };
 
 uint32_t pow2_at_least(int64_t v) {
@@ -1009,6 +1015,11 @@ Table<K64> tin_at(char* ws, const Layout& L);
 template <>
 Table<false> tin_at<false>(char* ws, const Layout& L) {
   Table<false> t = table_at<false>(ws, L.off_tin, L.off_tin_vals, L.cap_in);
+  if (L.shared_bits != nullptr) {
+    t.obits = const_cast<uint32_t*>(L.shared_bits);
+    t.oprefix = L.shared_prefix;
+    return t;  // `unsorted` stays null: the rows are the ranks
+  }
   if (L.bitmap_bytes) {
     t.obits = reinterpret_cast<uint32_t*>(ws + L.off_bitmap);
     t.oprefix = reinterpret_cast<const uint32_t*>(ws + L.off_iprefix);
@@ -1051,10 +1062,13 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
   // device status word, which the host reads at its next synchronisation point.
   int* dev_status = device_status_ptr();
   SPC_CUDA_OK(cudaMemsetAsync(counters, 0, 256, st));
-  SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin, 0xFF, static_cast<size_t>(L.cap_in) * 8, st));
-  if (K64) SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin_vals, 0x7F, static_cast<size_t>(L.cap_in) * 4, st));
+  const bool chained = L.shared_bits != nullptr;  // input bitmap and prefix exist already, no input table
+  if (!chained) {
+    SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin, 0xFF, static_cast<size_t>(L.cap_in) * 8, st));
+    if (K64) SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin_vals, 0x7F, static_cast<size_t>(L.cap_in) * 4, st));
+  }
   Table<K64> tin = tin_at<K64>(ws, L);
-  uint32_t* bitmap = L.bitmap_bytes ? reinterpret_cast<uint32_t*>(ws + L.off_bitmap) : nullptr;
+  uint32_t* bitmap = (L.bitmap_bytes && !chained) ? reinterpret_cast<uint32_t*>(ws + L.off_bitmap) : nullptr;
   if (bitmap != nullptr) {
     SPC_CUDA_OK(cudaMemsetAsync(bitmap, 0, L.bitmap_bytes, st));
     mark_inputs_kernel<ND><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, bitmap, counters, dev_status);
@@ -1066,9 +1080,11 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
     size_t scan_bytes = L.scan_bytes;
     SPC_CUDA_OK(cub::DeviceScan::ExclusiveSum(ws + L.off_scan, scan_bytes, iprefix, iprefix, static_cast<int>(words), st));
   }
-  insert_inputs_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, tin, counters, bitmap,
-                                                                       dev_status);
-  SPC_LAUNCH_OK();
+  if (!chained) {
+    insert_inputs_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, tin, counters, bitmap,
+                                                                         dev_status);
+    SPC_LAUNCH_OK();
+  }
   if (g.subm) {
     *n_out_host = n_in;
     return SPC_OK;
@@ -1198,7 +1214,8 @@ int igemm_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, 
   Table<K64> tout = tout_at<K64>(ws, L);
   const key_t* sorted = reinterpret_cast<const key_t*>(ws + L.off_sorted);
   uint32_t* words = reinterpret_cast<uint32_t*>(ws + L.off_words);
-  const uint32_t* bitmap = L.bitmap_bytes ? reinterpret_cast<const uint32_t*>(ws + L.off_bitmap) : nullptr;
+  const uint32_t* bitmap = L.shared_bits != nullptr ? L.shared_bits
+                           : (L.bitmap_bytes ? reinterpret_cast<const uint32_t*>(ws + L.off_bitmap) : nullptr);
   if (g.subm && pair_bwd != nullptr)
     fill_fwd_kernel<ND, K64, true><<<blocks_for(n_out), kThreads, 0, st>>>(
         g, idx, sorted, n_out, tin, out_indices, pair_fwd, pair_bwd, words, L.mic, fwd_rm, bwd_rm, kvp, bitmap);
@@ -1265,7 +1282,72 @@ int dispatch(int ndim, bool k64, F&& f) {
   }
 }
 
+// Points `L` at the output bitmap of `producer` if that strided layer numbered its outputs through
+// one and its output grid is this layer's input grid.
+void adopt_producer_bits(const Geo& g, Layout* L, const RulebookProducer* producer) {
+  if (producer == nullptr || producer->geom == nullptr || producer->workspace == nullptr || L->k64 ||
+      L->bitmap_bytes == 0)
+    return;
+  Geo gp;
+  if (!make_geo(producer->geom, &gp) || gp.subm || gp.ndim != g.ndim || gp.batch != g.batch) return;
+  for (int d = 0; d < g.ndim; ++d)
+    if (gp.out_shape[d] != g.in_shape[d]) return;
+  const Layout Lp = make_layout(gp, producer->n_in);
+  if (Lp.obits_words == 0) return;
+  const char* wp = static_cast<const char*>(producer->workspace);
+  L->shared_bits = reinterpret_cast<const uint32_t*>(wp + Lp.off_obits);
+  L->shared_prefix = reinterpret_cast<const uint32_t*>(wp + Lp.off_oprefix);
+}
+
 }  // namespace
+
+int rulebook_prepare_chained(const spc_geometry* sg, const int32_t* indices, int64_t n_in, void* workspace,
+                             size_t workspace_bytes, int64_t* n_out_host, const RulebookProducer* producer,
+                             cudaStream_t st) {
+  Geo g;
+  if (!make_geo(sg, &g)) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: bad geometry");
+  if (n_in <= 0 || indices == nullptr || n_out_host == nullptr || workspace == nullptr)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: n_in must be > 0 and pointers non-null");
+  if (n_in >= (1ll << 30)) return fail(SPC_ERR_SIZE_LIMIT, "rulebook: n_in %lld too large", (long long)n_in);
+  Layout L = make_layout(g, n_in);
+  if (workspace_bytes < L.total)
+    return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "rulebook: workspace %zu < %zu bytes", workspace_bytes, L.total);
+  adopt_producer_bits(g, &L, producer);
+  char* ws = static_cast<char*>(workspace);
+  return dispatch(g.ndim, L.k64, [&](auto nd, auto k64) {
+    return prepare_impl<decltype(nd)::value, decltype(k64)::value>(g, L, indices, n_in, ws, n_out_host, st);
+  });
+}
+
+int rulebook_igemm_chained(const spc_geometry* sg, const int32_t* indices, int64_t n_in, int64_t n_out,
+                           void* workspace, size_t workspace_bytes, int32_t* out_indices, int32_t* pair_fwd,
+                           int32_t* pair_bwd, int32_t* mask_fwd, int32_t* argsort_fwd, int32_t* mask_bwd,
+                           int32_t* argsort_bwd, const uint32_t* split_masks, int n_split, int do_sort,
+                           int32_t* pair_fwd_rowmajor, int32_t* pair_bwd_rowmajor, const RulebookProducer* producer,
+                           cudaStream_t st) {
+  Geo g;
+  if (!make_geo(sg, &g)) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: bad geometry");
+  if (n_in <= 0 || n_out <= 0 || !indices || !workspace || !pair_fwd || !mask_fwd || !argsort_fwd ||
+      !split_masks || n_split < 1 || n_split > 2)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: bad arguments");
+  if (!g.subm && out_indices == nullptr)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: out_indices required for non-subm layers");
+  if (g.subm && n_out != n_in) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: subm needs n_out == n_in");
+  if ((mask_bwd == nullptr) != (argsort_bwd == nullptr))
+    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: mask_bwd and argsort_bwd go together");
+  Layout L = make_layout(g, n_in);
+  if (workspace_bytes < L.total)
+    return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "rulebook: workspace %zu < %zu bytes", workspace_bytes, L.total);
+  if (n_out > L.bound) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: n_out exceeds prepared bound");
+  adopt_producer_bits(g, &L, producer);
+  char* ws = static_cast<char*>(workspace);
+  return dispatch(g.ndim, L.k64, [&](auto nd, auto k64) {
+    return igemm_impl<decltype(nd)::value, decltype(k64)::value>(
+        g, L, indices, n_in, n_out, ws, out_indices, pair_fwd, pair_bwd, mask_fwd, argsort_fwd, mask_bwd,
+        argsort_bwd, split_masks, n_split, do_sort, pair_fwd_rowmajor, pair_bwd_rowmajor, st);
+  });
+}
+
 }  // namespace spc
 
 using namespace spc;
@@ -1279,19 +1361,8 @@ extern "C" size_t spc_rulebook_workspace_bytes(const spc_geometry* sg, int64_t n
 extern "C" int spc_rulebook_prepare(const spc_geometry* sg, const int32_t* indices, int64_t n_in,
                                     void* workspace, size_t workspace_bytes, int64_t* n_out_host,
                                     void* stream) {
-  Geo g;
-  if (!make_geo(sg, &g)) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: bad geometry");
-  if (n_in <= 0 || indices == nullptr || n_out_host == nullptr || workspace == nullptr)
-    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: n_in must be > 0 and pointers non-null");
-  if (n_in >= (1ll << 30)) return fail(SPC_ERR_SIZE_LIMIT, "rulebook: n_in %lld too large", (long long)n_in);
-  const Layout L = make_layout(g, n_in);
-  if (workspace_bytes < L.total)
-    return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "rulebook: workspace %zu < %zu bytes", workspace_bytes, L.total);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  char* ws = static_cast<char*>(workspace);
-  return dispatch(g.ndim, L.k64, [&](auto nd, auto k64) {
-    return prepare_impl<decltype(nd)::value, decltype(k64)::value>(g, L, indices, n_in, ws, n_out_host, st);
-  });
+  return rulebook_prepare_chained(sg, indices, n_in, workspace, workspace_bytes, n_out_host, nullptr,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int spc_rulebook_igemm(const spc_geometry* sg, const int32_t* indices, int64_t n_in,
@@ -1301,27 +1372,9 @@ extern "C" int spc_rulebook_igemm(const spc_geometry* sg, const int32_t* indices
                                   int32_t* argsort_bwd, const uint32_t* split_masks, int n_split,
                                   int do_sort, int32_t* pair_fwd_rowmajor, int32_t* pair_bwd_rowmajor,
                                   void* stream) {
-  Geo g;
-  if (!make_geo(sg, &g)) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: bad geometry");
-  if (n_in <= 0 || n_out <= 0 || !indices || !workspace || !pair_fwd || !mask_fwd || !argsort_fwd ||
-      !split_masks || n_split < 1 || n_split > 2)
-    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: bad arguments");
-  if (!g.subm && out_indices == nullptr)
-    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: out_indices required for non-subm layers");
-  if (g.subm && n_out != n_in) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: subm needs n_out == n_in");
-  if ((mask_bwd == nullptr) != (argsort_bwd == nullptr))
-    return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: mask_bwd and argsort_bwd go together");
-  const Layout L = make_layout(g, n_in);
-  if (workspace_bytes < L.total)
-    return fail(SPC_ERR_WORKSPACE_TOO_SMALL, "rulebook: workspace %zu < %zu bytes", workspace_bytes, L.total);
-  if (n_out > L.bound) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: n_out exceeds prepared bound");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  char* ws = static_cast<char*>(workspace);
-  return dispatch(g.ndim, L.k64, [&](auto nd, auto k64) {
-    return igemm_impl<decltype(nd)::value, decltype(k64)::value>(
-        g, L, indices, n_in, n_out, ws, out_indices, pair_fwd, pair_bwd, mask_fwd, argsort_fwd, mask_bwd,
-        argsort_bwd, split_masks, n_split, do_sort, pair_fwd_rowmajor, pair_bwd_rowmajor, st);
-  });
+  return rulebook_igemm_chained(sg, indices, n_in, n_out, workspace, workspace_bytes, out_indices, pair_fwd, pair_bwd,
+                                mask_fwd, argsort_fwd, mask_bwd, argsort_bwd, split_masks, n_split, do_sort,
+                                pair_fwd_rowmajor, pair_bwd_rowmajor, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int spc_rulebook_igemm_backward(const spc_geometry* sg, const int32_t* indices, int64_t n_in,

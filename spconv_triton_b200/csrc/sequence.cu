@@ -23,6 +23,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "rulebook_internal.cuh"
 
 using namespace spc;
 
@@ -98,6 +99,10 @@ extern "C" int spc_sequence_forward(const spc_seq_layer* layers, int n_layers, c
   cudaEvent_t cur_indices_ready = ev_input;
   const void* cur_features = features;
   int cur_channels = layers[0].c_in;
+  // the strided layer that produced the current level's coordinates: its output bitmap doubles as
+  // the input bitmap of every rulebook generated from them
+  RulebookProducer producer{nullptr, nullptr, 0};
+  bool have_producer = false;
 
   for (int i = 0; i < n_layers; ++i) {
     const spc_seq_layer& L = layers[i];
@@ -122,7 +127,8 @@ extern "C" int spc_sequence_forward(const spc_seq_layer* layers, int n_layers, c
       R.workspace_bytes = ws_bytes;
       if (arena.overflow) break;
       int64_t n_out = 0;
-      rc = spc_rulebook_prepare(&L.geom, cur_indices, cur_n, arena.at(R.workspace), ws_bytes, &n_out, st);
+      rc = rulebook_prepare_chained(&L.geom, cur_indices, cur_n, arena.at(R.workspace), ws_bytes, &n_out,
+                                    have_producer ? &producer : nullptr, st);
       if (rc != SPC_OK) return rc;
       R.n_out = n_out;
       if (n_out == 0) return fail(SPC_ERR_POINTS_VANISHED, "sequence_forward: layer %d has no output points", i);
@@ -134,15 +140,18 @@ extern "C" int spc_sequence_forward(const spc_seq_layer* layers, int n_layers, c
       R.num_per_loc = arena.take(static_cast<size_t>(kv) * 4);
       if (arena.overflow) break;
       SPC_CUDA_OK(cudaMemsetAsync(arena.at(R.num_per_loc), 0, static_cast<size_t>(kv) * 4, st));
-      rc = spc_rulebook_igemm(&L.geom, cur_indices, cur_n, n_out, arena.at(R.workspace), ws_bytes,
-                              subm ? nullptr : static_cast<int32_t*>(arena.at(R.out_indices)),
-                              static_cast<int32_t*>(arena.at(R.pair_fwd)), nullptr,
-                              static_cast<int32_t*>(arena.at(R.pair_mask)), static_cast<int32_t*>(arena.at(R.mask_argsort)),
-                              nullptr, nullptr, &split_word, 1, /*do_sort=*/1,
-                              static_cast<int32_t*>(arena.at(R.pair_fwd_rowmajor)), nullptr, st);
+      rc = rulebook_igemm_chained(&L.geom, cur_indices, cur_n, n_out, arena.at(R.workspace), ws_bytes,
+                                  subm ? nullptr : static_cast<int32_t*>(arena.at(R.out_indices)),
+                                  static_cast<int32_t*>(arena.at(R.pair_fwd)), nullptr,
+                                  static_cast<int32_t*>(arena.at(R.pair_mask)),
+                                  static_cast<int32_t*>(arena.at(R.mask_argsort)), nullptr, nullptr, &split_word, 1,
+                                  /*do_sort=*/1, static_cast<int32_t*>(arena.at(R.pair_fwd_rowmajor)), nullptr,
+                                  have_producer ? &producer : nullptr, st);
       if (rc != SPC_OK) return rc;
       SPC_CUDA_OK(cudaEventRecord(ev[i], st));
       if (!subm) {
+        producer = RulebookProducer{&L.geom, arena.at(R.workspace), cur_n};
+        have_producer = true;
         cur_indices = static_cast<const int32_t*>(arena.at(R.out_indices));
         cur_n = n_out;
         cur_indices_ready = ev[i];
