@@ -592,19 +592,11 @@ def run_backbone_reference_gpu(dev, steps, warmup):
 
 
 def blob_scene(seed, batch, n_per_sample, grid=256):
-    """Dense-ish random blobs (BASELINE configs[4]): union of Gaussian blobs in a
-    grid^3 volume, n_per_sample unique voxels per sample."""
-    rng = np.random.default_rng(seed)
-    rows = []
-    for b in range(batch):
-        pts = np.zeros((0, 3), dtype=np.int64)
-        while pts.shape[0] < n_per_sample:
-            centres = rng.integers(grid // 8, grid - grid // 8, size=(64, 3))
-            new = np.concatenate([c + np.rint(rng.standard_normal((12000, 3)) * grid / 24) for c in centres])
-            pts = np.unique(np.concatenate([pts, np.clip(new, 0, grid - 1).astype(np.int64)]), axis=0)
-        pts = pts[rng.permutation(pts.shape[0])[:n_per_sample]]
-        rows.append(np.concatenate([np.full((n_per_sample, 1), b), pts], 1))
-    return torch.from_numpy(np.concatenate(rows).astype(np.int32))
+    """Dense-ish random blobs (BASELINE configs[4]): n_per_sample unique voxels per sample filling
+    random solid blobs of a grid^3 volume to 30 % occupancy."""
+    from spconv_triton_b200.scenes import blob_batch
+
+    return torch.from_numpy(blob_batch(seed, batch, n_per_sample, grid, 0.3))
 
 
 def run_op_bench(args):
@@ -692,7 +684,7 @@ def run_op_bench(args):
         return
     if args.op == "pool":
         batch, c = 4, 256
-        idx = blob_scene(7, batch, 400000)
+        idx = blob_scene(7, batch, args.pool_voxels)
         if args.voxel_order == "sorted":   # the order every rulebook of this library emits its outputs in
             key = ((idx[:, 0].long() * 256 + idx[:, 1]) * 256 + idx[:, 2]) * 256 + idx[:, 3]
             idx = idx[torch.argsort(key)]
@@ -885,6 +877,7 @@ def main():
                              "backbone_reference_gpu", "voxelize", "dense", "sparse_add", "global_pool", "from_dense"],
                     help="single-operator timings at the other configurations instead of the headline benchmark")
     ap.add_argument("--k5-voxels", type=int, default=400000, help="--op conv_k5: voxels per sample (4 samples)")
+    ap.add_argument("--pool-voxels", type=int, default=400000, help="--op pool: voxels per sample (4 samples)")
     ap.add_argument("--no-train", action="store_true",
                     help="skip the training-step record (BASELINE configs[3]) that follows the headline measurement")
     ap.add_argument("--voxel-order", default="random", choices=["random", "sorted"],

@@ -333,6 +333,19 @@ int spc_conv_forward(const void* features, const void* weight, const void* bias,
                      int out_dtype, int precision, int path, const float* out_scale,
                      const float* out_shift, int act, float act_alpha, void* stream);
 
+/* spc_conv_forward with a residual connection fused into the store:
+ *   out[m, n] = act((acc + bias[n]) * scale[n] + shift[n]) + residual[m, n]
+ * residual [n_out, c_out] has the OUTPUT dtype (16-byte aligned, NULL = none) and is
+ * added in fp32 before the single rounding of the store.  Replaces the separate
+ * pass the reference makes for `add_input` after its kernel
+ * (spconv_triton/pytorch/conv.py:503-511). */
+int spc_conv_forward_residual(const void* features, const void* weight, const void* bias,
+                              const int32_t* pair_fwd, const int32_t* pair_fwd_rowmajor,
+                              const int32_t* mask_argsort, void* out, int64_t n_in, int64_t n_out,
+                              int c_in, int c_out, int kv, int dtype, int out_dtype, int precision,
+                              int path, const float* out_scale, const float* out_shift, int act,
+                              float act_alpha, const void* residual, void* stream);
+
 /* Input gradient: replaces conv_backward_input, _impl/gemm.py:571-631.
  *   din[j, c] = sum_k sum_n grad_out[pair_bwd[k, j], n] * weight[n, k, c]
  *   grad_out [n_out, c_out]; din [n_in, c_in], both `dtype`. */

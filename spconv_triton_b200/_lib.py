@@ -108,6 +108,8 @@ _PROTOTYPES = {
     "spc_native_to_tables": (c_int, [_P, c_int, c_int64, c_int, _P, c_int64, _P, c_int64, _P]),
     "spc_conv_forward": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, _P, _P, c_int, ctypes.c_float, _P]),
+    "spc_conv_forward_residual": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int,
+                                          c_int, c_int, c_int, _P, _P, c_int, ctypes.c_float, _P, _P]),
     "spc_conv_backward_input": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int,
                                         c_int, c_int, _P]),
     "spc_conv_backward_weight_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int]),

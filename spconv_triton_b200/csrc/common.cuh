@@ -80,15 +80,18 @@ inline cudaError_t ensure_dynamic_smem(Kernel kernel, int bytes, bool (&done)[kM
 }
 
 // What happens to an accumulator row before it is stored:
-//   v = acc (+ bias[n]);  v = v * scale[n] + shift[n] (if scale);  v = act(v)
+//   v = acc (+ bias[n]);  v = v * scale[n] + shift[n] (if scale);  v = act(v);  v += residual[row, n]
 // bias has the dtype of the inputs; scale and shift are fp32 (a folded
-// inference BatchNorm); act is an spc_activation.
+// inference BatchNorm); act is an spc_activation; residual is a row-major
+// [rows, n_dim] matrix of the OUTPUT dtype, added in fp32 before the one rounding
+// of the store (a residual connection fused into the convolution).
 struct Epilogue {
   const void* bias = nullptr;
   const float* scale = nullptr;
   const float* shift = nullptr;
   int act = 0;
   float alpha = 0.f;
+  const void* residual = nullptr;
 };
 
 inline size_t dtype_size(int dtype) {
@@ -123,6 +126,33 @@ template <>
 __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// residual[row, n .. n + 16) added to 16 consecutive accumulators (16-byte loads).
+template <typename TO>
+__device__ __forceinline__ void add_residual16(float* v, const TO* r) {
+  if constexpr (sizeof(TO) == 4) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(r) + q);
+      v[4 * q] += a.x; v[4 * q + 1] += a.y; v[4 * q + 2] += a.z; v[4 * q + 3] += a.w;
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const uint4 a = __ldg(reinterpret_cast<const uint4*>(r) + q);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        TO lo, hi;
+        const unsigned short l16 = static_cast<unsigned short>(w[t] & 0xffffu), h16 = static_cast<unsigned short>(w[t] >> 16);
+        lo = *reinterpret_cast<const TO*>(&l16);
+        hi = *reinterpret_cast<const TO*>(&h16);
+        v[8 * q + 2 * t] += to_float(lo);
+        v[8 * q + 2 * t + 1] += to_float(hi);
+      }
+    }
+  }
+}
 
 template <typename T>
 __device__ __forceinline__ float apply_epilogue(float v, const Epilogue& e, int n) {

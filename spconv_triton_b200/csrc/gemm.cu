@@ -32,6 +32,17 @@ extern "C" int spc_conv_forward(const void* features, const void* weight, const 
                                 int64_t n_in, int64_t n_out, int c_in, int c_out, int kv, int dtype,
                                 int out_dtype, int precision, int path, const float* out_scale,
                                 const float* out_shift, int act, float act_alpha, void* stream) {
+  return spc_conv_forward_residual(features, weight, bias, pair_fwd, pair_fwd_rowmajor, mask_argsort, out, n_in, n_out,
+                                   c_in, c_out, kv, dtype, out_dtype, precision, path, out_scale, out_shift, act,
+                                   act_alpha, nullptr, stream);
+}
+
+extern "C" int spc_conv_forward_residual(const void* features, const void* weight, const void* bias,
+                                         const int32_t* pair_fwd, const int32_t* pair_fwd_rowmajor,
+                                         const int32_t* mask_argsort, void* out, int64_t n_in, int64_t n_out,
+                                         int c_in, int c_out, int kv, int dtype, int out_dtype, int precision,
+                                         int path, const float* out_scale, const float* out_shift, int act,
+                                         float act_alpha, const void* residual, void* stream) {
   if (!features || !weight || !pair_fwd || !out || n_in < 0 || n_out < 0 || c_in <= 0 || c_out <= 0 || kv <= 0)
     return fail(SPC_ERR_INVALID_ARGUMENT, "conv_forward: bad arguments");
   if ((out_scale == nullptr) != (out_shift == nullptr))
@@ -40,6 +51,9 @@ extern "C" int spc_conv_forward(const void* features, const void* weight, const 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Epilogue epi;
   epi.bias = bias; epi.scale = out_scale; epi.shift = out_shift; epi.act = act; epi.alpha = act_alpha;
+  epi.residual = residual;
+  if (residual != nullptr && (reinterpret_cast<uintptr_t>(residual) & 15u) != 0)
+    return fail(SPC_ERR_INVALID_ARGUMENT, "conv_forward: the residual must be 16-byte aligned");
   int status;
   if (want_tc(path, c_out, c_in, kv, dtype, out_dtype, precision, false, &status)) {
     if (path != SPC_GEMM_TCGEN05_CPASYNC &&

@@ -117,7 +117,9 @@ gather_gemm_simt_kernel(const T* __restrict__ src, const T* __restrict__ w, cons
     for (int j = 0; j < TN; ++j) {
       const int n = n0 + tx * TN + j;
       if (n >= n_dim) continue;
-      out[rm * n_dim + n] = from_acc<TO>(apply_epilogue<T>(acc[i][j], epi, n));
+      float v = apply_epilogue<T>(acc[i][j], epi, n);
+      if (epi.residual != nullptr) v += to_float(static_cast<const TO*>(epi.residual)[rm * n_dim + n]);
+      out[rm * n_dim + n] = from_acc<TO>(v);
     }
   }
 }
@@ -272,7 +274,11 @@ gather_gemm_thin_kernel(const T* __restrict__ src, const T* __restrict__ w, cons
   TO* o = out + row * n_dim;
 #pragma unroll
   for (int n = 0; n < NP; ++n)
-    if (n < n_dim) o[n] = from_acc<TO>(apply_epilogue<T>(acc[n], epi, n));
+    if (n < n_dim) {
+      float v = apply_epilogue<T>(acc[n], epi, n);
+      if (epi.residual != nullptr) v += to_float(static_cast<const TO*>(epi.residual)[row * n_dim + n]);
+      o[n] = from_acc<TO>(v);
+    }
 }
 
 template <typename T, typename TO>

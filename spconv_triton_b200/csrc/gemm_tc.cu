@@ -239,7 +239,9 @@ gather_gemm_tc_kernel(const __grid_constant__ TcParams p) {
           for (int q = 0; q < 16; ++q) v[q] = 0.f;
         }
         if (my_row >= 0) {
-if (has_epilogue) finish_epilogue16(v, epi_scale + c0, epi_shift + c0, p.epi.act, p.epi.alpha);
+            if (has_epilogue) finish_epilogue16(v, epi_scale + c0, epi_shift + c0, p.epi.act, p.epi.alpha);
+            if (p.epi.residual != nullptr)
+              add_residual16<TO>(v, static_cast<const TO*>(p.epi.residual) + my_row * p.n_dim + c0);
           store_row16<TO>(out_row + c0, v);
         }
       }

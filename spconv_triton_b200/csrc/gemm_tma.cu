@@ -291,7 +291,9 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
             for (int q = 0; q < 16; ++q) v[q] = 0.f;
           }
           if (my_row >= 0) {
-if (has_epilogue) finish_epilogue16(v, epi_scale + c0, epi_shift + c0, p.epi.act, p.epi.alpha);
+            if (has_epilogue) finish_epilogue16(v, epi_scale + c0, epi_shift + c0, p.epi.act, p.epi.alpha);
+            if (p.epi.residual != nullptr)
+              add_residual16<TO>(v, static_cast<const TO*>(p.epi.residual) + my_row * p.n_dim + c0);
             store_row16<TO>(out_row + c0, v);
           }
         }
@@ -425,7 +427,7 @@ int row_span(int elems, int elem_size) {
 template <typename T, typename TO, bool B_MN>
 int launch_tma(TmaParams p, const CUtensorMap& map_b, size_t smem_bytes, cudaStream_t st) {
   static bool configured[kMaxDevices] = {false};  // per instantiation and device
-  SPC_CUDA_OK(ensure_dynamic_smem(gather_gemm_tma_kernel<T, TO, B_MN>, 200 * 1024, configured));
+  SPC_CUDA_OK(ensure_dynamic_smem(gather_gemm_tma_kernel<T, TO, B_MN>, 226 * 1024, configured));
   const unsigned grid = static_cast<unsigned>(ceil_div(p.m_rows, kTileM));
   gather_gemm_tma_kernel<T, TO, B_MN><<<grid, kThreadsHybrid, smem_bytes, st>>>(p, map_b);
   SPC_LAUNCH_OK();
@@ -490,7 +492,7 @@ int gather_gemm_tma(const void* src, const void* w, const Epilogue& epi, const i
     p.stages = per_cta > fixed ? std::min<int>(kMaxStages, static_cast<int>((per_cta - fixed) / stage_bytes)) : 0;
   }
   // the kernel's dynamic shared memory limit is set to 200 KB
-  while (p.stages > 2 && fixed + static_cast<size_t>(p.stages) * stage_bytes > 200 * 1024) --p.stages;
+  while (p.stages > 2 && fixed + static_cast<size_t>(p.stages) * stage_bytes > 226 * 1024) --p.stages;
   // shared memory is carved out of the L1: beyond two stages, keep about 36 KB of the SM as cache
   // for the table and epilogue traffic (a third stage that took it cost 8 % on 64 -> 128)
   // (layers whose reduction spans several stages per offset keep the deeper pipeline: 128 -> 128

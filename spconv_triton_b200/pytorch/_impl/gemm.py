@@ -108,13 +108,17 @@ def _order(kv, pair_mask, mask_argsort):
 
 
 def conv_forward(features, filters_krsc, pair_fwd, n_out, bias=None, out_dtype=None, pair_mask=None,
-                 mask_argsort=None, fp32_accum=None, epilogue=None):
+                 mask_argsort=None, fp32_accum=None, epilogue=None, residual=None):
     """out [n_out, K] = gather-GEMM of features [N, C] with filters [K, kv, C].
 
     ``epilogue`` (not in the reference): ``(scale, shift, act, alpha)`` applied
     while the rows are stored -- out = act((acc + bias) * scale + shift) with
     fp32 ``scale``/``shift`` of shape [K] (or both None) and ``act`` one of the
     ``_lib.SPC_ACT_*`` codes.
+
+    ``residual`` (not in the reference): a tensor [n_out, K] of the output dtype
+    added to the result while the rows are stored (a residual connection in the
+    same pass; the reference adds ``add_input`` afterwards, conv.py:503-511).
 
     ``fp32_accum`` is accepted for signature parity: 16-bit inputs always
     accumulate in fp32 here, which the reference treats as the accurate
@@ -150,11 +154,15 @@ def conv_forward(features, filters_krsc, pair_fwd, n_out, bias=None, out_dtype=N
             feats = _prepared_rows(feats, plan[0], plan[2])
             w = _prepared_weight(w, False, plan[1], plan[2])
             c_in, precision, tensor_cores = plan[2] * c_in, _lib.SPC_PREC_TF32, True
-        _lib.check(_lib.load().spc_conv_forward(
+        if residual is not None:
+            if residual.shape != out.shape or residual.dtype != out_dtype or residual.device != dev:
+                raise ValueError("residual must have the shape, dtype and device of the output")
+            residual = residual.contiguous()
+        _lib.check(_lib.load().spc_conv_forward_residual(
             _lib.ptr(feats), _lib.ptr(w), _lib.ptr(b), _lib.ptr(pf), _lib.ptr(_rowmajor(pair_fwd, feats, tensor_cores)),
             _lib.ptr(order), _lib.ptr(out),
             feats.shape[0], n_out, c_in, k_out, kv, _lib.dtype_code(feats.dtype), _lib.dtype_code(out_dtype),
-            precision, GEMM_PATH, _lib.ptr(scale), _lib.ptr(shift), int(act), float(alpha),
+            precision, GEMM_PATH, _lib.ptr(scale), _lib.ptr(shift), int(act), float(alpha), _lib.ptr(residual),
             _lib.current_stream(dev)))
     return out
 

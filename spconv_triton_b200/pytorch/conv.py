@@ -262,9 +262,19 @@ class SparseConvolutionBase:
         else:
             pair_fwd, pair_bwd, pm_fwd, pm_bwd, ma_fwd, ma_bwd, masks = rb.igemm
             if training:
+                # a residual input is added inside the kernel's store when nothing comes between the
+                # kernel and the addition (no bias, which training adds after the kernel, no activation)
+                residual = None
+                if (add_input is not None and bias_after is None and self.act_type == _NO_ACT
+                        and add_input.features.shape == (n_out, self.out_channels)
+                        and add_input.features.device == features.device):
+                    out_dt = torch.float16 if torch.is_autocast_enabled() else features.dtype
+                    if add_input.features.dtype == out_dt:
+                        residual, add_input = add_input.features, None
                 out_features = Fsp.implicit_gemm(features, weight, pair_fwd, pair_bwd, pm_fwd, pm_bwd, ma_fwd,
                                                  ma_bwd, n_out, masks, training, self.subm, x._timer,
-                                                 self.fp32_accum, bias_fused, act_alpha, act_beta, act_type)
+                                                 self.fp32_accum, bias_fused, act_alpha, act_beta, act_type,
+                                                 residual)
             else:
                 out_features, _, _ = ops.implicit_gemm(
                     features, weight, pair_fwd, pm_fwd, ma_fwd, n_out, masks, training, self.subm, x._timer,

@@ -69,10 +69,14 @@ class SparseImplicitGemmFunction(Function):
                 mask_argsort_fwd_splits, mask_argsort_bwd_splits, num_activate_out: int,
                 masks: list[np.ndarray], is_train: bool, is_subm: bool, timer: CUDAKernelTimer = _NO_TIMER,
                 fp32_accum: bool | None = None, bias: torch.Tensor | None = None, act_alpha: float = 0.0,
-                act_beta: float = 0.0, act_type=_NO_ACT):
+                act_beta: float = 0.0, act_type=_NO_ACT, residual: torch.Tensor | None = None):
+        # ``residual`` (not in the reference): added to the output inside the kernel's store; its
+        # gradient is the output gradient
         out, mask_out, mask_width = ops.implicit_gemm(
             features, filters, pair_fwd, pair_mask_fwd_splits, mask_argsort_fwd_splits, num_activate_out,
-            masks, is_train, is_subm, timer, fp32_accum, bias, act_alpha, act_beta, act_type)
+            masks, is_train, is_subm, timer, fp32_accum, bias, act_alpha, act_beta, act_type,
+            _residual=residual)
+        ctx.has_residual = residual is not None
         ctx.save_for_backward(features, filters, pair_fwd, pair_bwd)
         ctx.extra = dict(pair_mask_fwd_splits=pair_mask_fwd_splits, pair_mask_bwd_splits=pair_mask_bwd_splits,
                          mask_argsort_fwd_splits=mask_argsort_fwd_splits,
@@ -92,7 +96,7 @@ class SparseImplicitGemmFunction(Function):
             e["pair_mask_bwd_splits"], e["mask_argsort_fwd_splits"], e["mask_argsort_bwd_splits"],
             mask_output_fwd=e["mask_output_fwd"], masks=e["masks"], mask_width=e["mask_width"],
             is_subm=e["is_subm"], timer=e["timer"], fp32_accum=e["fp32_accum"])
-        return (din, dw) + (None,) * 16
+        return (din, dw) + (None,) * 16 + ((grad_output if ctx.has_residual else None),)
 
 
 class SparseMaxPoolFunction(Function):

@@ -162,11 +162,12 @@ def implicit_gemm(features, filters, pair_fwd, pair_mask_fwd_splits, mask_argsor
                   bias: torch.Tensor | None = None, act_alpha: float = 0.0, act_beta: float = 0.0,
                   act_type=_NO_ACT, output_scale: float = 1.0, scale: torch.Tensor | None = None,
                   output_add: torch.Tensor | None = None, output_add_scale: float = 0.0,
-                  output_dtype: torch.dtype | None = None, _bn_fold=None):
+                  output_dtype: torch.dtype | None = None, _bn_fold=None, _residual=None):
     """Implicit-gemm forward -> ``(out, mask_output_fwd, mask_width)``
     (reference: ops.py:259-305).  The activation is applied inside the kernel's
     store; ``_bn_fold = (scale, shift)`` (fp32 [K], not in the reference) folds
-    an inference BatchNorm in front of it."""
+    an inference BatchNorm in front of it; ``_residual`` (not in the reference)
+    is added to the result in the same store."""
     if output_add is not None and features.dtype != torch.qint8:
         raise AssertionError("fused residual add only support int8")
     _reject_int8(features)
@@ -175,7 +176,7 @@ def implicit_gemm(features, filters, pair_fwd, pair_mask_fwd_splits, mask_argsor
     scale, shift = _bn_fold if _bn_fold is not None else (None, None)
     out = _gemm.conv_forward(features, _filters_krsc(filters), pair_fwd, num_activate_out, bias=bias,
                              out_dtype=output_dtype, pair_mask=pm, mask_argsort=ar, fp32_accum=fp32_accum,
-                             epilogue=(scale, shift, _act_code(act_type), float(act_alpha)))
+                             epilogue=(scale, shift, _act_code(act_type), float(act_alpha)), residual=_residual)
     return out, torch.Tensor(), -1
 
 

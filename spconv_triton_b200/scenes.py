@@ -105,3 +105,29 @@ def indoor_like_batch(seed, batch, n_range, grid=(512, 512, 64)):
         c = indoor_like_sample(rng, n, grid)
         rows.append(np.concatenate([np.full((c.shape[0], 1), b, np.int32), c], 1))
     return np.concatenate(rows, 0)
+
+
+def blob_batch(seed, batch, n_per_sample, grid=256, occupancy=0.3):
+    """int32 indices [batch * n_per_sample, 4] (batch, z, y, x): random solid blobs (spheres of radius
+    grid/32 .. grid/10) are placed until they hold n_per_sample / occupancy cells, and
+    ``n_per_sample`` of those cells are kept at random, so that the voxels fill their blobs to
+    ``occupancy`` ("dense-ish ... 30 % occupancy in random blobs").  Rows of a sample are in random order."""
+    rng = np.random.default_rng(seed)
+    rows = []
+    want = int(n_per_sample / occupancy)
+    for b in range(batch):
+        filled = np.zeros((grid, grid, grid), dtype=bool)
+        count = 0
+        while count < want:
+            r = int(rng.integers(max(grid // 32, 3), max(grid // 10, 5)))
+            c = rng.integers(r, grid - r, size=3)
+            ax = np.arange(-r, r + 1)
+            ball = (ax[:, None, None] ** 2 + ax[None, :, None] ** 2 + ax[None, None, :] ** 2) <= r * r
+            view = filled[c[0] - r:c[0] + r + 1, c[1] - r:c[1] + r + 1, c[2] - r:c[2] + r + 1]
+            count += int((ball & ~view).sum())
+            view |= ball
+        cells = np.flatnonzero(filled)
+        keep = cells[rng.permutation(cells.shape[0])[:n_per_sample]]
+        zyx = np.stack(np.unravel_index(keep, filled.shape), 1)
+        rows.append(np.concatenate([np.full((zyx.shape[0], 1), b), zyx], 1))
+    return np.concatenate(rows).astype(np.int32)

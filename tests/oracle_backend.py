@@ -41,7 +41,7 @@ def _native_pair_to_tables(pair, indice_pair_num, n_in, n_out, inverse, need_bwd
 
 
 def _conv_forward(features, w, pair_fwd, n_out, bias=None, out_dtype=None, pair_mask=None, mask_argsort=None,
-                  fp32_accum=None, epilogue=None):
+                  fp32_accum=None, epilogue=None, residual=None):
     scale, shift, act, alpha = epilogue if epilogue is not None else (None, None, 0, 0.0)
     out_dtype = out_dtype or features.dtype
     out = of.conv_forward(features.detach(), w.detach(), pair_fwd, n_out, bias=None if bias is None else bias.detach(),
@@ -54,6 +54,8 @@ def _conv_forward(features, w, pair_fwd, n_out, bias=None, out_dtype=None, pair_
         out = torch.sigmoid(out)
     elif act == 3:
         out = torch.nn.functional.leaky_relu(out, alpha)
+    if residual is not None:
+        out = out + residual.detach().double()
     return out.to(out_dtype)
 
 

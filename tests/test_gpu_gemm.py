@@ -176,3 +176,63 @@ def test_deterministic(gemm_path):
     for fn in (lambda: G.conv_forward(feats, w, pfd, n_out), lambda: G.conv_backward_input(gout, w, pbd, n_in),
                lambda: G.conv_backward_weight(feats, gout, pfd, (64, kv, 32))):
         assert torch.equal(fn(), fn())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("c_in,c_out", [(32, 64), (4, 16), (20, 12)])
+def test_residual_added_in_the_store(gemm_path, dtype, c_in, c_out):
+    """out = conv(x) + residual in one pass (every forward kernel), against the fp64 oracle plus the
+    residual; and through the layer: add_input in training mode gives the same output and the same
+    gradients as the separate addition."""
+    idx_np, res = _scene(77, True)
+    pf, pmf, maf = res[2], res[4], res[6]
+    n, kv = idx_np.shape[0], pf.shape[0]
+    gen = torch.Generator().manual_seed(5)
+    feats = torch.randn(n, c_in, generator=gen).to(dtype)
+    w = (torch.randn(c_out, kv, c_in, generator=gen) / (kv * c_in) ** 0.5).to(dtype)
+    resid = torch.randn(n, c_out, generator=gen).to(dtype)
+    G = _gemm()
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV)  # noqa: E731
+    out = G.conv_forward(feats.to(DEV), w.to(DEV), d(pf), n, mask_argsort=d(maf[0]), pair_mask=d(pmf[0])[:, 0],
+                         residual=resid.to(DEV))
+    e = of.conv_forward(feats, w, pf, n, out_dtype=torch.float64) + resid.double()
+    assert rel_err(to_np(out.double()), e.numpy()) <= TOL[str(dtype).split(".")[-1]]
+
+
+def test_add_input_in_training_is_fused_and_differentiable():
+    import spconv_triton_b200.pytorch as sp
+    from spconv_triton_b200.pytorch import ops
+
+    idx_np, _ = _scene(78, True, n=3000)
+    idx = torch.from_numpy(idx_np).to(DEV)
+    n = idx_np.shape[0]
+    torch.manual_seed(2)
+    conv = sp.SubMConv3d(16, 32, 3, padding=1, bias=False, indice_key="a").to(DEV).train()
+    x0 = torch.randn(n, 16, device=DEV)
+    r0 = torch.randn(n, 32, device=DEV)
+    shape, batch = [24, 40, 36], 2  # the grid _scene draws from
+    seen = []
+    orig = ops.implicit_gemm
+
+    def spy(*a, **kw):
+        seen.append(kw.get("_residual") is not None)
+        return orig(*a, **kw)
+
+    ops.implicit_gemm = spy
+    try:
+        xa, ra = x0.clone().requires_grad_(True), r0.clone().requires_grad_(True)
+        ya = conv(sp.SparseConvTensor(xa, idx, shape, batch), add_input=sp.SparseConvTensor(ra, idx, shape, batch))
+        ya.features.pow(2).sum().backward()
+    finally:
+        ops.implicit_gemm = orig
+    assert seen == [True]  # the residual went into the kernel
+    ga, gra, gwa = xa.grad.clone(), ra.grad.clone(), conv.weight.grad.clone()
+    conv.weight.grad = None
+    xb, rb = x0.clone().requires_grad_(True), r0.clone().requires_grad_(True)
+    yb = conv(sp.SparseConvTensor(xb, idx, shape, batch))
+    fb = yb.features + rb
+    fb.pow(2).sum().backward()
+    assert rel_err(to_np(ya.features), to_np(fb)) <= 1e-5
+    assert rel_err(to_np(ga), to_np(xb.grad)) <= 1e-5
+    assert rel_err(to_np(gra), to_np(rb.grad)) <= 1e-5
+    assert rel_err(to_np(gwa), to_np(conv.weight.grad)) <= 1e-5
