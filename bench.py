@@ -878,6 +878,9 @@ def main():
                     help="single-operator timings at the other configurations instead of the headline benchmark")
     ap.add_argument("--k5-voxels", type=int, default=400000, help="--op conv_k5: voxels per sample (4 samples)")
     ap.add_argument("--pool-voxels", type=int, default=400000, help="--op pool: voxels per sample (4 samples)")
+    ap.add_argument("--in-flight", type=int, default=2,
+                    help="independent steps in flight at a time, each issued by its own host thread and CUDA stream "
+                         "(1 = one pass after the other)")
     ap.add_argument("--no-train", action="store_true",
                     help="skip the training-step record (BASELINE configs[3]) that follows the headline measurement")
     ap.add_argument("--voxel-order", default="random", choices=["random", "sorted"],
@@ -963,16 +966,43 @@ def main():
     for w in range(max(args.warmup, 3 * N_SCENES)):
         out = None
         out = forward(*scenes_dev[w % N_SCENES], scene=w % N_SCENES)
+    # Consecutive steps are independent passes over different scenes.  A pass blocks its host thread
+    # at every strided layer (the read of the output count), so the steps are issued by worker
+    # threads, each on its own stream, with `--in-flight` passes in flight: the kernels that open
+    # step s+1 then overlap the ones that close step s.
+    import collections
+
+    from spconv_triton_b200.parallel import PassPipeline
+
+    pipe = PassPipeline(dev, depth=args.in_flight)
+
+    def run_steps(n_steps, fn):
+        """fn(s) for s in 0..n_steps-1 on the pipeline, at most `in_flight` at a time; results are
+        dropped as they complete (so that their memory returns to the allocator); returns the last."""
+        window, last = collections.deque(), None
+        for s in range(n_steps):
+            if len(window) == args.in_flight:
+                last = window.popleft().result()
+            window.append(pipe.submit(fn, s))
+        while window:
+            last = window.popleft().result()
+        pipe.join()
+        return last
+
+    def resident_step(s):
+        return forward(*scenes_dev[s % N_SCENES], scene=s % N_SCENES)
+
+    run_steps(4 * args.in_flight + N_SCENES, resident_step)  # every worker's allocator pool sees the pattern
     barrier()
     launches0 = lib.spc_launch_count()
+    mallocs0 = torch.cuda.memory_stats(dev).get("num_device_alloc", 0)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     clocks.open_window()
     e0.record()
-    for s in range(args.steps):
-        out = None
-        out = forward(*scenes_dev[s % N_SCENES], scene=s % N_SCENES)
+    out = run_steps(args.steps, resident_step)
     e1.record()
     barrier()
+    mallocs_resident = torch.cuda.memory_stats(dev).get("num_device_alloc", 0) - mallocs0
     launches = lib.spc_launch_count() - launches0
     dev_ms = max_over_ranks(e0.elapsed_time(e1))
     voxels = sum(voxels_per_scene[s % N_SCENES] for s in range(args.steps))
@@ -986,16 +1016,20 @@ def main():
     # crosses PCIe; a buffer is handed out again only after its copy has completed.
     h2d = int(np.mean([i.numel() * 4 + f.numel() * 2 for i, f in scenes_host]))
     max_rows = int(out.features.shape[0] * 1.5) + 1024
+    n_slots = 2 * args.in_flight
     host_out = [(torch.empty((max_rows, out.features.shape[1]), dtype=out.features.dtype).pin_memory(),
-                 torch.empty((max_rows, 4), dtype=torch.int32).pin_memory()) for _ in range(2)]
-    landed = [None, None]
+                 torch.empty((max_rows, 4), dtype=torch.int32).pin_memory()) for _ in range(n_slots)]
+    landed = [None] * n_slots
+    in_transit = [None] * n_slots  # the output tensors whose copy to the host may still be running
     copy_stream = torch.cuda.Stream(device=dev)
     d2h_bytes = []
 
     def e2e_step(s):
-        slot = s % 2
+        # runs on a worker thread, under that worker's stream
+        slot = s % n_slots
         if landed[slot] is not None:
             landed[slot].synchronize()  # the result that used this buffer has arrived (and been consumed)
+            in_transit[slot] = None     # its device memory goes back to the allocator only now
         idx_h, feats_h = scenes_host[s % N_SCENES]
         idx = idx_h.to(dev, non_blocking=True)
         feats = feats_h.to(dev, non_blocking=True)
@@ -1007,29 +1041,40 @@ def main():
         with torch.cuda.stream(copy_stream):
             host_out[slot][0][:n].copy_(o.features, non_blocking=True)
             host_out[slot][1][:n].copy_(o.indices, non_blocking=True)
-            o.features.record_stream(copy_stream)
-            o.indices.record_stream(copy_stream)
-            landed[slot] = torch.cuda.Event()
-            landed[slot].record(copy_stream)
+            done = torch.cuda.Event()
+            done.record(copy_stream)
+        landed[slot], in_transit[slot] = done, o
         d2h_bytes.append(n * (o.features.shape[1] * o.features.element_size() + 16))
+        return None
 
     def e2e_drain():
         torch.cuda.current_stream().wait_stream(copy_stream)
 
-    for w in range(args.warmup):
-        e2e_step(w)
+    run_steps(max(args.warmup, 4 * n_slots), e2e_step)  # buffers, allocator pools and copy stream in steady state
     e2e_drain()
     d2h_bytes.clear()
+    # what the link gives a plain device-to-host copy of one result's size (pinned memory, copy stream)
+    torch.cuda.synchronize()
+    n_probe = min(max_rows, out.features.shape[0])
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(copy_stream):
+        p0.record(copy_stream)
+        for _ in range(4):
+            host_out[0][0][:n_probe].copy_(out.features[:n_probe], non_blocking=True)
+        p1.record(copy_stream)
+    copy_stream.synchronize()
+    d2h_gbps = 4 * n_probe * out.features.shape[1] * out.features.element_size() / (p0.elapsed_time(p1) * 1e-3) / 1e9
     barrier()
+    mallocs1 = torch.cuda.memory_stats(dev).get("num_device_alloc", 0)
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
-    for s in range(args.steps):
-        e2e_step(s)
+    run_steps(args.steps, e2e_step)
     e2e_drain()  # the last results have to be on the host before the clock stops
     e3.record()
     barrier()
     clocks.close_window()
     clocks.stop()
+    mallocs_e2e = torch.cuda.memory_stats(dev).get("num_device_alloc", 0) - mallocs1
     e2e_ms = max_over_ranks(e2.elapsed_time(e3))
     e2e_value = total_voxels / (e2e_ms * 1e-3) / 1e6
 
@@ -1096,12 +1141,18 @@ def main():
             "l2": f"inputs larger than L2: rulebook tables of one step hold {table_bytes / 1e6:.0f} MB "
                   "and scenes rotate every step",
             "parallelism": f"replicas x{world} (sharded by sample, no collective)",
+            "in_flight": f"{args.in_flight} steps in flight (independent passes over different scenes, issued by "
+                         f"{args.in_flight} host threads on their own streams); --in-flight 1 = one pass after the other",
         },
         "e2e": {"value": e2e_value, "unit": "Mvoxels/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": int(np.mean(d2h_bytes)), "ms_per_step": e2e_ms / args.steps,
+                "d2h_link_GBps": d2h_gbps,
                 "result": "output features and indices copied to pinned host memory every step, on a copy stream, "
-                          "double-buffered (step s+1 computes while the result of step s crosses PCIe)"},
+                          "double-buffered (step s+1 computes while the result of step s crosses PCIe)",
+                "in_flight": args.in_flight},
         "gpu_launches": int(launches),
+        "allocator": {"device_mallocs_in_timed_region": int(mallocs_resident),
+                      "device_mallocs_in_e2e_timed_region": int(mallocs_e2e)},
         "clocks": clocks.summary(),
         "rulebook_ms": {"per_indice_key": rulebook_ms, "per_step": rulebook_total_ms,
                         "timing": "CUDA events around each rulebook generation, run-ahead off (host read of the "

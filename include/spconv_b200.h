@@ -102,8 +102,9 @@ long long spc_launch_count(void);
  * device-side waits). */
 int spc_check_device_status(void* stream);
 /* Queues, on `stream`, a copy of the current device's status word into
- * `pinned_host_word` (page-locked host memory owned by the caller) and returns
- * without waiting.  The word is non-zero when a kernel gave up on a bounded wait
+ * `pinned_host_word` (page-locked host memory owned by the caller, allocated with
+ * cudaHostAlloc / cudaMallocHost so that the device can write it: a one-thread
+ * kernel stores the word, no copy engine is involved) and returns without waiting.  The word is non-zero when a kernel gave up on a bounded wait
  * (SPC_ERR_DEVICE_WAIT_EXPIRED) or a rulebook kernel met an index row outside
  * batch_size / spatial_shape (SPC_ERR_INVALID_ARGUMENT).  The host reads the
  * mailbox after work it synchronises on anyway, e.g. at the start of the next

@@ -521,6 +521,17 @@ enumerate_outputs_kernel(const __grid_constant__ Geo g, const int32_t* __restric
   }
 }
 
+// counters[kUniqueCount], counters[kStatus] and the device status word -> page-locked host memory.
+__global__ void publish_counters_kernel(const int* __restrict__ counters, const int* __restrict__ dev_status,
+                                        int* __restrict__ host_box) {
+  if (threadIdx.x == 0) {
+    host_box[0] = counters[0];
+    host_box[1] = counters[1];
+    host_box[2] = dev_status != nullptr ? *dev_status : 0;
+    __threadfence_system();
+  }
+}
+
 template <bool K64>
 __global__ void __launch_bounds__(kThreads)
 assign_ranks_kernel(Table<K64> tout, const typename Table<K64>::key_t* __restrict__ sorted,
@@ -543,10 +554,11 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
                 Table<K64> tin, int32_t* __restrict__ out_indices, int32_t* __restrict__ pair_fwd,
                 int32_t* __restrict__ pair_bwd, uint32_t* __restrict__ words, int mic,
                 int32_t* __restrict__ fwd_rm, int32_t* __restrict__ bwd_rm, int kvp,
-                const uint32_t* __restrict__ bitmap) {
+                const uint32_t* __restrict__ bitmap, int32_t* __restrict__ iota) {
   using key_t = typename Table<K64>::key_t;
   const long long r = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
   if (r >= n_out) return;
+  if (iota != nullptr) iota[r] = static_cast<int32_t>(r);  // the values the mask sort permutes
   int o[ND + 1];
   int quad[4] = {-1, -1, -1, -1};  // four consecutive offsets of the row-major copy
   bool row_ok = true;
@@ -666,10 +678,12 @@ template <int ND, bool K64>
 __global__ void __launch_bounds__(kThreads)
 fill_bwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx, long long n_in,
                 long long n_out, Table<K64> tout, int32_t* __restrict__ pair_bwd,
-                uint32_t* __restrict__ words, int mic, int32_t* __restrict__ bwd_rm, int kvp) {
+                uint32_t* __restrict__ words, int mic, int32_t* __restrict__ bwd_rm, int kvp,
+                int32_t* __restrict__ iota) {
   using key_t = typename Table<K64>::key_t;
   const long long j = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
   if (j >= n_in) return;
+  if (iota != nullptr) iota[j] = static_cast<int32_t>(j);
   int quad[4] = {-1, -1, -1, -1};
   int c[ND + 1];
   load_coord<ND>(idx, j, c);
@@ -1048,6 +1062,21 @@ Table<true> tout_at<true>(char* ws, const Layout& L) {
   return table_at<true>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
 }
 
+// A few page-locked words per host thread and device that kernels write and the host reads after
+// synchronising (host memory: the library still allocates no device memory).
+int host_mailbox(volatile int** out) {
+  static thread_local int* boxes[kMaxDevices] = {nullptr};
+  const int dev = current_device_slot();
+  if (dev < 0) return fail(SPC_ERR_CUDA, "rulebook: no current device");
+  if (boxes[dev] == nullptr) {
+    void* p = nullptr;
+    SPC_CUDA_OK(cudaHostAlloc(&p, 64, cudaHostAllocPortable | cudaHostAllocMapped));
+    boxes[dev] = static_cast<int*>(p);
+  }
+  *out = boxes[dev];
+  return SPC_OK;
+}
+
 inline unsigned blocks_for(int64_t n) { return static_cast<unsigned>(ceil_div(std::max<int64_t>(n, 1), kThreads)); }
 
 // ------------------------------------------------------------------------
@@ -1120,11 +1149,18 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
         bits, prefix, L.obits_words, L.bound, reinterpret_cast<uint32_t*>(sorted), counters);
     SPC_LAUNCH_OK();
   }
-  int host[2] = {0, 0};
-  int sticky = 0;  // the device status word: a bounded wait of an earlier kernel, or a bad row of an earlier layer
-  SPC_CUDA_OK(cudaMemcpyAsync(host, counters, sizeof(host), cudaMemcpyDeviceToHost, st));
-  if (dev_status != nullptr) SPC_CUDA_OK(cudaMemcpyAsync(&sticky, dev_status, sizeof(int), cudaMemcpyDeviceToHost, st));
+  // The output count reaches the host through a page-locked word that a one-thread kernel writes,
+  // not through a device-to-host copy: a copy would queue on the copy engine behind whatever
+  // transfer the application has in flight (a previous result going back to the host, say) and
+  // stall the whole rulebook chain for its duration.
+  volatile int* box = nullptr;
+  int rc_box = host_mailbox(&box);
+  if (rc_box != SPC_OK) return rc_box;
+  publish_counters_kernel<<<1, 32, 0, st>>>(counters, dev_status, const_cast<int*>(box));
+  SPC_LAUNCH_OK();
   SPC_CUDA_OK(cudaStreamSynchronize(st));
+  int host[2] = {box[kUniqueCount], box[kStatus]};
+  const int sticky = box[2];  // the device status word: a bounded wait of an earlier kernel, or a bad row of an earlier layer
   if (host[kStatus] != 0 || sticky != 0) {
     if (dev_status != nullptr && sticky != 0) SPC_CUDA_OK(cudaMemsetAsync(dev_status, 0, sizeof(int), st));
     const int code = host[kStatus] != 0 ? host[kStatus] : sticky;
@@ -1150,9 +1186,27 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
 
 // Sorts the per-row bitmasks (stable, ascending as unsigned, highest word most
 // significant) and emits pair_mask / mask_argsort for every split.
+// One mask word per row, one split that keeps every bit, sorted: the words are the sort keys as
+// they stand and the sort can write pair_mask / mask_argsort itself, if the kernel that produced the
+// words also left 0..n-1 in the value scratch (mask_iota()).
+bool masks_sort_in_place(const Layout& L, const uint32_t* split_masks, int n_split, int do_sort) {
+  return L.mic == 1 && n_split == 1 && do_sort != 0 && split_masks[0] == 0xffffffffu;
+}
+int32_t* mask_iota(const Layout& L, char* ws, const uint32_t* split_masks, int n_split, int do_sort) {
+  return masks_sort_in_place(L, split_masks, n_split, do_sort) ? reinterpret_cast<int32_t*>(ws + L.off_vals_a)
+                                                                 : nullptr;
+}
+
 int emit_masks(const Layout& L, char* ws, int64_t n, int kv, const uint32_t* split_masks, int n_split,
                int do_sort, int32_t* mask_out, int32_t* argsort_out, cudaStream_t st) {
   const uint32_t* words = reinterpret_cast<const uint32_t*>(ws + L.off_words);
+  if (masks_sort_in_place(L, split_masks, n_split, do_sort)) {
+    size_t cub_bytes = L.cub_bytes;
+    SPC_CUDA_OK(cub::DeviceRadixSort::SortPairs(ws + L.off_cub, cub_bytes, words, reinterpret_cast<uint32_t*>(mask_out),
+                                                 reinterpret_cast<const int32_t*>(ws + L.off_vals_a), argsort_out, n, 0,
+                                                 std::min(32, kv), st));
+    return SPC_OK;
+  }
   uint32_t* keys_a = reinterpret_cast<uint32_t*>(ws + L.off_keys_a);
   uint32_t* keys_b = reinterpret_cast<uint32_t*>(ws + L.off_keys_b);
   int32_t* vals_a = reinterpret_cast<int32_t*>(ws + L.off_vals_a);
@@ -1195,8 +1249,9 @@ int igemm_backward_impl(const Geo& g, const Layout& L, const int32_t* idx, int64
   const int kvp = (g.kv + 3) & ~3;
   Table<K64> tout = tout_at<K64>(ws, L);
   uint32_t* words = reinterpret_cast<uint32_t*>(ws + L.off_words);
+  int32_t* iota = mask_bwd != nullptr ? mask_iota(L, ws, split_masks, n_split, do_sort) : nullptr;
   fill_bwd_kernel<ND, K64><<<blocks_for(n_in), kThreads, 0, st>>>(
-      g, idx, n_in, n_out, tout, pair_bwd, mask_bwd ? words : nullptr, L.mic, bwd_rm, kvp);
+      g, idx, n_in, n_out, tout, pair_bwd, mask_bwd ? words : nullptr, L.mic, bwd_rm, kvp, iota);
   SPC_LAUNCH_OK();
   if (mask_bwd != nullptr) return emit_masks(L, ws, n_in, g.kv, split_masks, n_split, do_sort, mask_bwd, argsort_bwd, st);
   return SPC_OK;
@@ -1216,12 +1271,13 @@ int igemm_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, 
   uint32_t* words = reinterpret_cast<uint32_t*>(ws + L.off_words);
   const uint32_t* bitmap = L.shared_bits != nullptr ? L.shared_bits
                            : (L.bitmap_bytes ? reinterpret_cast<const uint32_t*>(ws + L.off_bitmap) : nullptr);
+  int32_t* iota = mask_iota(L, ws, split_masks, n_split, do_sort);
   if (g.subm && pair_bwd != nullptr)
     fill_fwd_kernel<ND, K64, true><<<blocks_for(n_out), kThreads, 0, st>>>(
-        g, idx, sorted, n_out, tin, out_indices, pair_fwd, pair_bwd, words, L.mic, fwd_rm, bwd_rm, kvp, bitmap);
+        g, idx, sorted, n_out, tin, out_indices, pair_fwd, pair_bwd, words, L.mic, fwd_rm, bwd_rm, kvp, bitmap, iota);
   else
     fill_fwd_kernel<ND, K64, false><<<blocks_for(n_out), kThreads, 0, st>>>(
-        g, idx, sorted, n_out, tin, out_indices, pair_fwd, nullptr, words, L.mic, fwd_rm, nullptr, kvp, bitmap);
+        g, idx, sorted, n_out, tin, out_indices, pair_fwd, nullptr, words, L.mic, fwd_rm, nullptr, kvp, bitmap, iota);
   SPC_LAUNCH_OK();
   int rc = emit_masks(L, ws, n_out, g.kv, split_masks, n_split, do_sort, mask_fwd, argsort_fwd, st);
   if (rc != SPC_OK) return rc;

@@ -163,6 +163,65 @@ class GradientReducer:
         self._handles.clear()
 
 
+class PassPipeline:
+    """Independent forward passes in flight from several host threads, one CUDA stream each.
+
+    A pass over a sparse backbone blocks its host thread a few times (each strided layer reads its
+    output count before it can size the next launch), so one thread cannot keep two passes in
+    flight.  The library releases the interpreter lock while it waits, so ``depth`` worker threads,
+    each issuing whole passes on its own stream, keep the GPU supplied with the kernels of ``depth``
+    passes at once (throughput mode of an inference server; a single pass is not faster).
+
+        pipe = PassPipeline(device, depth=2)
+        futures = [pipe.submit(net, batch) for batch in batches]     # each returns net(batch)
+        outputs = [f.result() for f in futures]
+        pipe.join()                                                  # current stream waits for all passes
+    """
+
+    def __init__(self, device, depth: int = 2):
+        import concurrent.futures
+        import threading
+
+        self.device = torch.device(device)
+        self.depth = max(1, int(depth))
+        self._pool = concurrent.futures.ThreadPoolExecutor(max_workers=self.depth, thread_name_prefix="spc-pass")
+        self._local = threading.local()
+        self._streams: list = []
+        self._lock = threading.Lock()
+        self._origin = torch.cuda.current_stream(self.device)
+
+    def _stream(self):
+        st = getattr(self._local, "stream", None)
+        if st is None:
+            torch.cuda.set_device(self.device)
+            st = torch.cuda.Stream(device=self.device)
+            st.wait_stream(self._origin)  # set-up queued on the creating thread's stream comes first
+            self._local.stream = st
+            with self._lock:
+                self._streams.append(st)
+        return st
+
+    def submit(self, fn, *args, **kwargs):
+        """Runs ``fn(*args, **kwargs)`` on a worker thread under its stream (no autograd)."""
+
+        def work():
+            with torch.cuda.stream(self._stream()), torch.no_grad():
+                return fn(*args, **kwargs)
+
+        return self._pool.submit(work)
+
+    def join(self):
+        """Makes the current stream wait for everything the workers have issued so far
+        (call it after the futures of interest have completed)."""
+        cur = torch.cuda.current_stream(self.device)
+        with self._lock:
+            for st in self._streams:
+                cur.wait_stream(st)
+
+    def close(self):
+        self._pool.shutdown(wait=True)
+
+
 def aggregate_throughput(local_units: float, local_ms: float, device=None):
     """(sum of units over ranks, max of milliseconds over ranks)."""
     import torch.distributed as dist

@@ -22,6 +22,8 @@ Switch: ``spconv_triton_b200.constants.SPCONV_RULEBOOK_RUNAHEAD``.
 
 from __future__ import annotations
 
+import threading
+
 import torch
 
 from spconv_triton_b200.core import ConvAlgo
@@ -35,7 +37,9 @@ _side_streams: dict = {}
 
 
 def _side_stream(device: torch.device, which: int) -> torch.cuda.Stream:
-    key = (device.index if device.index is not None else torch.cuda.current_device(), which)
+    # one set per host thread: passes issued from different threads must not queue behind (or
+    # synchronise on) each other's rulebook work
+    key = (device.index if device.index is not None else torch.cuda.current_device(), which, threading.get_ident())
     if key not in _side_streams:
         _side_streams[key] = torch.cuda.Stream(device=device, priority=-1)
     return _side_streams[key]

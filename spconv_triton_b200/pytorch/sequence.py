@@ -20,6 +20,7 @@ one by one as before.  Switch: ``constants.SPCONV_NATIVE_SEQUENCE``.
 from __future__ import annotations
 
 import ctypes
+import threading
 
 import numpy as np
 import torch
@@ -159,6 +160,7 @@ _ITEMSIZE = {torch.float16: 2, torch.bfloat16: 2, torch.int32: 4}
 # first guess of the arena size, before a pass has told how much a plan needs
 _ARENA_BYTES_PER_VOXEL = 6144.0
 _ARENA_MARGIN = 64 << 20
+_ARENA_GRANULE = 128 << 20
 
 
 def _view(arena, offset, count, dtype, shape):
@@ -176,15 +178,19 @@ def forward(container, x):
             or indices.dtype != torch.int32 or _gemm.GEMM_PATH != _lib.SPC_GEMM_AUTO
             or torch.cuda.is_current_stream_capturing()):
         return None
+    # one plan per host thread: its layer and result arrays are written during a pass, and passes
+    # may run concurrently from several threads (parallel.PassPipeline)
     sig = _signature(container, x)
-    cached = container.__dict__.get("_spc_plan")
+    plans = container.__dict__.setdefault("_spc_plans", {})
+    me = threading.get_ident()
+    cached = plans.get(me)
     if cached is None or cached.signature != sig:
         plan = _compile(container, x)
         if plan is None:
-            container.__dict__["_spc_plan"] = None
+            plans.pop(me, None)
             return None
         plan.signature = sig
-        container.__dict__["_spc_plan"] = plan
+        plans[me] = plan
     else:
         plan = cached
     steps = plan.steps
@@ -224,8 +230,11 @@ def forward(container, x):
     with torch.cuda.device(dev):
         main = torch.cuda.current_stream(dev)
         chain, side = _side_stream(dev, 0), _side_stream(dev, 1)
+        # sized from the largest need per input voxel seen so far and rounded up coarsely, so that
+        # passes over scenes of similar size ask the caching allocator for the same block again
         per_voxel = plan.bytes_per_voxel or _ARENA_BYTES_PER_VOXEL
-        arena_bytes = int(per_voxel * n_in * 1.25) + _ARENA_MARGIN
+        arena_bytes = int(per_voxel * n_in * 1.2) + _ARENA_MARGIN
+        arena_bytes = -(-arena_bytes // _ARENA_GRANULE) * _ARENA_GRANULE
         needed = ctypes.c_size_t(0)
         for _attempt in range(4):
             arena = torch.empty(arena_bytes, dtype=torch.uint8, device=dev)
@@ -246,9 +255,10 @@ def forward(container, x):
             if rc != _lib.SPC_ERR_WORKSPACE_TOO_SMALL:
                 return None  # e.g. a layer without output points: the modules raise the proper error
             arena_bytes = int(needed.value * 1.5) + _ARENA_MARGIN
+            arena_bytes = -(-arena_bytes // _ARENA_GRANULE) * _ARENA_GRANULE
         else:
             return None
-        plan.bytes_per_voxel = max(plan.bytes_per_voxel * 0.98, needed.value / n_in)
+        plan.bytes_per_voxel = max(plan.bytes_per_voxel, needed.value / n_in)
         return _wrap(plan, x, indices, arena, dev, keep)
 
 

@@ -115,14 +115,40 @@ def test_arena_that_is_too_small_is_retried():
 
     net, idx, feats, grid, batch = _net_and_scene()
     expect = _run(net, idx, feats, grid, batch, False)
-    old = sequence._ARENA_BYTES_PER_VOXEL, sequence._ARENA_MARGIN
-    sequence._ARENA_BYTES_PER_VOXEL, sequence._ARENA_MARGIN = 64.0, 0
-    net.__dict__.pop("_spc_plan", None)
+    old = sequence._ARENA_BYTES_PER_VOXEL, sequence._ARENA_MARGIN, sequence._ARENA_GRANULE
+    sequence._ARENA_BYTES_PER_VOXEL, sequence._ARENA_MARGIN, sequence._ARENA_GRANULE = 64.0, 0, 4096
+    net.__dict__.pop("_spc_plans", None)
     try:
         got = _run(net, idx, feats, grid, batch, True)
-        assert net.__dict__["_spc_plan"].bytes_per_voxel > 64.0
+        assert next(iter(net.__dict__["_spc_plans"].values())).bytes_per_voxel > 64.0
     finally:
-        sequence._ARENA_BYTES_PER_VOXEL, sequence._ARENA_MARGIN = old
+        sequence._ARENA_BYTES_PER_VOXEL, sequence._ARENA_MARGIN, sequence._ARENA_GRANULE = old
     assert torch.equal(got.indices, expect.indices) and torch.equal(got.features, expect.features)
     again = _run(net, idx, feats, grid, batch, True)  # sized from what the first pass needed
     assert torch.equal(again.features, expect.features)
+
+
+def test_passes_in_flight_from_two_threads_give_the_same_results():
+    """Independent passes issued by two worker threads, each on its own stream (their kernels overlap
+    on the GPU), against the same passes one after the other."""
+    import bench
+    import spconv_triton_b200.pytorch as sp
+    from spconv_triton_b200.parallel import PassPipeline
+
+    net, _, _, grid, batch = _net_and_scene()
+    scenes = [(i.to(DEV), f.to(DEV)) for i, f in bench.make_scenes(5, n_scenes=3, batch=batch)]
+    expect = [_run(net, i, f, grid, batch, True) for i, f in scenes]
+    pipe = PassPipeline(torch.device(DEV, torch.cuda.current_device()), depth=2)
+    futures = [pipe.submit(lambda i=i, f=f: net(sp.SparseConvTensor(f, i, grid, batch)))
+               for _ in range(3) for i, f in scenes]
+    got = [f.result() for f in futures]
+    pipe.join()
+    torch.cuda.synchronize()
+    pipe.close()
+    assert len(net.__dict__["_spc_plans"]) >= 2  # each thread compiled its own plan
+    for k, g in enumerate(got):
+        e = expect[k % len(scenes)]
+        assert torch.equal(g.indices, e.indices) and torch.equal(g.features, e.features)
+        for key in e.indice_dict:
+            assert torch.equal(g.indice_dict[key].pair_fwd, e.indice_dict[key].pair_fwd)
+            assert torch.equal(g.indice_dict[key].mask_argsort_fwd_splits[0], e.indice_dict[key].mask_argsort_fwd_splits[0])
