@@ -631,6 +631,8 @@ def run_op_bench(args):
     def emit(name, ms, nbytes, flops=None, **extra):
         line = {"op": name, "ms": ms, "algorithmic_GBps": nbytes / ms / 1e6, "hbm_frac": nbytes / ms / 1e6 / hbm_peak,
                 "peak_kind": peak_kind, **extra}
+        if "gathered_bytes" in line:
+            line["gathered_GBps"] = line.pop("gathered_bytes") / ms / 1e6
         if "mpoints_per_s" in line:
             line["mpoints_per_s"] = line["points"] / ms / 1e3
         if flops:
@@ -695,21 +697,30 @@ def run_op_bench(args):
             pf, pb = res[2], res[3]
             n_out, kv = pf.shape[1], pf.shape[0]
             pairs = int((pf >= 0).sum())
-            fwd_bytes = pairs * c * 2 + n_out * c * 2 + kv * n_out * 4
+            n_in = int(idx.shape[0])
+            # gathered: every (pair, row) read counted (a 3^3 window re-reads rows out of L2);
+            # compulsory: every input row once + table + stored rows, what has to cross the HBM interface
+            fwd_gathered = pairs * c * 2 + n_out * c * 2 + kv * n_out * 4
+            fwd_bytes = n_in * c * 2 + n_out * c * 2 + kv * n_out * 4
             if name.startswith("max"):
                 out = PL.maxpool_forward(feats, pf, n_out)
                 g = torch.randn_like(out)
                 emit(name + "_fwd", timed(lambda: PL.maxpool_forward(feats, pf, n_out), iters), fwd_bytes,
-                     voxels=int(idx.shape[0]), n_out=n_out, pairs=pairs, voxel_order=args.voxel_order)
-                bwd_bytes = idx.shape[0] * c * 2 * 2 + pairs * c * 2 * 2 + kv * idx.shape[0] * 4
-                emit(name + "_bwd", timed(lambda: PL.maxpool_backward(feats, out, g, pb), iters), bwd_bytes)
+                     voxels=n_in, n_out=n_out, pairs=pairs, voxel_order=args.voxel_order, bytes="compulsory",
+                     gathered_bytes=fwd_gathered)
+                # features + output + output gradient read, input gradient written, table
+                bwd_bytes = n_in * c * 2 * 2 + n_out * c * 2 * 2 + kv * n_in * 4
+                emit(name + "_bwd", timed(lambda: PL.maxpool_backward(feats, out, g, pb), iters), bwd_bytes,
+                     bytes="compulsory", gathered_bytes=n_in * c * 2 * 2 + pairs * c * 2 * 2 + kv * n_in * 4)
             else:
                 out, cnt = PL.avgpool_forward(feats, pf, n_out)
                 g = torch.randn_like(out)
                 emit(name + "_fwd", timed(lambda: PL.avgpool_forward(feats, pf, n_out), iters), fwd_bytes + 4 * n_out,
-                     voxels=int(idx.shape[0]), n_out=n_out, pairs=pairs, voxel_order=args.voxel_order)
-                bwd_bytes = idx.shape[0] * c * 2 + pairs * (c * 2 + 4) + kv * idx.shape[0] * 4
-                emit(name + "_bwd", timed(lambda: PL.avgpool_backward(g, pb, cnt), iters), bwd_bytes)
+                     voxels=n_in, n_out=n_out, pairs=pairs, voxel_order=args.voxel_order, bytes="compulsory",
+                     gathered_bytes=fwd_gathered + 4 * n_out)
+                bwd_bytes = n_in * c * 2 + n_out * (c * 2 + 4) + kv * n_in * 4
+                emit(name + "_bwd", timed(lambda: PL.avgpool_backward(g, pb, cnt), iters), bwd_bytes, bytes="compulsory",
+                     gathered_bytes=n_in * c * 2 + pairs * (c * 2 + 4) + kv * n_in * 4)
     elif args.op == "dense":
         # the step after the backbone: 8 samples, 128 channels, BEV volume [2, 200, 176], 60k rows per sample
         import spconv_triton_b200.pytorch as sp
