@@ -602,12 +602,79 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
       inside[d] = m;
     }
   }
+  // rows in ascending key order: a neighbour's row is the rank of its bit (one load of the word's prefix)
+  const bool ranked = bitmap != nullptr && table_ranked(tin);
+  // what is written for offset k once its input row j (-1: none) is known
+  auto emit = [&](int k, int j) {
+    pair_fwd[static_cast<long long>(k) * n_out + r] = j;
+    if (SUBM_BWD) {
+      pair_bwd[static_cast<long long>(g.kv - 1 - k) * n_out + r] = j;
+      if (bwd_rm != nullptr) bwd_rm[r * kvp + (g.kv - 1 - k)] = j;
+    }
+    if (fwd_rm != nullptr) {
+      quad[k & 3] = j;
+      if ((k & 3) == 3 || k == g.kv - 1) {
+        *reinterpret_cast<int4*>(&fwd_rm[r * kvp + (k & ~3)]) = make_int4(quad[0], quad[1], quad[2], quad[3]);
+        quad[0] = quad[1] = quad[2] = quad[3] = -1;
+      }
+    }
+    word |= static_cast<uint32_t>(j >= 0) << (k & 31);
+    if ((k & 31) == 31 || k == g.kv - 1) {
+      words[r * mic + (k >> 5)] = word;
+      word = 0;
+    }
+  };
+  const int kl = g.ksize[ND - 1];
+  if (fast && row_ok && bitmap != nullptr && g.dil[ND - 1] == 1) {
+    // Window path.  The kl offsets along the last axis are kl consecutive cells, i.e. consecutive
+    // bits of the occupancy bitmap: one (at a word boundary two) loads test all of them, and in
+    // ranked mode one prefix load numbers all of them, since the prefix of the next word is this
+    // word's prefix plus its population count.  A scattered load costs an L1 wavefront per lane, so
+    // 2-3 loads per axis line instead of one or two per offset is what this kernel's time follows.
+    const uint32_t in_mask = inside[ND - 1] & (kl >= 32 ? 0xffffffffu : ((1u << kl) - 1u));
+    for (int k0 = 0; k0 < g.kv; k0 += kl) {
+      uint32_t ok = in_mask != 0;
+      long long kk = base;
+#pragma unroll
+      for (int d = 0; d < ND - 1; ++d) {
+        ok &= inside[d] >> od.pos[d];
+        kk += od.pos[d] * step[d];
+      }
+      uint32_t present = 0, w0 = 0, w1 = 0, pfx0 = 0;
+      int qlo = 0, sh = 0;
+      long long kb = 0;
+      if (ok & 1u) {
+        qlo = __ffs(in_mask) - 1;                 // first offset of the line that lies inside the grid
+        const int qhi = 31 - __clz(in_mask);      // and the last one
+        kb = kk + qlo;                            // its cell: a valid key
+        const long long wi = kb >> 5;
+        sh = static_cast<int>(kb & 31);
+        w0 = __ldg(&bitmap[wi]);
+        if (sh + (qhi - qlo) >= 32) w1 = __ldg(&bitmap[wi + 1]);  // the word of a valid cell as well
+        const unsigned long long win = ((static_cast<unsigned long long>(w1) << 32) | w0) >> sh;
+        present = (static_cast<uint32_t>(win) << qlo) & in_mask;
+        if (present != 0 && ranked) pfx0 = rank_prefix(tin, kb);
+      }
+      for (int q = 0; q < kl; ++q) {
+        int j = -1;
+        if ((present >> q) & 1u) {
+          if (ranked) {
+            const int bit = sh + (q - qlo);
+            j = bit < 32 ? static_cast<int>(pfx0) + __popc(w0 & ((1u << bit) - 1u))
+                         : static_cast<int>(pfx0) + __popc(w0) + __popc(w1 & ((1u << (bit - 32)) - 1u));
+          } else {
+            j = tin.find(static_cast<key_t>(kb + (q - qlo)));
+          }
+        }
+        emit(k0 + q, j);
+        od.next(g);
+      }
+    }
+  } else {
   // Offsets are handled three at a time (the three neighbours along the last axis of a 3^3
   // kernel): their bitmap words, then their first hash probes, are requested together, so a row
   // has up to three L2 accesses in flight instead of one after the other.
   constexpr int kBatch = 3;
-  // rows in ascending key order: a neighbour's row is the rank of its bit (one load of the word's prefix)
-  const bool ranked = bitmap != nullptr && table_ranked(tin);
   for (int k0 = 0; k0 < g.kv; k0 += kBatch) {
     long long key[kBatch];
     uint32_t bits[kBatch];
@@ -649,24 +716,9 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
       const int j = key[b] < 0 ? -1
                     : ranked  ? static_cast<int>(probe[b]) + __popc(bits[b] & ((1u << (key[b] & 31)) - 1u))
                               : tin.finish(static_cast<key_t>(key[b]), probe[b]);
-      pair_fwd[static_cast<long long>(k) * n_out + r] = j;
-      if (SUBM_BWD) {
-        pair_bwd[static_cast<long long>(g.kv - 1 - k) * n_out + r] = j;
-        if (bwd_rm != nullptr) bwd_rm[r * kvp + (g.kv - 1 - k)] = j;
-      }
-      if (fwd_rm != nullptr) {
-        quad[k & 3] = j;
-        if ((k & 3) == 3 || k == g.kv - 1) {
-          *reinterpret_cast<int4*>(&fwd_rm[r * kvp + (k & ~3)]) = make_int4(quad[0], quad[1], quad[2], quad[3]);
-          quad[0] = quad[1] = quad[2] = quad[3] = -1;
-        }
-      }
-      word |= static_cast<uint32_t>(j >= 0) << (k & 31);
-      if ((k & 31) == 31 || k == g.kv - 1) {
-        words[r * mic + (k >> 5)] = word;
-        word = 0;
-      }
+      emit(k, j);
     }
+  }
   }
   if (SUBM_BWD && bwd_rm != nullptr)
     for (int k = g.kv; k < kvp; ++k) bwd_rm[r * kvp + k] = -1;
@@ -1062,6 +1114,34 @@ Table<true> tout_at<true>(char* ws, const Layout& L) {
   return table_at<true>(ws, L.off_tout, L.off_tout_vals, L.cap_out);
 }
 
+// Byte fill of scratch regions by a kernel of this library rather than cudaMemsetAsync: the
+// regions are 16-byte multiples at 16-byte aligned offsets, and a kernel can neither be routed
+// to a copy engine (where it would queue behind a large transfer of the application) nor
+// cost a driver memset's set-up.
+__global__ void __launch_bounds__(256) fill_bytes_kernel(uint4* __restrict__ dst, uint32_t word, long long n16) {
+  const long long stride = static_cast<long long>(gridDim.x) * 256;
+  const uint4 v = make_uint4(word, word, word, word);
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n16; i += stride) dst[i] = v;
+}
+int fill_bytes(void* dst, int byte, size_t bytes, cudaStream_t st) {
+  if (bytes == 0) return SPC_OK;
+  if ((reinterpret_cast<uintptr_t>(dst) & 15u) != 0 || bytes % 16 != 0) {
+    SPC_CUDA_OK(cudaMemsetAsync(dst, byte, bytes, st));
+    return SPC_OK;
+  }
+  const long long n16 = static_cast<long long>(bytes / 16);
+  const uint32_t b = static_cast<uint32_t>(byte) & 0xffu;
+  const unsigned blocks = static_cast<unsigned>(std::min<long long>(ceil_div(n16, 256), 16ll * sm_count()));
+  fill_bytes_kernel<<<blocks, 256, 0, st>>>(static_cast<uint4*>(dst), b * 0x01010101u, n16);
+  SPC_LAUNCH_OK();
+  return SPC_OK;
+}
+#define SPC_FILL(dst, byte, bytes, st)                              \
+  do {                                                              \
+    const int rc__ = fill_bytes((dst), (byte), (bytes), (st));      \
+    if (rc__ != SPC_OK) return rc__;                                \
+  } while (0)
+
 // A few page-locked words per host thread and device that kernels write and the host reads after
 // synchronising (host memory: the library still allocates no device memory).
 int host_mailbox(volatile int** out) {
@@ -1090,16 +1170,16 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
   // Submanifold layers return without a host read, so a row outside the grid is also recorded in the
   // device status word, which the host reads at its next synchronisation point.
   int* dev_status = device_status_ptr();
-  SPC_CUDA_OK(cudaMemsetAsync(counters, 0, 256, st));
+  SPC_FILL(counters, 0, 256, st);
   const bool chained = L.shared_bits != nullptr;  // input bitmap and prefix exist already, no input table
   if (!chained) {
-    SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin, 0xFF, static_cast<size_t>(L.cap_in) * 8, st));
-    if (K64) SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tin_vals, 0x7F, static_cast<size_t>(L.cap_in) * 4, st));
+    SPC_FILL(ws + L.off_tin, 0xFF, static_cast<size_t>(L.cap_in) * 8, st);
+    if (K64) SPC_FILL(ws + L.off_tin_vals, 0x7F, static_cast<size_t>(L.cap_in) * 4, st);
   }
   Table<K64> tin = tin_at<K64>(ws, L);
   uint32_t* bitmap = (L.bitmap_bytes && !chained) ? reinterpret_cast<uint32_t*>(ws + L.off_bitmap) : nullptr;
   if (bitmap != nullptr) {
-    SPC_CUDA_OK(cudaMemsetAsync(bitmap, 0, L.bitmap_bytes, st));
+    SPC_FILL(bitmap, 0, L.bitmap_bytes, st);
     mark_inputs_kernel<ND><<<blocks_for(n_in), kThreads, 0, st>>>(g, idx, n_in, bitmap, counters, dev_status);
     SPC_LAUNCH_OK();
     const int64_t words = static_cast<int64_t>(L.bitmap_bytes / 4);
@@ -1120,10 +1200,10 @@ int prepare_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in
   }
   const bool dense_out = L.obits_words != 0;
   if (dense_out) {
-    SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_obits, 0, static_cast<size_t>(L.obits_words) * 4, st));
+    SPC_FILL(ws + L.off_obits, 0, align_up(static_cast<size_t>(L.obits_words) * 4, 16), st);
   } else {
-    SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tout, 0xFF, static_cast<size_t>(L.cap_out) * 8, st));
-    if (K64) SPC_CUDA_OK(cudaMemsetAsync(ws + L.off_tout_vals, 0x7F, static_cast<size_t>(L.cap_out) * 4, st));
+    SPC_FILL(ws + L.off_tout, 0xFF, static_cast<size_t>(L.cap_out) * 8, st);
+    if (K64) SPC_FILL(ws + L.off_tout_vals, 0x7F, static_cast<size_t>(L.cap_out) * 4, st);
   }
   Table<K64> tout = tout_at<K64>(ws, L);
   key_t* uniq = reinterpret_cast<key_t*>(ws + L.off_uniq);

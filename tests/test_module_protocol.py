@@ -149,3 +149,31 @@ def test_posted_device_status_raises_at_the_next_pass():
     view[0] = _lib.SPC_ERR_INVALID_ARGUMENT
     with pytest.raises(_lib.SpconvB200Error, match="outside batch_size"):
         _lib.raise_posted_status()
+
+
+def test_native_sequence_plan():
+    """Which containers the one-call inference pass takes, and how it maps layers to rulebooks
+    (host logic only: the plan is compiled without touching the GPU)."""
+    import bench
+    from spconv_triton_b200.pytorch import sequence
+
+    net = bench.build_backbone().eval()
+    x = sp.SparseConvTensor(torch.zeros(5, 4), torch.zeros(5, 4, dtype=torch.int32), bench.GRID, 8)
+    plan = sequence._compile(net, x)
+    assert plan is not None and len(plan.steps) == len(bench.LAYERS)
+    # layers that share an indice_key share the rulebook of the first of them
+    assert [st.rulebook for st in plan.steps] == [0, 1, 2, 2, 4, 5, 5, 7, 8, 8]
+    assert [st.generates for st in plan.steps] == [True, True, True, False, True, True, False, True, True, False]
+    assert all(st.bn is not None and st.relu for st in plan.steps)
+    assert plan.out_shape == [6, 200, 176]
+    assert plan.layers[1].geom.subm == 0 and plan.layers[2].geom.subm == 1 and plan.layers[3].rulebook == 2
+    # left to the modules: training mode, a pooling layer, a Native-algorithm layer, an inverse layer,
+    # a rulebook that exists already
+    assert sequence._compile(net.train(), x) is None
+    net.eval()
+    assert sequence._compile(sp.SparseSequential(sp.SubMConv3d(4, 8, 3, indice_key="a"), sp.SparseMaxPool3d(2, 2)).eval(), x) is None
+    assert sequence._compile(sp.SparseSequential(sp.SubMConv3d(4, 8, 5)).eval(), x) is None
+    assert sequence._compile(sp.SparseSequential(sp.SparseConv3d(4, 8, 3, 2, indice_key="d"),
+                                                 sp.SparseInverseConv3d(8, 4, 3, indice_key="d")).eval(), x) is None
+    x.indice_dict["subm0"] = object()
+    assert sequence._compile(net, x) is None
