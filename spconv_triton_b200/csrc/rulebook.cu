@@ -554,10 +554,19 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
                 Table<K64> tin, int32_t* __restrict__ out_indices, int32_t* __restrict__ pair_fwd,
                 int32_t* __restrict__ pair_bwd, uint32_t* __restrict__ words, int mic,
                 int32_t* __restrict__ fwd_rm, int32_t* __restrict__ bwd_rm, int kvp,
-                const uint32_t* __restrict__ bitmap, int32_t* __restrict__ iota) {
+                const uint32_t* __restrict__ bitmap, int32_t* __restrict__ iota, int staged) {
   using key_t = typename Table<K64>::key_t;
   const long long r = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x;
-  if (r >= n_out) return;
+  // Row-major copies: a thread owns one row of kvp entries, so direct stores are 16 (or 4) bytes at
+  // a stride of kvp * 4 bytes -- a warp-wide store then touches 32 sectors and writes half (an
+  // eighth) of each.  With `staged` the warp collects its 32 rows in shared memory and writes the
+  // 32 * kvp * 4 contiguous bytes with full 16-byte-per-lane stores.
+  extern __shared__ int32_t stage_s[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int32_t* tile_f = stage_s + static_cast<size_t>(warp) * (SUBM_BWD ? 2 : 1) * 32 * kvp;
+  int32_t* tile_b = tile_f + 32 * kvp;
+  const bool live = r < n_out;
+  if (live) {
   if (iota != nullptr) iota[r] = static_cast<int32_t>(r);  // the values the mask sort permutes
   int o[ND + 1];
   int quad[4] = {-1, -1, -1, -1};  // four consecutive offsets of the row-major copy
@@ -609,13 +618,20 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
     pair_fwd[static_cast<long long>(k) * n_out + r] = j;
     if (SUBM_BWD) {
       pair_bwd[static_cast<long long>(g.kv - 1 - k) * n_out + r] = j;
-      if (bwd_rm != nullptr) bwd_rm[r * kvp + (g.kv - 1 - k)] = j;
+      if (bwd_rm != nullptr) {
+        if (staged) tile_b[lane * kvp + (g.kv - 1 - k)] = j;
+        else bwd_rm[r * kvp + (g.kv - 1 - k)] = j;
+      }
     }
     if (fwd_rm != nullptr) {
-      quad[k & 3] = j;
-      if ((k & 3) == 3 || k == g.kv - 1) {
-        *reinterpret_cast<int4*>(&fwd_rm[r * kvp + (k & ~3)]) = make_int4(quad[0], quad[1], quad[2], quad[3]);
-        quad[0] = quad[1] = quad[2] = quad[3] = -1;
+      if (staged) {
+        tile_f[lane * kvp + k] = j;
+      } else {
+        quad[k & 3] = j;
+        if ((k & 3) == 3 || k == g.kv - 1) {
+          *reinterpret_cast<int4*>(&fwd_rm[r * kvp + (k & ~3)]) = make_int4(quad[0], quad[1], quad[2], quad[3]);
+          quad[0] = quad[1] = quad[2] = quad[3] = -1;
+        }
       }
     }
     word |= static_cast<uint32_t>(j >= 0) << (k & 31);
@@ -720,8 +736,33 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
     }
   }
   }
-  if (SUBM_BWD && bwd_rm != nullptr)
+  if (staged) {
+    for (int k = g.kv; k < kvp; ++k) {
+      if (fwd_rm != nullptr) tile_f[lane * kvp + k] = -1;
+      if (SUBM_BWD && bwd_rm != nullptr) tile_b[lane * kvp + k] = -1;
+    }
+  } else if (SUBM_BWD && bwd_rm != nullptr) {
     for (int k = g.kv; k < kvp; ++k) bwd_rm[r * kvp + k] = -1;
+  }
+  }  // live
+  if (staged) {
+    __syncwarp();
+    const long long row0 = r - lane;  // first row of this warp
+    const long long left = n_out - row0;
+    if (left > 0) {
+      const int n4 = static_cast<int>(left < 32 ? left : 32) * kvp / 4;  // kvp is a multiple of 4
+      if (fwd_rm != nullptr) {
+        int4* dst = reinterpret_cast<int4*>(fwd_rm + row0 * kvp);
+        const int4* src = reinterpret_cast<const int4*>(tile_f);
+        for (int i = lane; i < n4; i += 32) dst[i] = src[i];
+      }
+      if (SUBM_BWD && bwd_rm != nullptr) {
+        int4* dst = reinterpret_cast<int4*>(bwd_rm + row0 * kvp);
+        const int4* src = reinterpret_cast<const int4*>(tile_b);
+        for (int i = lane; i < n4; i += 32) dst[i] = src[i];
+      }
+    }
+  }
 }
 
 // Column j of pair_bwd (strided / transposed layers): for each offset the
@@ -1352,12 +1393,22 @@ int igemm_impl(const Geo& g, const Layout& L, const int32_t* idx, int64_t n_in, 
   const uint32_t* bitmap = L.shared_bits != nullptr ? L.shared_bits
                            : (L.bitmap_bytes ? reinterpret_cast<const uint32_t*>(ws + L.off_bitmap) : nullptr);
   int32_t* iota = mask_iota(L, ws, split_masks, n_split, do_sort);
-  if (g.subm && pair_bwd != nullptr)
-    fill_fwd_kernel<ND, K64, true><<<blocks_for(n_out), kThreads, 0, st>>>(
-        g, idx, sorted, n_out, tin, out_indices, pair_fwd, pair_bwd, words, L.mic, fwd_rm, bwd_rm, kvp, bitmap, iota);
-  else
-    fill_fwd_kernel<ND, K64, false><<<blocks_for(n_out), kThreads, 0, st>>>(
-        g, idx, sorted, n_out, tin, out_indices, pair_fwd, nullptr, words, L.mic, fwd_rm, nullptr, kvp, bitmap, iota);
+  // the row-major copies go through shared memory when a warp's 32 rows fit (kernel volumes up to 32)
+  const bool with_bwd = g.subm && pair_bwd != nullptr;
+  const int staged = (fwd_rm != nullptr && kvp <= 32 && (reinterpret_cast<uintptr_t>(fwd_rm) & 15u) == 0 &&
+                      (!with_bwd || bwd_rm == nullptr || (reinterpret_cast<uintptr_t>(bwd_rm) & 15u) == 0)) ? 1 : 0;
+  const size_t stage_bytes = staged ? static_cast<size_t>(kThreads / 32) * (with_bwd ? 2 : 1) * 32 * kvp * 4 : 0;
+  if (with_bwd) {
+    static bool configured[kMaxDevices] = {false};
+    SPC_CUDA_OK(ensure_dynamic_smem(fill_fwd_kernel<ND, K64, true>, 64 * 1024, configured));
+    fill_fwd_kernel<ND, K64, true><<<blocks_for(n_out), kThreads, stage_bytes, st>>>(
+        g, idx, sorted, n_out, tin, out_indices, pair_fwd, pair_bwd, words, L.mic, fwd_rm, bwd_rm, kvp, bitmap, iota,
+        staged);
+  } else {
+    fill_fwd_kernel<ND, K64, false><<<blocks_for(n_out), kThreads, stage_bytes, st>>>(
+        g, idx, sorted, n_out, tin, out_indices, pair_fwd, nullptr, words, L.mic, fwd_rm, nullptr, kvp, bitmap, iota,
+        staged);
+  }
   SPC_LAUNCH_OK();
   int rc = emit_masks(L, ws, n_out, g.kv, split_masks, n_split, do_sort, mask_fwd, argsort_fwd, st);
   if (rc != SPC_OK) return rc;

@@ -58,7 +58,7 @@ class _Step:
 
 
 class _Plan:
-    __slots__ = ("steps", "layers", "results", "signature", "out_shape", "bytes_per_voxel")
+    __slots__ = ("steps", "layers", "results", "signature", "out_shape", "bytes_per_voxel", "arena_bytes")
 
 
 def _flatten(container, out) -> bool:
@@ -141,6 +141,7 @@ def _compile(container, x) -> _Plan | None:
     plan.results = (SeqResult * len(steps))()
     plan.out_shape = shape
     plan.bytes_per_voxel = 0.0
+    plan.arena_bytes = 0
     for st, L in zip(steps, plan.layers):
         c = st.conv
         L.geom = _lib.make_geometry(x.batch_size, st.in_shape, st.out_shape, c.kernel_size, c.stride, c.padding,
@@ -235,6 +236,9 @@ def forward(container, x):
         per_voxel = plan.bytes_per_voxel or _ARENA_BYTES_PER_VOXEL
         arena_bytes = int(per_voxel * n_in * 1.2) + _ARENA_MARGIN
         arena_bytes = -(-arena_bytes // _ARENA_GRANULE) * _ARENA_GRANULE
+        # never smaller than the last one: equal requests are what the caching allocator serves
+        # from its free list without splitting or growing
+        arena_bytes = plan.arena_bytes = max(arena_bytes, plan.arena_bytes)
         needed = ctypes.c_size_t(0)
         for _attempt in range(4):
             arena = torch.empty(arena_bytes, dtype=torch.uint8, device=dev)
@@ -255,7 +259,7 @@ def forward(container, x):
             if rc != _lib.SPC_ERR_WORKSPACE_TOO_SMALL:
                 return None  # e.g. a layer without output points: the modules raise the proper error
             arena_bytes = int(needed.value * 1.5) + _ARENA_MARGIN
-            arena_bytes = -(-arena_bytes // _ARENA_GRANULE) * _ARENA_GRANULE
+            arena_bytes = plan.arena_bytes = -(-arena_bytes // _ARENA_GRANULE) * _ARENA_GRANULE
         else:
             return None
         plan.bytes_per_voxel = max(plan.bytes_per_voxel, needed.value / n_in)
