@@ -95,7 +95,8 @@ class SparseImplicitGemmFunction(Function):
             features, filters, grad_output, pair_fwd, pair_bwd, e["pair_mask_fwd_splits"],
             e["pair_mask_bwd_splits"], e["mask_argsort_fwd_splits"], e["mask_argsort_bwd_splits"],
             mask_output_fwd=e["mask_output_fwd"], masks=e["masks"], mask_width=e["mask_width"],
-            is_subm=e["is_subm"], timer=e["timer"], fp32_accum=e["fp32_accum"])
+            is_subm=e["is_subm"], timer=e["timer"], fp32_accum=e["fp32_accum"],
+            _need_din=ctx.needs_input_grad[0])
         return (din, dw) + (None,) * 16 + ((grad_output if ctx.has_residual else None),)
 
 

@@ -183,14 +183,19 @@ def implicit_gemm(features, filters, pair_fwd, pair_mask_fwd_splits, mask_argsor
 def implicit_gemm_backward(features, filters, grad_output, pair_fwd, pair_bwd, pair_mask_fwd_splits,
                            pair_mask_bwd_splits, mask_argsort_fwd_splits, mask_argsort_bwd_splits,
                            mask_output_fwd, masks: list[np.ndarray], mask_width: int, is_subm: bool,
-                           timer: CUDAKernelTimer = CUDAKernelTimer(False), fp32_accum: bool | None = None):
-    """Implicit-gemm backward -> ``(din, dfilters)`` (reference: ops.py:308-347)."""
+                           timer: CUDAKernelTimer = CUDAKernelTimer(False), fp32_accum: bool | None = None,
+                           _need_din: bool = True):
+    """Implicit-gemm backward -> ``(din, dfilters)`` (reference: ops.py:308-347).
+    ``_need_din=False`` (not in the reference) skips the input gradient, which autograd does not
+    ask for at the first layer of a network; ``din`` is then None."""
     features = features.contiguous()
     grad_output = grad_output.contiguous()
     w = _filters_krsc(filters)
     pm, ar = _single_split_mask(pair_mask_bwd_splits, mask_argsort_bwd_splits, masks)
-    din = _gemm.conv_backward_input(grad_output, w, pair_bwd, features.shape[0], pair_mask=pm,
-                                    mask_argsort=ar, fp32_accum=fp32_accum)
+    din = None
+    if _need_din:
+        din = _gemm.conv_backward_input(grad_output, w, pair_bwd, features.shape[0], pair_mask=pm,
+                                        mask_argsort=ar, fp32_accum=fp32_accum)
     dw = _gemm.conv_backward_weight(features, grad_output, pair_fwd, w.shape, fp32_accum=fp32_accum)
     return din, dw.reshape(filters.shape)
 
