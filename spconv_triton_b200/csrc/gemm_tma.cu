@@ -81,30 +81,51 @@ __host__ __device__ inline uint32_t layout_type_for(int row_bytes) {
 // (shared memory permitting), i.e. three or four MMA issuers and that many tiles whose table
 // load, pipeline drain and epilogue overlap the others' stages: 64 -> 64 went from 166 us with
 // 2 x 288 threads to 141 us with 3 x 160, 32 -> 32 from 149 us to 103 us with 4 x 160.
+//
+// The copy warps are bound by the instructions they issue per stage, not by bytes: with the
+// copies, the multiplications and the stores all removed the kernel still took 60 % of its time.
+// So a stage costs a copy thread as few instructions as the job allows: one vector read of its
+// rows' table entries (the table tile is stored in the order the copy threads read it), per row
+// one clamp, one address and one copy whose zero fill is a predicate, destinations that are
+// compile-time offsets from the stage base; the MMA warp counts the stages itself from the same
+// vote, so no per-stage record goes through shared memory and no terminator stage exists.
 constexpr int kIssueWarps = 4;                        // warps that issue the feature-row copies
 constexpr int kIssueThreads = kIssueWarps * 32;       // 128
 constexpr int kMmaWarp = kIssueWarps;                 // warp 4
 constexpr int kThreadsHybrid = kIssueThreads + 32;    // 160
-constexpr int kRowsPerThread = kTileM * 8 / kIssueThreads;  // 8: a thread copies one 16-byte piece of 8 rows
-constexpr int kRowStep = kTileM / kRowsPerThread;            // 16
+constexpr int kPassBytes = kIssueThreads * 16;        // one copy per thread covers 2048 bytes of the tile
 constexpr int kMaxCtasPerSm = 4;                      // 4 x 160 threads x 96 registers fit the register file
 
-template <typename T, typename TO, bool B_MN>
+// 16-byte copy into shared memory; zeros instead when row < 0 (the source is then not read).
+__device__ __forceinline__ void cp_async16_row(uint32_t dst, const void* src, int row) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.lt.s32 p, %2, 0;\n\t"
+      "cp.async.cg.shared.global [%0], [%1], 16, p;\n\t}" ::"r"(dst), "l"(src), "r"(row)
+      : "memory");
+}
+
+// LPR: lanes per row = 16-byte pieces of one A row in a stage (8, 4 or 2 for rows of 128, 64 or 32
+// bytes).  128 / LPR rows are covered by one copy per thread, so a thread copies piece
+// tid % LPR of rows tid / LPR + i * (128 / LPR), i < LPR.
+template <typename T, typename TO, bool B_MN, int LPR>
 __global__ void __maxnreg__(96)
 gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constant__ CUtensorMap map_b) {
   constexpr int ELEM = sizeof(T);
   constexpr int UMMA_K = 32 / ELEM;
   constexpr bool TF32 = TcType<T>::tf32;
+  constexpr int A_ROW_BYTES = 16 * LPR;
+  constexpr int kRowsPass = kIssueThreads / LPR;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int stage_bytes = p.a_stage_bytes + p.b_stage_bytes;
   uint8_t* stage_base = smem;
-  int* idx_s = reinterpret_cast<int*>(smem + static_cast<size_t>(p.stages) * stage_bytes);  // [group_rows][128]
+  // table entries of the group, [offset][row / kRowsPass-th copy of thread row % kRowsPass]
+  int* idx_s = reinterpret_cast<int*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(idx_s + p.group_rows * kTileM);
-  StageInfo* info = reinterpret_cast<StageInfo*>(bars + 2 * kMaxStages + 1);
-  uint32_t* vote = reinterpret_cast<uint32_t*>(info + kMaxStages);
-  uint32_t* tmem_slot = vote + 4;
+  uint32_t* vote = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 1);  // [2][4]: groups alternate
+  uint32_t* tmem_slot = vote + 8;
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
   float* epi_scale = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(abort_flag + 1) + 15) & ~uintptr_t(15));  // [epi_pad]
   float* epi_shift = epi_scale + p.epi_pad;                       // [epi_pad] per-channel shift (bias folded in)
@@ -140,41 +161,41 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int epr = p.a_row_bytes / ELEM;  // reduction elements per stage
+  const int epr = A_ROW_BYTES / ELEM;  // reduction elements per stage
   const int n_rchunks = (p.r_dim + epr - 1) / epr;
-  const int ksteps = epr / UMMA_K;
-  int real_stages = 0;
+  constexpr int KSTEPS = A_ROW_BYTES / 32;  // tcgen05.mma instructions per stage
+  const uint32_t stage0 = smem_u32(stage_base);
+  const uint32_t ring_end = stage0 + static_cast<uint32_t>(p.stages * stage_bytes);
 
   if (warp < kIssueWarps) {
-    const bool tile_warp = warp < 4;  // these also load the table entries and run the epilogue
     long long my_row = -1;
-    if (tile_warp) {
+    {
       const long long slot = m0 + tid;
       if (slot < p.m_rows) my_row = p.order ? static_cast<long long>(__ldg(&p.order[slot])) : slot;
     }
-    int stage = 0;
-    uint32_t empty_parity = 1;
+    int real_stages = 0;
     bool ok = true;
     const int b_cols = p.b_row_bytes / ELEM;  // MN-major: output channels per column block
     const int ncb = B_MN ? (p.n_dim + b_cols - 1) / b_cols : 1;
     const uint32_t b_bytes = B_MN ? static_cast<uint32_t>(ncb * epr * p.b_row_bytes)
-                                  : static_cast<uint32_t>(p.n_dim * p.a_row_bytes);
-    // this thread copies 16-byte piece `chunk` of rows row_lo, row_lo + 16, .., row_lo + 112
-    const int chunk = tid & 7, row_lo = tid >> 3;
-    const bool copies = chunk < p.a_row_bytes / 16;
-    const uint32_t swz_mask = static_cast<uint32_t>(p.a_row_bytes / 16 - 1);  // 7, 3 or 1
-    uint32_t dst_off[kRowsPerThread];
-#pragma unroll
-    for (int i = 0; i < kRowsPerThread; ++i) {
-      const uint32_t lin = static_cast<uint32_t>((row_lo + kRowStep * i) * p.a_row_bytes + chunk * 16);
-      dst_off[i] = lin ^ (((lin >> 7) & swz_mask) << 4);
-    }
+                                  : static_cast<uint32_t>(p.n_dim * A_ROW_BYTES);
+    const int chunk = tid & (LPR - 1), row_lo = tid / LPR;
+    // 128 / LPR rows further down the tile is 2048 bytes further and leaves the swizzle term
+    // (row modulo 8, 4 or 2) alone: the i-th copy goes to a_dst + i * kPassBytes
+    const uint32_t lin0 = static_cast<uint32_t>(row_lo * A_ROW_BYTES + chunk * 16);
+    uint32_t a_dst = stage0 + (lin0 ^ (((lin0 >> 7) & static_cast<uint32_t>(LPR - 1)) << 4));  // this thread's piece of row_lo
+    uint32_t full = bar_full, empty = bar_empty, empty_parity = 1;
+    const uint32_t a_dst0 = a_dst;
     const uint8_t* src_chunk = static_cast<const uint8_t*>(p.src) + chunk * 16;
     const uint32_t src_pitch = static_cast<uint32_t>(p.r_dim) * ELEM;
+    // the tile row `tid` is the (tid / kRowsPass)-th copy of copy thread row_lo = tid % kRowsPass
+    int* const wr_ptr = idx_s + (tid % kRowsPass) * LPR + tid / kRowsPass;
+    const int* const rd_ptr = idx_s + row_lo * LPR;
 
-    for (int k0 = 0; k0 < p.kv; k0 += kGroup) {
+    int group = 0;
+    for (int k0 = 0; k0 < p.kv; k0 += kGroup, ++group) {
       const int gcount = min(kGroup, p.kv - k0);
-      if (tile_warp) {
+      {
         // all table entries of the group are requested before any is used
         int jj[kGroup];
         if (p.pairs_rm != nullptr) {
@@ -198,137 +219,136 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
 #pragma unroll
         for (int kk = 0; kk < kGroup; ++kk) {
           mine |= static_cast<uint32_t>(jj[kk] >= 0) << kk;
-          if (kk < gcount) idx_s[kk * kTileM + tid] = jj[kk];
+          if (kk < gcount) wr_ptr[kk * kTileM] = jj[kk];
         }
         mine = __reduce_or_sync(0xffffffffu, mine);
-        if (lane == 0) vote[warp] = mine;
+        if (lane == 0) vote[(group & 1) * 4 + warp] = mine;
       }
-      named_bar_sync(1, kIssueThreads);
-      const uint32_t active = vote[0] | vote[1] | vote[2] | vote[3];
+      named_bar_sync(1, kThreadsHybrid);  // the MMA warp reads the vote too
+      const uint32_t* v4 = vote + (group & 1) * 4;
+      const uint32_t active = v4[0] | v4[1] | v4[2] | v4[3];
       real_stages += __popc(active) * n_rchunks;
 
-      for (uint32_t rest = active; rest != 0; rest &= rest - 1) {
+      for (uint32_t rest = ok ? active : 0u; rest != 0; rest &= rest - 1) {
         const int kk = __ffs(rest) - 1;
         const int k = k0 + kk;
-        int j[kRowsPerThread];
-#pragma unroll
-        for (int i = 0; i < kRowsPerThread; ++i) j[i] = idx_s[kk * kTileM + row_lo + kRowStep * i];
+        int j[LPR];
+        if constexpr (LPR == 8) {
+          const int4 lo = *reinterpret_cast<const int4*>(rd_ptr + kk * kTileM);
+          const int4 hi = *reinterpret_cast<const int4*>(rd_ptr + kk * kTileM + 4);
+          j[0] = lo.x; j[1] = lo.y; j[2] = lo.z; j[3] = lo.w; j[4] = hi.x; j[5] = hi.y; j[6] = hi.z; j[7] = hi.w;
+        } else if constexpr (LPR == 4) {
+          const int4 lo = *reinterpret_cast<const int4*>(rd_ptr + kk * kTileM);
+          j[0] = lo.x; j[1] = lo.y; j[2] = lo.z; j[3] = lo.w;
+        } else {
+          const int2 lo = *reinterpret_cast<const int2*>(rd_ptr + kk * kTileM);
+          j[0] = lo.x; j[1] = lo.y;
+        }
         for (int rc = 0; rc < n_rchunks; ++rc) {
-          if (ok && !mbar_wait(bar_empty + 8 * stage, empty_parity)) ok = false;
-          if (ok) {
-            const int r0 = rc * epr;
-            const uint32_t a_dst = smem_u32(stage_base + static_cast<size_t>(stage) * stage_bytes);
-            const uint32_t full = bar_full + 8 * stage;
-            if (copies) {
-              const uint8_t* base = src_chunk + static_cast<long long>(r0) * ELEM;
+          if (!mbar_wait(empty, empty_parity)) {
+            ok = false;
+            rest = 0;  // leaves the offset loop after this one
+            break;
+          }
+          const int r0 = rc * epr;
+          const uint8_t* base = src_chunk + static_cast<long long>(r0) * ELEM;
 #pragma unroll
-              for (int i = 0; i < kRowsPerThread; ++i) {
-                const bool present = j[i] >= 0;
-                cp_async16(a_dst + dst_off[i],
-                           base + static_cast<unsigned long long>(present ? static_cast<uint32_t>(j[i]) : 0u) * src_pitch,
-                           present ? 16u : 0u);
-              }
+          for (int i = 0; i < LPR; ++i)
+            cp_async16_row(a_dst + i * kPassBytes,
+                           base + static_cast<unsigned long long>(static_cast<uint32_t>(max(j[i], 0))) * src_pitch, j[i]);
+          // delivered to the barrier by the copy unit once this thread's copies have landed
+          cp_async_arrive_noinc(full);
+          if (tid == 0) {
+            mbar_expect_tx(full, b_bytes);
+            const uint32_t b_dst = a_dst - (a_dst0 - stage0) + p.a_stage_bytes;
+            if (!B_MN) {
+              // weight viewed as [c_out][kv][c_in]: rows n = 0..n_dim-1 of offset k, reduction chunk r0
+              tma_load_3d(b_dst, &map_b, r0, k, 0, full);
+            } else {
+              // weight viewed as [c_out = reduction][kv][c_in]: rows r0.., one load per column block
+              for (int cb = 0; cb < ncb; ++cb)
+                tma_load_3d(b_dst + cb * epr * p.b_row_bytes, &map_b, cb * b_cols, k, r0, full);
             }
-            // delivered to the barrier by the copy unit once this thread's copies have landed
-            cp_async_arrive_noinc(full);
-            if (tid == 0) {
-              info[stage].ksteps = ksteps;
-              info[stage].last = 0;
-              mbar_expect_tx(full, b_bytes);
-              const uint32_t b_dst = a_dst + p.a_stage_bytes;
-              if (!B_MN) {
-                // weight viewed as [c_out][kv][c_in]: rows n = 0..n_dim-1 of offset k, reduction chunk r0
-                tma_load_3d(b_dst, &map_b, r0, k, 0, full);
-              } else {
-                // weight viewed as [c_out = reduction][kv][c_in]: rows r0.., one load per column block
-                for (int cb = 0; cb < ncb; ++cb)
-                  tma_load_3d(b_dst + cb * epr * p.b_row_bytes, &map_b, cb * b_cols, k, r0, full);
-              }
-            }
-            if (++stage == p.stages) {
-              stage = 0;
-              empty_parity ^= 1;
-            }
+          }
+          a_dst += stage_bytes;
+          full += 8;
+          empty += 8;
+          if (a_dst >= ring_end) {
+            a_dst = a_dst0;
+            full = bar_full;
+            empty = bar_empty;
+            empty_parity ^= 1;
           }
         }
       }
-      named_bar_sync(1, kIssueThreads);  // idx_s may be overwritten by the next group
+      // the table tile may be overwritten by the next group once every copy thread is done with it
+      if (k0 + kGroup < p.kv) named_bar_sync(2, kIssueThreads);
     }
-    // terminator stage: no data, tells the MMA warp the tile is complete
-    if (ok && !mbar_wait(bar_empty + 8 * stage, empty_parity)) ok = false;
-    if (ok) {
-      mbar_arrive(bar_full + 8 * stage);
-      if (tid == 0) {
-        info[stage].ksteps = 0;
-        info[stage].last = 1;
-        mbar_arrive(bar_full + 8 * stage);
-      }
-    } else {
+    if (!ok) {
       atomicExch(p.status, SPC_ERR_DEVICE_WAIT_EXPIRED);
       atomicExch(abort_flag, 1);
     }
     cp_async_wait_all();
 
-    // ---------------- epilogue (warps 0-3) ----------------
-    if (tile_warp) {
-      bool have_acc = mbar_wait(bar_accum, 0);
-      if (!have_acc) atomicExch(p.status, SPC_ERR_DEVICE_WAIT_EXPIRED);
-      have_acc = __all_sync(0xffffffffu, have_acc);
-      tc_fence_after();
-      if (have_acc) {
-        TO* out_row = static_cast<TO*>(p.out) + (my_row >= 0 ? my_row : 0) * p.n_dim;
-          const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-        for (int c0 = 0; c0 < p.n_dim; c0 += 16) {
-          float v[16];
-          if (real_stages > 0) {
-            uint32_t raw[16];
-            tmem_ld16(lane_addr + c0, raw);
-            tmem_ld_wait();
+    // ---------------- epilogue ----------------
+    bool have_acc = mbar_wait(bar_accum, 0);
+    if (!have_acc) atomicExch(p.status, SPC_ERR_DEVICE_WAIT_EXPIRED);
+    have_acc = __all_sync(0xffffffffu, have_acc);
+    tc_fence_after();
+    if (have_acc) {
+      TO* out_row = static_cast<TO*>(p.out) + (my_row >= 0 ? my_row : 0) * p.n_dim;
+      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+      for (int c0 = 0; c0 < p.n_dim; c0 += 16) {
+        float v[16];
+        if (real_stages > 0) {
+          uint32_t raw[16];
+          tmem_ld16(lane_addr + c0, raw);
+          tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < 16; ++q) v[q] = __uint_as_float(raw[q]);
-          } else {
+          for (int q = 0; q < 16; ++q) v[q] = __uint_as_float(raw[q]);
+        } else {
 #pragma unroll
-            for (int q = 0; q < 16; ++q) v[q] = 0.f;
-          }
-          if (my_row >= 0) {
-            if (has_epilogue) finish_epilogue16(v, epi_scale + c0, epi_shift + c0, p.epi.act, p.epi.alpha);
-            if (p.epi.residual != nullptr)
-              add_residual16<TO>(v, static_cast<const TO*>(p.epi.residual) + my_row * p.n_dim + c0);
-            store_row16<TO>(out_row + c0, v);
-          }
+          for (int q = 0; q < 16; ++q) v[q] = 0.f;
+        }
+        if (my_row >= 0) {
+          if (has_epilogue) finish_epilogue16(v, epi_scale + c0, epi_shift + c0, p.epi.act, p.epi.alpha);
+          if (p.epi.residual != nullptr)
+            add_residual16<TO>(v, static_cast<const TO*>(p.epi.residual) + my_row * p.n_dim + c0);
+          store_row16<TO>(out_row + c0, v);
         }
       }
-      tc_fence_before();
     }
+    tc_fence_before();
   } else {
     // ---------------- MMA issuer ----------------
     // One thread paces the whole CTA: every instruction between "stage full" and the commit is
     // on the critical path, so the loop carries running descriptor words (a stage advance is one
-    // add to the address field) and the reduction steps are unrolled.
-    if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | (TcType<T>::fmt << 7) | (TcType<T>::fmt << 10) |
-                             ((B_MN ? 1u : 0u) << 16) | (static_cast<uint32_t>(p.n_dim >> 3) << 17) |
-                             (static_cast<uint32_t>(kTileM >> 4) << 24);
-      const uint32_t a_type = layout_type_for(p.a_row_bytes);
-      const uint32_t b_type = B_MN ? layout_type_for(p.b_row_bytes) : a_type;
-      const uint32_t a_addr0 = smem_u32(stage_base);
-      const uint64_t a_desc0 = make_desc(a_addr0, 16, 8 * p.a_row_bytes, a_type);
-      const uint64_t b_desc0 = B_MN ? make_desc(a_addr0 + p.a_stage_bytes, epr * p.b_row_bytes, 8 * p.b_row_bytes, b_type)
-                                    : make_desc(a_addr0 + p.a_stage_bytes, 16, 8 * p.a_row_bytes, a_type);
-      const uint32_t a_hi = static_cast<uint32_t>(a_desc0 >> 32), b_hi = static_cast<uint32_t>(b_desc0 >> 32);
-      const uint32_t a_lo0 = static_cast<uint32_t>(a_desc0), b_lo0 = static_cast<uint32_t>(b_desc0);
-      const uint32_t stage_step = static_cast<uint32_t>(stage_bytes >> 4);  // address field counts 16-byte units
-      const uint32_t b_step = static_cast<uint32_t>(B_MN ? UMMA_K * p.b_row_bytes / 16 : 2);
-      const uint32_t info0 = smem_u32(info);
-      bool ok = true;
-
-      auto run = [&](auto ks_tag) {
-        constexpr int KS = decltype(ks_tag)::value;
-        uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full, empty = bar_empty, inf = info0;
-        uint32_t full_parity = 0, accumulate = 0;
-        int stage = 0;
-        while (true) {
-          // a wait that expires here is either a real failure or the producers having aborted
+    // add to the address field) and the reduction steps are unrolled.  The number of stages of a
+    // group follows from the copy warps' vote.
+    const uint32_t idesc = (1u << 4) | (TcType<T>::fmt << 7) | (TcType<T>::fmt << 10) |
+                           ((B_MN ? 1u : 0u) << 16) | (static_cast<uint32_t>(p.n_dim >> 3) << 17) |
+                           (static_cast<uint32_t>(kTileM >> 4) << 24);
+    const uint32_t a_type = layout_type_for(A_ROW_BYTES);
+    const uint32_t b_type = B_MN ? layout_type_for(p.b_row_bytes) : a_type;
+    const uint64_t a_desc0 = make_desc(stage0, 16, 8 * A_ROW_BYTES, a_type);
+    const uint64_t b_desc0 = B_MN ? make_desc(stage0 + p.a_stage_bytes, epr * p.b_row_bytes, 8 * p.b_row_bytes, b_type)
+                                  : make_desc(stage0 + p.a_stage_bytes, 16, 8 * A_ROW_BYTES, a_type);
+    const uint32_t a_hi = static_cast<uint32_t>(a_desc0 >> 32), b_hi = static_cast<uint32_t>(b_desc0 >> 32);
+    const uint32_t a_lo0 = static_cast<uint32_t>(a_desc0), b_lo0 = static_cast<uint32_t>(b_desc0);
+    const uint32_t stage_step = static_cast<uint32_t>(stage_bytes >> 4);  // address field counts 16-byte units
+    const uint32_t b_step = static_cast<uint32_t>(B_MN ? UMMA_K * p.b_row_bytes / 16 : 2);
+    uint32_t a_lo = a_lo0, b_lo = b_lo0, full = bar_full, empty = bar_empty;
+    uint32_t full_parity = 0, accumulate = 0;
+    int stage = 0;
+    bool ok = true;
+    int group = 0;
+    for (int k0 = 0; k0 < p.kv; k0 += kGroup, ++group) {
+      named_bar_sync(1, kThreadsHybrid);
+      const uint32_t* v4 = vote + (group & 1) * 4;
+      const int n_stages = __popc(v4[0] | v4[1] | v4[2] | v4[3]) * n_rchunks;
+      if (lane == 0 && ok) {
+        for (int s = 0; s < n_stages; ++s) {
+          // a wait that expires here is either a real failure or the copy warps having aborted
           if (!mbar_wait(full, full_parity)) {
             ok = false;
             break;
@@ -337,14 +357,8 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
           // those writes before the tensor core's async-proxy reads
           fence_proxy_async();
           tc_fence_after();
-          uint32_t ksteps;
-          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(ksteps) : "r"(inf) : "memory");
-          if (ksteps == 0) {  // terminator
-            tc_commit(bar_accum);
-            break;
-          }
 #pragma unroll
-          for (int ks = 0; ks < KS; ++ks) {
+          for (int ks = 0; ks < KSTEPS; ++ks) {
             const uint64_t a_desc = (static_cast<uint64_t>(a_hi) << 32) | (a_lo + 2u * ks);
             const uint64_t b_desc = (static_cast<uint64_t>(b_hi) << 32) | (b_lo + b_step * ks);
             tc_mma<TF32>(tmem_base, a_desc, b_desc, idesc, accumulate);
@@ -355,7 +369,6 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
           b_lo += stage_step;
           full += 8;
           empty += 8;
-          inf += static_cast<uint32_t>(sizeof(StageInfo));
           if (++stage == p.stages) {
             stage = 0;
             full_parity ^= 1;
@@ -363,14 +376,15 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
             b_lo = b_lo0;
             full = bar_full;
             empty = bar_empty;
-            inf = info0;
           }
         }
-      };
-      if (ksteps == 4) run(std::integral_constant<int, 4>{});
-      else if (ksteps == 2) run(std::integral_constant<int, 2>{});
-      else run(std::integral_constant<int, 1>{});
-      if (!ok) {
+      }
+      __syncwarp();
+    }
+    if (lane == 0) {
+      if (ok) {
+        tc_commit(bar_accum);  // arrives once every multiplication above has completed
+      } else {
         atomicExch(p.status, SPC_ERR_DEVICE_WAIT_EXPIRED);
         // release the epilogue warps: nothing more will be accumulated
         mbar_arrive(bar_accum);
@@ -424,14 +438,21 @@ int row_span(int elems, int elem_size) {
   return 0;
 }
 
-template <typename T, typename TO, bool B_MN>
-int launch_tma(TmaParams p, const CUtensorMap& map_b, size_t smem_bytes, cudaStream_t st) {
+template <typename T, typename TO, bool B_MN, int LPR>
+int launch_tma_rows(const TmaParams& p, const CUtensorMap& map_b, size_t smem_bytes, cudaStream_t st) {
   static bool configured[kMaxDevices] = {false};  // per instantiation and device
-  SPC_CUDA_OK(ensure_dynamic_smem(gather_gemm_tma_kernel<T, TO, B_MN>, 226 * 1024, configured));
+  SPC_CUDA_OK(ensure_dynamic_smem(gather_gemm_tma_kernel<T, TO, B_MN, LPR>, 226 * 1024, configured));
   const unsigned grid = static_cast<unsigned>(ceil_div(p.m_rows, kTileM));
-  gather_gemm_tma_kernel<T, TO, B_MN><<<grid, kThreadsHybrid, smem_bytes, st>>>(p, map_b);
+  gather_gemm_tma_kernel<T, TO, B_MN, LPR><<<grid, kThreadsHybrid, smem_bytes, st>>>(p, map_b);
   SPC_LAUNCH_OK();
   return SPC_OK;
+}
+
+template <typename T, typename TO, bool B_MN>
+int launch_tma(const TmaParams& p, const CUtensorMap& map_b, size_t smem_bytes, cudaStream_t st) {
+  if (p.a_row_bytes == 128) return launch_tma_rows<T, TO, B_MN, 8>(p, map_b, smem_bytes, st);
+  if (p.a_row_bytes == 64) return launch_tma_rows<T, TO, B_MN, 4>(p, map_b, smem_bytes, st);
+  return launch_tma_rows<T, TO, B_MN, 2>(p, map_b, smem_bytes, st);
 }
 
 }  // namespace
@@ -477,13 +498,12 @@ int gather_gemm_tma(const void* src, const void* w, const Epilogue& epi, const i
   // Everything besides the stages is sized to the layer.  As many CTAs per SM as shared memory
   // (228 KB per SM, 1 KB reserved per CTA), tensor memory (512 columns) and registers allow, as
   // long as each keeps at least two stages.
-  p.group_rows = std::min(kv, kGroup);
   p.epi_pad = (n_dim + 15) / 16 * 16;
   int cols = 32;
   while (cols < n_dim) cols <<= 1;
   p.tmem_cols = cols;
-  const size_t fixed = 1024 + static_cast<size_t>(p.group_rows) * kTileM * 4 + (2 * kMaxStages + 1) * 8 +
-                       kMaxStages * sizeof(StageInfo) + 64 + 2 * p.epi_pad * sizeof(float) + 16;
+  p.group_rows = std::min(kv, kGroup);
+  const size_t fixed = 1024 + static_cast<size_t>(p.group_rows) * kTileM * 4 + (2 * kMaxStages + 1) * 8 + 64 + 2 * p.epi_pad * sizeof(float) + 16;
   p.stages = 0;
   int ctas = std::min(kMaxCtasPerSm, 512 / cols) + 1;
   while (p.stages < 2 && ctas > 1) {

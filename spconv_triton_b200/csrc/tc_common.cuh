@@ -17,7 +17,7 @@ constexpr int kGroup = 32;  // kernel offsets voted on together
 constexpr int kMaxStages = 8;
 // A wait polls kSpinLimit times, then keeps polling against a wall-clock limit, so that a slow
 // tile (a long reduction, a preempted SM) is not mistaken for a failure while every wait still ends.
-constexpr uint32_t kSpinLimit = 1u << 16;
+constexpr uint32_t kSpinLimit = 1u << 10;
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // one second
 
 // ---- PTX wrappers --------------------------------------------------------
@@ -30,14 +30,18 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One try: the hardware may park the thread until the phase completes or, at the latest, for
+// about kWaitHintNs; a parked warp issues nothing, a spinning one takes issue slots and
+// shared-memory cycles from the warps that copy and multiply.
+constexpr uint32_t kWaitHintNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kWaitHintNs)
       : "memory");
   return ok != 0;
 }
@@ -49,7 +53,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
   const unsigned long long t0 = global_timer_ns();
   do {
-    for (uint32_t it = 0; it < 1024; ++it)
+    for (uint32_t it = 0; it < 16; ++it)
       if (mbar_try_wait(bar, parity)) return true;
   } while (global_timer_ns() - t0 < kWaitLimitNs);
   return false;
