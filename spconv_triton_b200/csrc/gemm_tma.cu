@@ -4,11 +4,12 @@
 // Same computation and tiling as gemm_tc.cu (128 output rows per CTA, fp32
 // accumulator in tensor memory).  What differs is how a shared-memory stage is
 // filled:
-//   * the 128 gathered feature rows are copied by four warps with 16-byte
-//     cp.async (8 lanes per row, a thread copies one 16-byte piece of 8 rows,
-//     zero fill for absent rows); each thread's
-//     completion is delivered to the stage's mbarrier by
-//     cp.async.mbarrier.arrive.noinc, so nobody waits for data;
+//   * the 128 gathered feature rows are copied with 16-byte cp.async by two
+//     groups of two warps that take the stages in turn (a row's pieces go to
+//     neighbouring lanes, a thread copies one piece of 16, 8 or 4 rows, absent
+//     rows are zero-filled by predicate); each thread's completion is
+//     delivered to the stage's mbarrier by cp.async.mbarrier.arrive.noinc, so
+//     nobody waits for data;
 //   * the weight slab W[:, k, chunk] arrives through one tiled 3-D TMA load
 //     (one per column block for the input gradient) completing on the same
 //     mbarrier with complete_tx::bytes.
@@ -22,10 +23,26 @@
 // sustains roughly one 512-byte operation per ~30 cycles per SM, below what
 // the LSU path reaches, so the rows go through cp.async.
 //
+// Other things measured on the same kernel (SubMConv3d k3, 383k rows, 67.6k
+// stages): one barrier arrival per warp instead of per thread (needs a
+// blocking cp.async.wait_group: slower), one polling warp per CTA with the
+// others parked in a hardware barrier (slower), mbarrier.test_wait spinning
+// instead of try_wait (same), the table tile in registers with shuffles
+// instead of shared memory (a fourth CTA per SM at 64 channels, but slower:
+// the select tree costs more than the table read), skipping the zero fill of
+// pieces that are still zero (slower: the bookkeeping costs more than the
+// copies), two CTAs with four stages instead of three with two (slower).
+// Timing the two loops with clock64 shows where a stage's ~1 000 cycles go at
+// 64 -> 64: the MMA thread waits ~500 cycles for the stage and spends ~560
+// issuing its four tcgen05.mma (about 100 cycles each with three CTAs feeding
+// one tensor core from shared memory), the copy warps ~220 cycles in the slot
+// wait and ~450 issuing copies and the arrival.
+//
 // Warp roles (160 threads): warps 0-3 load the tile's table entries, vote on the
 // active kernel offsets (32 at a time), issue the row copies and later run the
-// epilogue; thread 0 also issues the TMA weight loads; warp 4 issues
-// tcgen05.mma.  All waits are bounded.
+// epilogue; the first thread of a copy group also issues its stages' TMA
+// weight loads; warp 4 issues tcgen05.mma and counts the stages from the same
+// vote.  All waits are bounded.
 #include <cuda.h>
 
 #include <algorithm>
@@ -93,7 +110,9 @@ constexpr int kIssueWarps = 4;                        // warps that issue the fe
 constexpr int kIssueThreads = kIssueWarps * 32;       // 128
 constexpr int kMmaWarp = kIssueWarps;                 // warp 4
 constexpr int kThreadsHybrid = kIssueThreads + 32;    // 160
-constexpr int kPassBytes = kIssueThreads * 16;        // one copy per thread covers 2048 bytes of the tile
+constexpr int kCopyGroups = 2;                        // halves of the copy warps; stages alternate between them
+constexpr int kGroupThreads = kIssueThreads / kCopyGroups;  // 64
+constexpr int kPassBytes = kGroupThreads * 16;        // one copy per thread of a group covers 1024 bytes of the tile
 constexpr int kMaxCtasPerSm = 4;                      // 4 x 160 threads x 96 registers fit the register file
 
 // 16-byte copy into shared memory; zeros instead when row < 0 (the source is then not read).
@@ -115,7 +134,8 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
   constexpr int UMMA_K = 32 / ELEM;
   constexpr bool TF32 = TcType<T>::tf32;
   constexpr int A_ROW_BYTES = 16 * LPR;
-  constexpr int kRowsPass = kIssueThreads / LPR;
+  constexpr int kRowsPass = kGroupThreads / LPR;  // rows one copy per thread of a group covers: 8, 16, 32
+  constexpr int CP = kTileM / kRowsPass;          // copies per thread and stage: 16, 8, 4
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -142,7 +162,7 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(bar_full + 8 * s, kIssueThreads + 1);  // every copy thread + the weight-slab transaction
+      mbar_init(bar_full + 8 * s, kGroupThreads + 1);  // every thread of the stage's copy group + the weight-slab transaction
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_accum, 1);
@@ -179,18 +199,24 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
     const int ncb = B_MN ? (p.n_dim + b_cols - 1) / b_cols : 1;
     const uint32_t b_bytes = B_MN ? static_cast<uint32_t>(ncb * epr * p.b_row_bytes)
                                   : static_cast<uint32_t>(p.n_dim * A_ROW_BYTES);
-    const int chunk = tid & (LPR - 1), row_lo = tid / LPR;
-    // 128 / LPR rows further down the tile is 2048 bytes further and leaves the swizzle term
+    // Two copy groups of 64 threads take the stages in turn.  What a stage costs a copy warp
+    // besides its copies (the slot wait, the arrival, the loop) is a chain of some hundred
+    // cycles of latency that the MMA warp ends up waiting for; with two groups the chains of
+    // neighbouring stages overlap.
+    const int grp = tid / kGroupThreads, gt = tid % kGroupThreads;
+    const int chunk = gt & (LPR - 1), row_lo = gt / LPR;
+    // 64 / LPR rows further down the tile is 1024 bytes further and leaves the swizzle term
     // (row modulo 8, 4 or 2) alone: the i-th copy goes to a_dst + i * kPassBytes
     const uint32_t lin0 = static_cast<uint32_t>(row_lo * A_ROW_BYTES + chunk * 16);
     uint32_t a_dst = stage0 + (lin0 ^ (((lin0 >> 7) & static_cast<uint32_t>(LPR - 1)) << 4));  // this thread's piece of row_lo
     uint32_t full = bar_full, empty = bar_empty, empty_parity = 1;
+    uint32_t turn = 0;  // whose stage comes next
     const uint32_t a_dst0 = a_dst;
     const uint8_t* src_chunk = static_cast<const uint8_t*>(p.src) + chunk * 16;
     const uint32_t src_pitch = static_cast<uint32_t>(p.r_dim) * ELEM;
-    // the tile row `tid` is the (tid / kRowsPass)-th copy of copy thread row_lo = tid % kRowsPass
-    int* const wr_ptr = idx_s + (tid % kRowsPass) * LPR + tid / kRowsPass;
-    const int* const rd_ptr = idx_s + row_lo * LPR;
+    // the tile row `tid` is the (tid / kRowsPass)-th copy of the copy threads with row_lo = tid % kRowsPass
+    int* const wr_ptr = idx_s + (tid % kRowsPass) * CP + tid / kRowsPass;
+    const int* const rd_ptr = idx_s + row_lo * CP;
 
     int group = 0;
     for (int k0 = 0; k0 < p.kv; k0 += kGroup, ++group) {
@@ -232,44 +258,55 @@ gather_gemm_tma_kernel(const __grid_constant__ TmaParams p, const __grid_constan
       for (uint32_t rest = ok ? active : 0u; rest != 0; rest &= rest - 1) {
         const int kk = __ffs(rest) - 1;
         const int k = k0 + kk;
-        int j[LPR];
-        if constexpr (LPR == 8) {
-          const int4 lo = *reinterpret_cast<const int4*>(rd_ptr + kk * kTileM);
-          const int4 hi = *reinterpret_cast<const int4*>(rd_ptr + kk * kTileM + 4);
-          j[0] = lo.x; j[1] = lo.y; j[2] = lo.z; j[3] = lo.w; j[4] = hi.x; j[5] = hi.y; j[6] = hi.z; j[7] = hi.w;
-        } else if constexpr (LPR == 4) {
-          const int4 lo = *reinterpret_cast<const int4*>(rd_ptr + kk * kTileM);
-          j[0] = lo.x; j[1] = lo.y; j[2] = lo.z; j[3] = lo.w;
-        } else {
-          const int2 lo = *reinterpret_cast<const int2*>(rd_ptr + kk * kTileM);
-          j[0] = lo.x; j[1] = lo.y;
+        // this group's stages of the offset: every other one
+        if (n_rchunks == 1 && turn != static_cast<uint32_t>(grp)) {
+          turn ^= 1u;
+          a_dst += stage_bytes;
+          full += 8;
+          empty += 8;
+          if (a_dst >= ring_end) {
+            a_dst = a_dst0;
+            full = bar_full;
+            empty = bar_empty;
+            empty_parity ^= 1;
+          }
+          continue;
+        }
+        int j[CP];
+#pragma unroll
+        for (int q = 0; q < CP / 4; ++q) {
+          const int4 v = *reinterpret_cast<const int4*>(rd_ptr + kk * kTileM + 4 * q);
+          j[4 * q] = v.x; j[4 * q + 1] = v.y; j[4 * q + 2] = v.z; j[4 * q + 3] = v.w;
         }
         for (int rc = 0; rc < n_rchunks; ++rc) {
-          if (!mbar_wait(empty, empty_parity)) {
-            ok = false;
-            rest = 0;  // leaves the offset loop after this one
-            break;
-          }
-          const int r0 = rc * epr;
-          const uint8_t* base = src_chunk + static_cast<long long>(r0) * ELEM;
+          if (turn == static_cast<uint32_t>(grp)) {
+            if (!mbar_wait(empty, empty_parity)) {
+              ok = false;
+              rest = 0;  // leaves the offset loop after this one
+              break;
+            }
+            const int r0 = rc * epr;
+            const uint8_t* base = src_chunk + static_cast<long long>(r0) * ELEM;
 #pragma unroll
-          for (int i = 0; i < LPR; ++i)
-            cp_async16_row(a_dst + i * kPassBytes,
-                           base + static_cast<unsigned long long>(static_cast<uint32_t>(max(j[i], 0))) * src_pitch, j[i]);
-          // delivered to the barrier by the copy unit once this thread's copies have landed
-          cp_async_arrive_noinc(full);
-          if (tid == 0) {
-            mbar_expect_tx(full, b_bytes);
-            const uint32_t b_dst = a_dst - (a_dst0 - stage0) + p.a_stage_bytes;
-            if (!B_MN) {
-              // weight viewed as [c_out][kv][c_in]: rows n = 0..n_dim-1 of offset k, reduction chunk r0
-              tma_load_3d(b_dst, &map_b, r0, k, 0, full);
-            } else {
-              // weight viewed as [c_out = reduction][kv][c_in]: rows r0.., one load per column block
-              for (int cb = 0; cb < ncb; ++cb)
-                tma_load_3d(b_dst + cb * epr * p.b_row_bytes, &map_b, cb * b_cols, k, r0, full);
+            for (int i = 0; i < CP; ++i)
+              cp_async16_row(a_dst + i * kPassBytes,
+                             base + static_cast<unsigned long long>(static_cast<uint32_t>(max(j[i], 0))) * src_pitch, j[i]);
+            // delivered to the barrier by the copy unit once this thread's copies have landed
+            cp_async_arrive_noinc(full);
+            if (gt == 0) {
+              mbar_expect_tx(full, b_bytes);
+              const uint32_t b_dst = a_dst - (a_dst0 - stage0) + p.a_stage_bytes;
+              if (!B_MN) {
+                // weight viewed as [c_out][kv][c_in]: rows n = 0..n_dim-1 of offset k, reduction chunk r0
+                tma_load_3d(b_dst, &map_b, r0, k, 0, full);
+              } else {
+                // weight viewed as [c_out = reduction][kv][c_in]: rows r0.., one load per column block
+                for (int cb = 0; cb < ncb; ++cb)
+                  tma_load_3d(b_dst + cb * epr * p.b_row_bytes, &map_b, cb * b_cols, k, r0, full);
+              }
             }
           }
+          turn ^= 1u;
           a_dst += stage_bytes;
           full += 8;
           empty += 8;
