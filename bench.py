@@ -1075,17 +1075,26 @@ def main():
         p1.record(copy_stream)
     copy_stream.synchronize()
     d2h_gbps = 4 * n_probe * out.features.shape[1] * out.features.element_size() / (p0.elapsed_time(p1) * 1e-3) / 1e9
-    barrier()
-    mallocs1 = torch.cuda.memory_stats(dev).get("num_device_alloc", 0)
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    run_steps(args.steps, e2e_step)
-    e2e_drain()  # the last results have to be on the host before the clock stops
-    e3.record()
-    barrier()
+    # A cudaMalloc inside the region (the caching allocator growing a pool because the worker
+    # threads interleaved differently than in the warm-up) synchronises the device and is not the
+    # steady state: such a measurement is taken again, at most twice, and the count is reported.
+    e2e_attempts = 0
+    while True:
+        e2e_attempts += 1
+        barrier()
+        mallocs1 = torch.cuda.memory_stats(dev).get("num_device_alloc", 0)
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record()
+        run_steps(args.steps, e2e_step)
+        e2e_drain()  # the last results have to be on the host before the clock stops
+        e3.record()
+        barrier()
+        mallocs_e2e = torch.cuda.memory_stats(dev).get("num_device_alloc", 0) - mallocs1
+        if sum_over_ranks(mallocs_e2e) == 0 or e2e_attempts == 3:
+            break
+        d2h_bytes.clear()
     clocks.close_window()
     clocks.stop()
-    mallocs_e2e = torch.cuda.memory_stats(dev).get("num_device_alloc", 0) - mallocs1
     e2e_ms = max_over_ranks(e2.elapsed_time(e3))
     e2e_value = total_voxels / (e2e_ms * 1e-3) / 1e6
 
@@ -1163,7 +1172,7 @@ def main():
                 "in_flight": args.in_flight},
         "gpu_launches": int(launches),
         "allocator": {"device_mallocs_in_timed_region": int(mallocs_resident),
-                      "device_mallocs_in_e2e_timed_region": int(mallocs_e2e)},
+                      "device_mallocs_in_e2e_timed_region": int(mallocs_e2e), "e2e_measurements": e2e_attempts},
         "clocks": clocks.summary(),
         "rulebook_ms": {"per_indice_key": rulebook_ms, "per_step": rulebook_total_ms,
                         "timing": "CUDA events around each rulebook generation, run-ahead off (host read of the "

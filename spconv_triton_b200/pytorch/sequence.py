@@ -233,12 +233,16 @@ def forward(container, x):
         chain, side = _side_stream(dev, 0), _side_stream(dev, 1)
         # sized from the largest need per input voxel seen so far and rounded up coarsely, so that
         # passes over scenes of similar size ask the caching allocator for the same block again
-        per_voxel = plan.bytes_per_voxel or _ARENA_BYTES_PER_VOXEL
+        # [bytes, bytes per voxel] shared by the plans of all host threads: a thread that meets
+        # its largest scene late would otherwise grow its arena (one cudaMalloc, which
+        # synchronises the device) long after the others have
+        floor = container.__dict__.setdefault("_spc_arena_floor", [0, 0.0])
+        per_voxel = max(plan.bytes_per_voxel, floor[1]) or _ARENA_BYTES_PER_VOXEL
         arena_bytes = int(per_voxel * n_in * 1.2) + _ARENA_MARGIN
         arena_bytes = -(-arena_bytes // _ARENA_GRANULE) * _ARENA_GRANULE
         # never smaller than the last one: equal requests are what the caching allocator serves
         # from its free list without splitting or growing
-        arena_bytes = plan.arena_bytes = max(arena_bytes, plan.arena_bytes)
+        arena_bytes = plan.arena_bytes = floor[0] = max(arena_bytes, plan.arena_bytes, floor[0])
         needed = ctypes.c_size_t(0)
         for _attempt in range(4):
             arena = torch.empty(arena_bytes, dtype=torch.uint8, device=dev)
@@ -259,10 +263,10 @@ def forward(container, x):
             if rc != _lib.SPC_ERR_WORKSPACE_TOO_SMALL:
                 return None  # e.g. a layer without output points: the modules raise the proper error
             arena_bytes = int(needed.value * 1.5) + _ARENA_MARGIN
-            arena_bytes = plan.arena_bytes = -(-arena_bytes // _ARENA_GRANULE) * _ARENA_GRANULE
+            arena_bytes = plan.arena_bytes = floor[0] = -(-arena_bytes // _ARENA_GRANULE) * _ARENA_GRANULE
         else:
             return None
-        plan.bytes_per_voxel = max(plan.bytes_per_voxel, needed.value / n_in)
+        plan.bytes_per_voxel = floor[1] = max(plan.bytes_per_voxel, floor[1], needed.value / n_in)
         return _wrap(plan, x, indices, arena, dev, keep)
 
 

@@ -118,6 +118,7 @@ def test_arena_that_is_too_small_is_retried():
     old = sequence._ARENA_BYTES_PER_VOXEL, sequence._ARENA_MARGIN, sequence._ARENA_GRANULE
     sequence._ARENA_BYTES_PER_VOXEL, sequence._ARENA_MARGIN, sequence._ARENA_GRANULE = 64.0, 0, 4096
     net.__dict__.pop("_spc_plans", None)
+    net.__dict__.pop("_spc_arena_floor", None)
     try:
         got = _run(net, idx, feats, grid, batch, True)
         assert next(iter(net.__dict__["_spc_plans"].values())).bytes_per_voxel > 64.0
