@@ -245,10 +245,11 @@ def forward(container, x):
         arena_bytes = plan.arena_bytes = floor[0] = max(arena_bytes, plan.arena_bytes, floor[0])
         needed = ctypes.c_size_t(0)
         for _attempt in range(4):
+            # The rulebook streams touch the arena and the indices only inside the call, and the
+            # caller's stream joins both before the call returns: to the caching allocator the
+            # arena is a block of the caller's stream like any other (no record_stream, whose
+            # deferred frees made the pool grow in bursts when several threads run passes).
             arena = torch.empty(arena_bytes, dtype=torch.uint8, device=dev)
-            for t in (arena, indices):
-                t.record_stream(chain)
-                t.record_stream(side)
             rc = lib.spc_sequence_forward(ctypes.cast(plan.layers, ctypes.c_void_p), len(steps), indices.data_ptr(),
                                           feats.data_ptr(), n_in, _lib.dtype_code(feats.dtype), arena.data_ptr(),
                                           arena_bytes, ctypes.cast(ctypes.pointer(needed), ctypes.c_void_p),
