@@ -334,6 +334,15 @@ int spc_conv_forward(const void* features, const void* weight, const void* bias,
                      int out_dtype, int precision, int path, const float* out_scale,
                      const float* out_shift, int act, float act_alpha, void* stream);
 
+/* 1 if spc_conv_forward for this layer reads the column-major table pair_fwd, 0 if the
+ * row-major copy is all it reads (the tcgen05 kernel with TMA-fed weights).  In the
+ * second case pair_fwd may be NULL as long as pair_fwd_rowmajor is given, which lets a
+ * caller that owns both tables not write the one nobody reads (spc_sequence_forward
+ * does).  No counterpart in the reference, whose kernels read one table layout
+ * (spconv_triton/pytorch/ops.py:259-305). */
+int spc_conv_forward_needs_colmajor(int c_in, int c_out, int kv, int dtype, int out_dtype, int precision,
+                                    int path);
+
 /* spc_conv_forward with a residual connection fused into the store:
  *   out[m, n] = act((acc + bias[n]) * scale[n] + shift[n]) + residual[m, n]
  * residual [n_out, c_out] has the OUTPUT dtype (16-byte aligned, NULL = none) and is
@@ -465,7 +474,9 @@ typedef struct {
   int64_t n_in, n_out;
   uint64_t workspace, workspace_bytes;   /* rulebook workspace, as spc_rulebook_prepare left it */
   uint64_t out_indices;                  /* [n_out, ndim+1] int32 */
-  uint64_t pair_fwd;                     /* [kv, n_out] int32 */
+  uint64_t pair_fwd;                     /* [kv, n_out] int32; not produced when no layer that uses the
+                                            rulebook reads it (spc_conv_forward_needs_colmajor): it is
+                                            the transpose of pair_fwd_rowmajor[:, :kv] */
   uint64_t pair_fwd_rowmajor;            /* [n_out, kvp] int32 */
   uint64_t pair_mask;                    /* [n_out] int32 (one split, one word) */
   uint64_t mask_argsort;                 /* [n_out] int32 */

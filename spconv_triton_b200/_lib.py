@@ -108,6 +108,7 @@ _PROTOTYPES = {
     "spc_native_to_tables": (c_int, [_P, c_int, c_int64, c_int, _P, c_int64, _P, c_int64, _P]),
     "spc_conv_forward": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, _P, _P, c_int, ctypes.c_float, _P]),
+    "spc_conv_forward_needs_colmajor": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     "spc_conv_forward_residual": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int,
                                           c_int, c_int, c_int, _P, _P, c_int, ctypes.c_float, _P, _P]),
     "spc_conv_backward_input": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int, c_int, c_int, c_int,

@@ -26,6 +26,14 @@ bool want_tc(int path, int n_dim, int r_dim, int kv, int dtype, int out_dtype, i
 
 }  // namespace
 
+extern "C" int spc_conv_forward_needs_colmajor(int c_in, int c_out, int kv, int dtype, int out_dtype, int precision,
+                                               int path) {
+  const bool tma = path != SPC_GEMM_SIMT && path != SPC_GEMM_TCGEN05_CPASYNC &&
+                   gather_gemm_tc_supported(c_out, c_in, kv, dtype, out_dtype, precision, false) &&
+                   gather_gemm_tma_supported(c_out, c_in, kv, dtype, out_dtype, precision, false);
+  return tma ? 0 : 1;
+}
+
 extern "C" int spc_conv_forward(const void* features, const void* weight, const void* bias,
                                 const int32_t* pair_fwd, const int32_t* pair_fwd_rowmajor,
                                 const int32_t* mask_argsort, void* out,
@@ -43,8 +51,11 @@ extern "C" int spc_conv_forward_residual(const void* features, const void* weigh
                                          int c_in, int c_out, int kv, int dtype, int out_dtype, int precision,
                                          int path, const float* out_scale, const float* out_shift, int act,
                                          float act_alpha, const void* residual, void* stream) {
-  if (!features || !weight || !pair_fwd || !out || n_in < 0 || n_out < 0 || c_in <= 0 || c_out <= 0 || kv <= 0)
+  if (!features || !weight || !out || n_in < 0 || n_out < 0 || c_in <= 0 || c_out <= 0 || kv <= 0)
     return fail(SPC_ERR_INVALID_ARGUMENT, "conv_forward: bad arguments");
+  if (!pair_fwd && (!pair_fwd_rowmajor ||
+                    spc_conv_forward_needs_colmajor(c_in, c_out, kv, dtype, out_dtype, precision, path)))
+    return fail(SPC_ERR_INVALID_ARGUMENT, "conv_forward: this layer reads the column-major table");
   if ((out_scale == nullptr) != (out_shift == nullptr))
     return fail(SPC_ERR_INVALID_ARGUMENT, "conv_forward: out_scale and out_shift go together");
   if (n_out == 0) return SPC_OK;

@@ -615,7 +615,7 @@ fill_fwd_kernel(const __grid_constant__ Geo g, const int32_t* __restrict__ idx,
   const bool ranked = bitmap != nullptr && table_ranked(tin);
   // what is written for offset k once its input row j (-1: none) is known
   auto emit = [&](int k, int j) {
-    pair_fwd[static_cast<long long>(k) * n_out + r] = j;
+    if (pair_fwd != nullptr) pair_fwd[static_cast<long long>(k) * n_out + r] = j;
     if (SUBM_BWD) {
       pair_bwd[static_cast<long long>(g.kv - 1 - k) * n_out + r] = j;
       if (bwd_rm != nullptr) {
@@ -1514,8 +1514,9 @@ int rulebook_igemm_chained(const spc_geometry* sg, const int32_t* indices, int64
                            cudaStream_t st) {
   Geo g;
   if (!make_geo(sg, &g)) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook: bad geometry");
-  if (n_in <= 0 || n_out <= 0 || !indices || !workspace || !pair_fwd || !mask_fwd || !argsort_fwd ||
-      !split_masks || n_split < 1 || n_split > 2)
+  // pair_fwd may be absent when the row-major copy is all the caller's GEMMs read (native pass)
+  if (n_in <= 0 || n_out <= 0 || !indices || !workspace || (!pair_fwd && (!pair_fwd_rowmajor || pair_bwd)) || !mask_fwd ||
+      !argsort_fwd || !split_masks || n_split < 1 || n_split > 2)
     return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: bad arguments");
   if (!g.subm && out_indices == nullptr)
     return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: out_indices required for non-subm layers");
@@ -1559,6 +1560,7 @@ extern "C" int spc_rulebook_igemm(const spc_geometry* sg, const int32_t* indices
                                   int32_t* argsort_bwd, const uint32_t* split_masks, int n_split,
                                   int do_sort, int32_t* pair_fwd_rowmajor, int32_t* pair_bwd_rowmajor,
                                   void* stream) {
+  if (!pair_fwd) return fail(SPC_ERR_INVALID_ARGUMENT, "rulebook igemm: bad arguments");
   return rulebook_igemm_chained(sg, indices, n_in, n_out, workspace, workspace_bytes, out_indices, pair_fwd, pair_bwd,
                                 mask_fwd, argsort_fwd, mask_bwd, argsort_bwd, split_masks, n_split, do_sort,
                                 pair_fwd_rowmajor, pair_bwd_rowmajor, nullptr, static_cast<cudaStream_t>(stream));

@@ -133,7 +133,13 @@ extern "C" int spc_sequence_forward(const spc_seq_layer* layers, int n_layers, c
       R.n_out = n_out;
       if (n_out == 0) return fail(SPC_ERR_POINTS_VANISHED, "sequence_forward: layer %d has no output points", i);
       if (!subm) R.out_indices = arena.take(static_cast<size_t>(n_out) * (L.geom.ndim + 1) * 4);
-      R.pair_fwd = arena.take(static_cast<size_t>(kv) * n_out * 4);
+      // the column-major table only if a layer that uses this rulebook reads it
+      bool colmajor = false;
+      for (int j = i; j < n_layers; ++j)
+        if (layers[j].rulebook == i &&
+            spc_conv_forward_needs_colmajor(layers[j].c_in, layers[j].c_out, kv, dtype, dtype, SPC_PREC_IEEE, SPC_GEMM_AUTO))
+          colmajor = true;
+      if (colmajor) R.pair_fwd = arena.take(static_cast<size_t>(kv) * n_out * 4);
       R.pair_fwd_rowmajor = arena.take(static_cast<size_t>(n_out) * kvp * 4);
       R.pair_mask = arena.take(static_cast<size_t>(n_out) * 4);
       R.mask_argsort = arena.take(static_cast<size_t>(n_out) * 4);
@@ -142,7 +148,7 @@ extern "C" int spc_sequence_forward(const spc_seq_layer* layers, int n_layers, c
       SPC_CUDA_OK(cudaMemsetAsync(arena.at(R.num_per_loc), 0, static_cast<size_t>(kv) * 4, st));
       rc = rulebook_igemm_chained(&L.geom, cur_indices, cur_n, n_out, arena.at(R.workspace), ws_bytes,
                                   subm ? nullptr : static_cast<int32_t*>(arena.at(R.out_indices)),
-                                  static_cast<int32_t*>(arena.at(R.pair_fwd)), nullptr,
+                                  colmajor ? static_cast<int32_t*>(arena.at(R.pair_fwd)) : nullptr, nullptr,
                                   static_cast<int32_t*>(arena.at(R.pair_mask)),
                                   static_cast<int32_t*>(arena.at(R.mask_argsort)), nullptr, nullptr, &split_word, 1,
                                   /*do_sort=*/1, static_cast<int32_t*>(arena.at(R.pair_fwd_rowmajor)), nullptr,
@@ -168,7 +174,8 @@ extern "C" int spc_sequence_forward(const spc_seq_layer* layers, int n_layers, c
     SPC_CUDA_OK(cudaStreamWaitEvent(main, ev[L.rulebook], 0));
     R.features = arena.take(static_cast<size_t>(R.n_out) * L.c_out * esize);
     if (arena.overflow) break;
-    rc = spc_conv_forward(cur_features, L.weight, L.bias, static_cast<const int32_t*>(arena.at(G.pair_fwd)),
+    rc = spc_conv_forward(cur_features, L.weight, L.bias,
+                          G.pair_fwd != UINT64_MAX ? static_cast<const int32_t*>(arena.at(G.pair_fwd)) : nullptr,
                           static_cast<const int32_t*>(arena.at(G.pair_fwd_rowmajor)),
                           kv > 1 ? static_cast<const int32_t*>(arena.at(G.mask_argsort)) : nullptr, arena.at(R.features),
                           R.n_in, R.n_out, L.c_in, L.c_out, kv, dtype, dtype, SPC_PREC_IEEE, SPC_GEMM_AUTO, L.scale,

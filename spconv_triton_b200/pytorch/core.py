@@ -77,6 +77,21 @@ class ImplicitGemmIndiceData(_Record):
             self.__dict__.update(_pair_bwd=pair_bwd, _pair_mask_bwd_splits=pm_bwd, _mask_argsort_bwd_splits=ma_bwd)
         return self.__dict__[name]
 
+    # The column-major table may be pending too (the native pass writes only the row-major copy when
+    # that is all its kernels read): it is then the transpose of the copy, made when first read.
+    def _resolved_fwd(self):
+        d = self.__dict__
+        thunk = d.get("_pair_fwd_thunk")
+        if thunk is not None:
+            d["_pair_fwd_thunk"] = None
+            d["_pair_fwd"] = thunk()
+        return d["_pair_fwd"]
+
+    def _set_fwd(self, v):
+        self.__dict__["_pair_fwd_thunk"] = None
+        self.__dict__["_pair_fwd"] = v
+
+    pair_fwd = property(_resolved_fwd, _set_fwd)
     pair_bwd = property(lambda self: self._resolved("_pair_bwd"),
                         lambda self, v: self.__dict__.__setitem__("_pair_bwd", v))
     pair_mask_bwd_splits = property(lambda self: self._resolved("_pair_mask_bwd_splits"),

@@ -20,6 +20,7 @@ one by one as before.  Switch: ``constants.SPCONV_NATIVE_SEQUENCE``.
 from __future__ import annotations
 
 import ctypes
+import functools
 import threading
 
 import numpy as np
@@ -271,6 +272,20 @@ def forward(container, x):
         return _wrap(plan, x, indices, arena, dev, keep)
 
 
+_ABSENT = 0xFFFFFFFFFFFFFFFF  # offset of a table the pass did not produce
+
+
+def _column_major(rowmajor, kv, late, table=None):
+    """The [kv, n_out] table with the attributes the operator layer looks for on it; transposed out
+    of the row-major copy when the pass did not write it."""
+    if table is None:
+        table = rowmajor[:, :kv].t().contiguous()
+    table._spc_rowmajor = rowmajor
+    if late is not None:
+        table._spc_late = late
+    return table
+
+
 def _wrap(plan, x, indices, arena, dev, keep):
     """The output tensor and the rulebook cache entries, as views of the arena."""
     steps, results = plan.steps, plan.results
@@ -287,22 +302,27 @@ def _wrap(plan, x, indices, arena, dev, keep):
             cur_indices = _view(arena, R.out_indices, n_out * (ndim + 1), torch.int32, (n_out, ndim + 1))
         if c.indice_key is None:
             continue
-        pair_fwd = _view(arena, R.pair_fwd, kv * n_out, torch.int32, (kv, n_out))
-        pair_fwd._spc_rowmajor = _view(arena, R.pair_fwd_rowmajor, n_out * kvp, torch.int32, (n_out, kvp))
-        pm = _view(arena, R.pair_mask, n_out, torch.int32, (n_out, 1))
-        ma = _view(arena, R.mask_argsort, n_out, torch.int32, (n_out,))
-        masks = [np.array([0xFFFFFFFF], dtype=np.uint32)]
-        data = ImplicitGemmIndiceData(
-            in_indices if c.subm else cur_indices, in_indices, pair_fwd, torch.Tensor(), [pm], [], [ma], [], masks,
-            st.in_shape, st.out_shape, c.subm, c.algo, c.kernel_size, c.stride, c.dilation, c.padding)
+        rowmajor = _view(arena, R.pair_fwd_rowmajor, n_out * kvp, torch.int32, (n_out, kvp))
+        late = None
         if not c.subm:
             # the input-side tables stay pending; they are built from the workspace when somebody reads them
             p = _pairs._Prepared()
             p.geom, p.indices, p.n_in, p.n_out, p.out_shape, p.kv, p.subm = L.geom, in_indices, n_in, n_out, st.out_shape, kv, False
             p.workspace = arena[R.workspace:R.workspace + R.workspace_bytes]
             late = _pairs.LateTables(p, n_out, (ctypes.c_uint32 * 1)(0xFFFFFFFF), 1, True, 1)
-            pair_fwd._spc_late = late
-            data._late = late
+        if R.pair_fwd != _ABSENT:
+            pair_fwd = _column_major(rowmajor, kv, late, _view(arena, R.pair_fwd, kv * n_out, torch.int32, (kv, n_out)))
+        else:
+            pair_fwd = None  # not written: no layer of the pass reads it
+        pm = _view(arena, R.pair_mask, n_out, torch.int32, (n_out, 1))
+        ma = _view(arena, R.mask_argsort, n_out, torch.int32, (n_out,))
+        masks = [np.array([0xFFFFFFFF], dtype=np.uint32)]
+        data = ImplicitGemmIndiceData(
+            in_indices if c.subm else cur_indices, in_indices, pair_fwd, torch.Tensor(), [pm], [], [ma], [], masks,
+            st.in_shape, st.out_shape, c.subm, c.algo, c.kernel_size, c.stride, c.dilation, c.padding)
+        if pair_fwd is None:
+            data._pair_fwd_thunk = functools.partial(_column_major, rowmajor, kv, late)
+        data._late = late
         indice_dict[c.indice_key] = data
     last, R = steps[-1], results[len(steps) - 1]
     feats = _view(arena, R.features, int(R.n_out) * last.conv.out_channels, x.features.dtype,

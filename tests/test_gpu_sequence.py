@@ -48,6 +48,10 @@ def test_same_bits_as_the_modules_one_by_one():
     assert a.spatial_shape == b.spatial_shape and a.batch_size == b.batch_size
     assert torch.equal(a.indices, b.indices) and torch.equal(a.features, b.features)
     assert sorted(a.indice_dict) == sorted(b.indice_dict)
+    # the pass writes the column-major table only where one of its layers reads it (the 4 -> 16
+    # stem runs on the CUDA cores); elsewhere it is made from the row-major copy when first read
+    pending = [key for key, d in a.indice_dict.items() if d.__dict__.get("_pair_fwd_thunk") is not None]
+    assert pending and len(pending) < len(a.indice_dict), pending
     for key in a.indice_dict:
         da, db = a.indice_dict[key], b.indice_dict[key]
         assert da.is_subm == db.is_subm and da.ksize == db.ksize and da.stride == db.stride
