@@ -187,12 +187,15 @@ def run_train_arm(dev, rank, world, steps, warmup):
         opt.step()
         return loss
 
+    mallocs = []  # device allocations inside each timed region
+
     def timed(reducer):
         for i in range(warmup):
             step(i, reducer)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+        mallocs0 = torch.cuda.memory_stats(dev).get("num_device_alloc", 0)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(steps):
@@ -201,6 +204,7 @@ def run_train_arm(dev, rank, world, steps, warmup):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+        mallocs.append(torch.cuda.memory_stats(dev).get("num_device_alloc", 0) - mallocs0)
         ms = e0.elapsed_time(e1)
         if world > 1:
             t = torch.tensor([ms], dtype=torch.float64, device=dev)
@@ -216,7 +220,7 @@ def run_train_arm(dev, rank, world, steps, warmup):
         "scaling": "strong", "n_gpus": world, "steps": steps, "warmup": warmup,
         "voxels_per_step": int(np.mean(voxels)), "ms_per_step": ms / steps,
         "mvoxels_per_s": sum(voxels[i % len(voxels)] for i in range(steps)) / (ms * 1e-3) / 1e6,
-        "parameters": n_params, "loss": loss,
+        "parameters": n_params, "loss": loss, "device_mallocs_in_timed_region": mallocs[0],
     }
     if reducer is not None:
         # the same steps without the exchange: the difference is what the all-reduce costs when overlapped
@@ -1144,7 +1148,7 @@ def main():
     train = None
     if not args.no_train:
         torch.cuda.empty_cache()
-        train = run_train_arm(dev, rank, world, steps=max(3, min(args.steps, 10)), warmup=3)
+        train = run_train_arm(dev, rank, world, steps=max(3, min(args.steps, 10)), warmup=6)
 
     if rank != 0:
         clocks.summary()

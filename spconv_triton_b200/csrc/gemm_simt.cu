@@ -268,7 +268,21 @@ wgrad_thin_kernel(const T* __restrict__ feats, const T* __restrict__ gout, const
     __syncthreads();
     if (owner) {
       int p = grp;
-      for (; p + 3 * groups < total; p += 4 * groups) {  // four pairs in flight
+      // The blocks of the offsets most rows have (the in-plane ones of a wall or floor) carry most
+      // pairs and run on after the others have left the SM, so what a block's time follows is the
+      // number of dependent load round trips: sixteen pairs in flight per thread, then four.
+      for (; p + 15 * groups < total; p += 16 * groups) {
+        T g[16], f[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const int q = p + u * groups;
+          g[u] = gout[(base + list_o[q]) * c_out + n];
+          f[u] = feats[static_cast<long long>(list_i[q]) * c_in + c];
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) acc = fmaf(to_float(g[u]), to_float(f[u]), acc);
+      }
+      for (; p + 3 * groups < total; p += 4 * groups) {
         float g[4], f[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -295,6 +309,103 @@ wgrad_thin_kernel(const T* __restrict__ feats, const T* __restrict__ gout, const
 }
 
 inline bool wgrad_is_thin(int c_in, int c_out) { return c_in <= 8 && c_in * c_out <= kGemmThreads; }
+
+// Stem layers with four input channels and 16 or 32 output channels: a THREAD takes a pair (and
+// 16 of the output channels: PARTS = c_out / 16 thread groups per block walk the same rows).  It
+// loads the pair's 8 bytes of features and 32 bytes of output gradient with vector loads and keeps
+// its 64 products in registers, so a pair costs three loads in one or two threads instead of two
+// loads in each of 64 - 128 threads; two rows are in flight per thread, and the block's sums are
+// combined once at the end (warp shuffles, then shared memory, in a fixed order).  16-bit inputs.
+template <typename T, int PARTS>
+__global__ void __launch_bounds__(kGemmThreads, 2)
+wgrad_stem4_kernel(const T* __restrict__ feats, const T* __restrict__ gout, const int32_t* __restrict__ pair_fwd,
+                   float* __restrict__ partial, long long n_out, int kv, int splits, long long rows_per_split) {
+  constexpr int CIN = 4, NT = 16, COUT = NT * PARTS, GT = kGemmThreads / PARTS;
+  static_assert(sizeof(T) == 2, "16-bit inputs");
+  __shared__ float red[kGemmThreads / 32][CIN * NT];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int part = tid / GT, gt = tid % GT;
+  const int k = blockIdx.x / splits, split = blockIdx.x % splits;
+  const long long lo = split * rows_per_split;
+  const long long hi = min(n_out, lo + rows_per_split);
+  float acc[NT][CIN];
+#pragma unroll
+  for (int n = 0; n < NT; ++n)
+#pragma unroll
+    for (int c = 0; c < CIN; ++c) acc[n][c] = 0.f;
+  const int32_t* col = pair_fwd + static_cast<long long>(k) * n_out;
+  const T* gcol = gout + part * NT;
+  for (long long m0 = lo + gt; m0 < hi; m0 += 2 * GT) {
+    const long long m1 = m0 + GT;
+    const int r0 = __ldg(col + m0);
+    const int r1 = m1 < hi ? __ldg(col + m1) : -1;
+    uint2 f0 = make_uint2(0u, 0u), f1 = make_uint2(0u, 0u);
+    uint4 g0[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+    uint4 g1[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+    if (r0 >= 0) {
+      f0 = __ldg(reinterpret_cast<const uint2*>(feats + static_cast<long long>(r0) * CIN));
+      g0[0] = __ldg(reinterpret_cast<const uint4*>(gcol + m0 * COUT));
+      g0[1] = __ldg(reinterpret_cast<const uint4*>(gcol + m0 * COUT) + 1);
+    }
+    if (r1 >= 0) {
+      f1 = __ldg(reinterpret_cast<const uint2*>(feats + static_cast<long long>(r1) * CIN));
+      g1[0] = __ldg(reinterpret_cast<const uint4*>(gcol + m1 * COUT));
+      g1[1] = __ldg(reinterpret_cast<const uint4*>(gcol + m1 * COUT) + 1);
+    }
+    // an absent pair contributes zeros (its registers were cleared), in the same row order as a
+    // thread that walks one row at a time
+    {
+      const T* fh = reinterpret_cast<const T*>(&f0);
+      const T* gh = reinterpret_cast<const T*>(g0);
+      if (r0 >= 0) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          const float g = to_float(gh[n]);
+#pragma unroll
+          for (int c = 0; c < CIN; ++c) acc[n][c] = fmaf(g, to_float(fh[c]), acc[n][c]);
+        }
+      }
+    }
+    {
+      const T* fh = reinterpret_cast<const T*>(&f1);
+      const T* gh = reinterpret_cast<const T*>(g1);
+      if (r1 >= 0) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          const float g = to_float(gh[n]);
+#pragma unroll
+          for (int c = 0; c < CIN; ++c) acc[n][c] = fmaf(g, to_float(fh[c]), acc[n][c]);
+        }
+      }
+    }
+  }
+  // warps never straddle two parts (GT is a multiple of 32)
+  for (int pp = 0; pp < PARTS; ++pp) {
+    if (part == pp) {
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int c = 0; c < CIN; ++c) {
+          float v = acc[n][c];
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+          if (lane == 0) red[warp][n * CIN + c] = v;
+        }
+    }
+    __syncthreads();
+    if (tid < CIN * NT) {
+      float sum = 0.f;
+      for (int w = pp * (GT / 32); w < (pp + 1) * (GT / 32); ++w) sum += red[w][tid];
+      const int n = pp * NT + tid / CIN, c = tid % CIN;
+      partial[((static_cast<long long>(split) * COUT + n) * kv + k) * CIN + c] = sum;
+    }
+    __syncthreads();
+  }
+}
+
+inline bool wgrad_is_stem4(int c_in, int c_out, int dtype) {
+  return c_in == 4 && (c_out == 16 || c_out == 32) && (dtype == SPC_F16 || dtype == SPC_BF16);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -445,6 +556,21 @@ int wgrad_simt(const void* feats, const void* gout, const int32_t* pair_fwd, voi
   const bool thin = wgrad_is_thin(c_in, c_out);
   int e_pad = 1;
   while (e_pad < c_in * c_out) e_pad <<= 1;
+  if (wgrad_is_stem4(c_in, c_out, dtype) && (reinterpret_cast<uintptr_t>(feats) & 7u) == 0 &&
+      (reinterpret_cast<uintptr_t>(gout) & 15u) == 0) {
+    const unsigned blocks = static_cast<unsigned>(kv * s.splits);
+#define SPC_STEM(T, N)                                                                                  \
+    wgrad_stem4_kernel<T, N><<<blocks, kGemmThreads, 0, st>>>(static_cast<const T*>(feats),            \
+                                                               static_cast<const T*>(gout), pair_fwd, partial, \
+                                                               n_out, kv, s.splits, s.rows_per_split)
+    if (dtype == SPC_F16 && c_out == 16) SPC_STEM(__half, 1);
+    else if (dtype == SPC_F16) SPC_STEM(__half, 2);
+    else if (c_out == 16) SPC_STEM(__nv_bfloat16, 1);
+    else SPC_STEM(__nv_bfloat16, 2);
+#undef SPC_STEM
+    SPC_LAUNCH_OK();
+    return wgrad_reduce(partial, dw, elems, s.splits, dtype, st);
+  }
 #define SPC_WG(T)                                                                                   \
   do {                                                                                              \
     if (thin)                                                                                       \
