@@ -920,13 +920,18 @@ def main():
 
         dist.init_process_group("nccl", device_id=dev)
     args.warmup = max(args.warmup, 3)
-    # every pass in flight keeps a host thread waiting on the device (the reads of the output counts):
-    # no more of them per rank than cores are left beside the main thread
+    # every pass in flight keeps a host thread waiting on the device (the reads of the output counts)
     try:
         cores = len(os.sched_getaffinity(0))
     except AttributeError:
         cores = os.cpu_count() or 1
-    args.in_flight = max(1, min(args.in_flight, cores // world - 1))
+    if cores // world >= args.in_flight + 1:
+        pass  # a core per pass in flight and one for the main thread: the waits may spin
+    else:
+        # fewer cores than waiting threads: the library's waits sleep instead of spinning (read by
+        # the library at its first rulebook call), and the passes in flight still fit twice over
+        os.environ["SPC_HOST_WAIT"] = "block"
+        args.in_flight = max(1, min(args.in_flight, 2 * cores // world - 1))
 
     from spconv_triton_b200 import _lib
     import spconv_triton_b200.pytorch as sp

@@ -137,7 +137,10 @@ size_t spc_rulebook_workspace_bytes(const spc_geometry* g, int64_t n_in);
  * sorts the unique linear coordinates ascending (the order torch.unique
  * gives the reference) and numbers them.  Writes the number of output rows
  * to *n_out_host after synchronising `stream` (subm: n_out = n_in, no
- * synchronisation).  n_out == 0 is the reference's "points vanished" case. */
+ * synchronisation).  n_out == 0 is the reference's "points vanished" case.
+ * The synchronisation spins (cudaStreamSynchronize) unless the environment holds
+ * SPC_HOST_WAIT=block when the first call is made: then the thread sleeps on a
+ * blocking event, which suits processes with more waiting threads than cores. */
 int spc_rulebook_prepare(const spc_geometry* g, const int32_t* indices, int64_t n_in,
                          void* workspace, size_t workspace_bytes, int64_t* n_out_host,
                          void* stream);
