@@ -1153,7 +1153,7 @@ def main():
     train = None
     if not args.no_train:
         torch.cuda.empty_cache()
-        train = run_train_arm(dev, rank, world, steps=max(3, min(args.steps, 10)), warmup=6)
+        train = run_train_arm(dev, rank, world, steps=max(3, min(args.steps, 10)), warmup=10)
 
     if rank != 0:
         clocks.summary()
