@@ -177,3 +177,30 @@ def test_native_sequence_plan():
                                                  sp.SparseInverseConv3d(8, 4, 3, indice_key="d")).eval(), x) is None
     x.indice_dict["subm0"] = object()
     assert sequence._compile(net, x) is None
+
+
+def test_pending_column_major_table_of_a_cache_entry():
+    """An indice_dict entry whose column-major pair table was not written hands out the transpose
+    of the row-major copy at the first read, once, and an assignment replaces it."""
+    from spconv_triton_b200.core import ConvAlgo
+    from spconv_triton_b200.pytorch.core import ImplicitGemmIndiceData
+    from spconv_triton_b200.pytorch.sequence import _column_major
+
+    kv, n = 27, 5
+    rowmajor = torch.arange(n * 28, dtype=torch.int32).reshape(n, 28)
+    idx = torch.zeros((n, 4), dtype=torch.int32)
+    data = ImplicitGemmIndiceData(idx, idx, None, torch.Tensor(), [], [], [], [], [], [4, 4, 4], [4, 4, 4], True,
+                                  ConvAlgo.MaskImplicitGemm, [3] * 3, [1] * 3, [1] * 3, [1] * 3)
+    calls = []
+
+    def thunk():
+        calls.append(1)
+        return _column_major(rowmajor, kv, None)
+
+    data._pair_fwd_thunk = thunk
+    table = data.pair_fwd
+    assert table.shape == (kv, n) and table.is_contiguous()
+    assert torch.equal(table, rowmajor[:, :kv].t()) and table._spc_rowmajor is rowmajor
+    assert data.pair_fwd is table and len(calls) == 1
+    data.pair_fwd = rowmajor
+    assert data.pair_fwd is rowmajor and len(calls) == 1
