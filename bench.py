@@ -844,7 +844,7 @@ def run_op_bench(args):
             r = P.igemm_pairs(idx, batch, shape, [3] * 3, [2] * 3, [1] * 3, [1] * 3, [0] * 3, False, False, False, False)
             idx, shape = r[0], P.get_conv_output_size(shape, [3] * 3, [2] * 3, [1] * 3, [1] * 3)
         r = P.igemm_pairs(idx, batch, shape, [3] * 3, [1] * 3, [1] * 3, [1] * 3, [0] * 3, True, False, True, False)
-        pf, pb, maf, mab = r[2], r[3], r[6][0], r[6][0]
+        pf, pb, maf, mab, pmf, pmb = r[2], r[3], r[6][0], r[6][0], r[4][0], r[4][0]
         n, kv = idx.shape[0], pf.shape[0]
         pairs = int((pf >= 0).sum())
         for c in (32, 64, 128):
@@ -853,9 +853,10 @@ def run_op_bench(args):
             g = torch.randn(n, c, device=dev).half()
             flops = 2.0 * pairs * c * c
             nbytes = pairs * c * 2 + n * c * 2 + kv * n * 4 + kv * c * c * 2
-            emit(f"subm_fwd_{c}_{c}", timed(lambda: G.conv_forward(x, w, pf, n, mask_argsort=maf), iters), nbytes, flops,
-                 voxels=n, pairs=pairs)
-            emit(f"subm_dgrad_{c}_{c}", timed(lambda: G.conv_backward_input(g, w, pb, n, mask_argsort=mab), iters), nbytes, flops)
+            emit(f"subm_fwd_{c}_{c}", timed(lambda: G.conv_forward(x, w, pf, n, pair_mask=pmf, mask_argsort=maf), iters),
+                 nbytes, flops, voxels=n, pairs=pairs)
+            emit(f"subm_dgrad_{c}_{c}", timed(lambda: G.conv_backward_input(g, w, pb, n, pair_mask=pmb, mask_argsort=mab), iters),
+                 nbytes, flops)
             emit(f"subm_wgrad_{c}_{c}", timed(lambda: G.conv_backward_weight(x, g, pf, (c, kv, c)), iters),
                  pairs * 2 * c * 2 + kv * n * 4, flops)
     else:

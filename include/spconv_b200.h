@@ -485,6 +485,13 @@ typedef struct {
   uint64_t mask_argsort;                 /* [n_out] int32 */
   uint64_t num_per_loc;                  /* [kv] int32, zeros (as igemm_pairs returns) */
   uint64_t features;                     /* [n_out, c_out], dtype */
+  int64_t masks_are_exact;               /* 1: pair_mask / mask_argsort are what spc_rulebook_igemm emits (the
+                                            mask words sorted ascending, stable, and their argsort); 0: the pass
+                                            ordered the rows for its own GEMMs by a key that packs rows with
+                                            common kernel offsets into the same 128-row tile: mask_argsort is
+                                            that order, pair_mask the sorted keys, and the exact pair is the
+                                            stable sort of the mask words of pair_fwd_rowmajor (bit k of a
+                                            row's word = entry k >= 0) */
 } spc_seq_result;
 
 /* Inference forward of `n_layers` convolutions applied one after the other to

@@ -31,5 +31,10 @@ int rulebook_igemm_chained(const spc_geometry* g, const int32_t* indices, int64_
                            int32_t* argsort_bwd, const uint32_t* split_masks, int n_split, int do_sort,
                            int32_t* pair_fwd_rowmajor, int32_t* pair_bwd_rowmajor,
                            const RulebookProducer* producer, cudaStream_t stream);
+// do_sort == 2 in rulebook_igemm_chained asks for the tile-key order (rows grouped so that the 128
+// rows of a gather-GEMM tile share kernel offsets; mask_fwd then holds sorted keys, not sorted mask
+// words).  It applies to single-word masks, one split that keeps every bit and no input-side tables;
+// otherwise 2 means 1.  This tells a caller in advance which of the two it will get.
+bool rulebook_tile_key_applies(const spc_geometry* g, bool with_backward, const uint32_t* split_masks, int n_split);
 
 }  // namespace spc

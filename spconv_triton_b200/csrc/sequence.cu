@@ -151,9 +151,10 @@ extern "C" int spc_sequence_forward(const spc_seq_layer* layers, int n_layers, c
                                   colmajor ? static_cast<int32_t*>(arena.at(R.pair_fwd)) : nullptr, nullptr,
                                   static_cast<int32_t*>(arena.at(R.pair_mask)),
                                   static_cast<int32_t*>(arena.at(R.mask_argsort)), nullptr, nullptr, &split_word, 1,
-                                  /*do_sort=*/1, static_cast<int32_t*>(arena.at(R.pair_fwd_rowmajor)), nullptr,
+                                  /*do_sort=*/2, static_cast<int32_t*>(arena.at(R.pair_fwd_rowmajor)), nullptr,
                                   have_producer ? &producer : nullptr, st);
       if (rc != SPC_OK) return rc;
+      R.masks_are_exact = rulebook_tile_key_applies(&L.geom, false, &split_word, 1) ? 0 : 1;
       SPC_CUDA_OK(cudaEventRecord(ev[i], st));
       if (!subm) {
         producer = RulebookProducer{&L.geom, arena.at(R.workspace), cur_n};

@@ -92,6 +92,25 @@ class ImplicitGemmIndiceData(_Record):
         self.__dict__["_pair_fwd"] = v
 
     pair_fwd = property(_resolved_fwd, _set_fwd)
+
+    # ... and so may the sorted masks and their argsort: the native pass orders the rows for its own
+    # kernels by a different key and leaves a thunk that makes the exactly sorted pair.
+    def _resolved_masks(self, name):
+        d = self.__dict__
+        thunk = d.get("_masks_fwd_thunk")
+        if thunk is not None:
+            d["_masks_fwd_thunk"] = None
+            pm, ma = thunk()
+            if d.get("_pair_mask_fwd_splits") is None:  # not assigned by the user in the meantime
+                d["_pair_mask_fwd_splits"] = pm
+            if d.get("_mask_argsort_fwd_splits") is None:
+                d["_mask_argsort_fwd_splits"] = ma
+        return d[name]
+
+    pair_mask_fwd_splits = property(lambda self: self._resolved_masks("_pair_mask_fwd_splits"),
+                                    lambda self, v: self.__dict__.__setitem__("_pair_mask_fwd_splits", v))
+    mask_argsort_fwd_splits = property(lambda self: self._resolved_masks("_mask_argsort_fwd_splits"),
+                                       lambda self, v: self.__dict__.__setitem__("_mask_argsort_fwd_splits", v))
     pair_bwd = property(lambda self: self._resolved("_pair_bwd"),
                         lambda self, v: self.__dict__.__setitem__("_pair_bwd", v))
     pair_mask_bwd_splits = property(lambda self: self._resolved("_pair_mask_bwd_splits"),

@@ -49,7 +49,8 @@ class SeqResult(ctypes.Structure):
     _fields_ = [("n_in", ctypes.c_int64), ("n_out", ctypes.c_int64), ("workspace", ctypes.c_uint64),
                 ("workspace_bytes", ctypes.c_uint64), ("out_indices", ctypes.c_uint64), ("pair_fwd", ctypes.c_uint64),
                 ("pair_fwd_rowmajor", ctypes.c_uint64), ("pair_mask", ctypes.c_uint64),
-                ("mask_argsort", ctypes.c_uint64), ("num_per_loc", ctypes.c_uint64), ("features", ctypes.c_uint64)]
+                ("mask_argsort", ctypes.c_uint64), ("num_per_loc", ctypes.c_uint64), ("features", ctypes.c_uint64),
+                ("masks_are_exact", ctypes.c_int64)]
 
 
 class _Step:
@@ -286,6 +287,18 @@ def _column_major(rowmajor, kv, late, table=None):
     return table
 
 
+def _exact_masks(rowmajor, kv):
+    """``pair_mask_fwd_splits`` / ``mask_argsort_fwd_splits`` as the rulebook generator emits them (one
+    split): the rows' mask words sorted ascending, stable, and their argsort.  The pass itself orders
+    the rows by a different key (rows that share kernel offsets end up in the same GEMM tile), so
+    these two are made from the row-major table when somebody reads them."""
+    weights = torch.ones(kv, dtype=torch.int64, device=rowmajor.device) << torch.arange(kv, device=rowmajor.device)
+    words = ((rowmajor[:, :kv] >= 0).to(torch.int64) * weights).sum(1)
+    vals, args = torch.sort(words, stable=True)
+    vals = torch.where(vals >= 2 ** 31, vals - 2 ** 32, vals)  # the words are unsigned, the tensor is int32
+    return [vals.to(torch.int32).reshape(-1, 1)], [args.to(torch.int32)]
+
+
 def _wrap(plan, x, indices, arena, dev, keep):
     """The output tensor and the rulebook cache entries, as views of the arena."""
     steps, results = plan.steps, plan.results
@@ -314,12 +327,15 @@ def _wrap(plan, x, indices, arena, dev, keep):
             pair_fwd = _column_major(rowmajor, kv, late, _view(arena, R.pair_fwd, kv * n_out, torch.int32, (kv, n_out)))
         else:
             pair_fwd = None  # not written: no layer of the pass reads it
-        pm = _view(arena, R.pair_mask, n_out, torch.int32, (n_out, 1))
-        ma = _view(arena, R.mask_argsort, n_out, torch.int32, (n_out,))
+        exact = int(R.masks_are_exact) != 0
+        pm = [_view(arena, R.pair_mask, n_out, torch.int32, (n_out, 1))] if exact else None
+        ma = [_view(arena, R.mask_argsort, n_out, torch.int32, (n_out,))] if exact else None
         masks = [np.array([0xFFFFFFFF], dtype=np.uint32)]
         data = ImplicitGemmIndiceData(
-            in_indices if c.subm else cur_indices, in_indices, pair_fwd, torch.Tensor(), [pm], [], [ma], [], masks,
+            in_indices if c.subm else cur_indices, in_indices, pair_fwd, torch.Tensor(), pm, [], ma, [], masks,
             st.in_shape, st.out_shape, c.subm, c.algo, c.kernel_size, c.stride, c.dilation, c.padding)
+        if not exact:
+            data._masks_fwd_thunk = functools.partial(_exact_masks, rowmajor, kv)
         if pair_fwd is None:
             data._pair_fwd_thunk = functools.partial(_column_major, rowmajor, kv, late)
         data._late = late

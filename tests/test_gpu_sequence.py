@@ -52,6 +52,9 @@ def test_same_bits_as_the_modules_one_by_one():
     # stem runs on the CUDA cores); elsewhere it is made from the row-major copy when first read
     pending = [key for key, d in a.indice_dict.items() if d.__dict__.get("_pair_fwd_thunk") is not None]
     assert pending and len(pending) < len(a.indice_dict), pending
+    # the pass orders the rows of a rulebook for its own GEMM tiles; the sorted masks and their
+    # argsort, as the rulebook generator emits them, are made when read (and compared below)
+    assert all(d.__dict__.get("_masks_fwd_thunk") is not None for d in a.indice_dict.values())
     for key in a.indice_dict:
         da, db = a.indice_dict[key], b.indice_dict[key]
         assert da.is_subm == db.is_subm and da.ksize == db.ksize and da.stride == db.stride

@@ -204,3 +204,26 @@ def test_pending_column_major_table_of_a_cache_entry():
     assert data.pair_fwd is table and len(calls) == 1
     data.pair_fwd = rowmajor
     assert data.pair_fwd is rowmajor and len(calls) == 1
+
+
+def test_pending_sorted_masks_of_a_cache_entry():
+    """The sorted mask words and their argsort are made from the row-major table at the first read
+    of either: ascending as unsigned, ties in row order."""
+    from spconv_triton_b200.core import ConvAlgo
+    from spconv_triton_b200.pytorch.core import ImplicitGemmIndiceData
+    from spconv_triton_b200.pytorch.sequence import _exact_masks
+    import functools
+
+    kv = 27
+    present = torch.tensor([[1, 0, 1], [0, 0, 1], [1, 0, 1], [0, 0, 0], [1, 1, 1]], dtype=torch.bool)
+    rowmajor = torch.full((5, 28), -1, dtype=torch.int32)
+    rowmajor[:, [0, 13, 26]] = torch.where(present, torch.arange(15, dtype=torch.int32).reshape(5, 3), -1)
+    words = [(1 << 0) * int(p[0]) + (1 << 13) * int(p[1]) + (1 << 26) * int(p[2]) for p in present]
+    idx = torch.zeros((5, 4), dtype=torch.int32)
+    data = ImplicitGemmIndiceData(idx, idx, None, torch.Tensor(), None, [], None, [], [], [4, 4, 4], [4, 4, 4], True,
+                                  ConvAlgo.MaskImplicitGemm, [3] * 3, [1] * 3, [1] * 3, [1] * 3)
+    data._masks_fwd_thunk = functools.partial(_exact_masks, rowmajor, kv)
+    order = sorted(range(5), key=lambda r: (words[r], r))
+    assert data.mask_argsort_fwd_splits[0].tolist() == order
+    assert data.pair_mask_fwd_splits[0][:, 0].tolist() == [words[r] for r in order]
+    assert data.__dict__["_masks_fwd_thunk"] is None
